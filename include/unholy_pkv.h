@@ -1,0 +1,251 @@
+/* unholy_pkv.h — C ABI of the B200 paged KV-cache library (libunholy_pkv.so).
+ *
+ * Plain pointers and sizes only. Every pointer named "device" is CUDA device memory owned by the caller; the
+ * library never allocates or frees it (the reference's kernels never allocate either: src/rt/hip.hpp:39-83 is the
+ * caller's RAII). Every data-path entry point enqueues work on `stream` and returns without synchronising; a NULL
+ * stream is the default stream (src/rt/hip.hpp:11-19 convention). Return value: PKV_OK or an error code;
+ * pkv_last_error() gives the message of the calling thread's last failure. The C++ wrappers in
+ * unholy_b200/csrc/host/kernels.hpp keep the reference's signatures and turn a non-zero code into
+ * std::runtime_error, as UH_CHECK_LAUNCH does in the reference.
+ *
+ * There is no CPU fallback: without a CUDA device every data-path call returns PKV_ERR_CUDA.
+ *
+ * Types: bf16 = uint16_t bit patterns, fp8 (e4m3fn) = uint8_t, scales = e8m0 exponent bytes (src/kernels/ref.hpp:6-7).
+ */
+#ifndef UNHOLY_PKV_H
+#define UNHOLY_PKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PKV_API __attribute__((visibility("default")))
+#else
+#define PKV_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* pkv_stream_t; /* == cudaStream_t */
+
+enum {
+  PKV_OK = 0,
+  PKV_ERR_ARG = 1,    /* bad shape / pointer / alignment: nothing was launched */
+  PKV_ERR_CUDA = 2,   /* a CUDA runtime call failed (message has cudaGetErrorString) */
+  PKV_ERR_DEVICE = 3, /* a kernel's own bounds check tripped (see pkv_device_status) */
+  PKV_ERR_LIMIT = 4   /* a size exceeds a compiled-in maximum */
+};
+
+#define PKV_MAX_LAYERS 48     /* layers one pkv_step_run launch can take */
+#define PKV_FP4_ROW_DIM 128   /* indexer key width the fp4 page layout is defined for */
+
+PKV_API const char* pkv_last_error(void);
+PKV_API int pkv_abi_version(void);
+
+/* First failed device-side check since the last call (0 = none): bit 0..7 = kind (1 page id out of range,
+ * 2 chunk row out of range, 3 bounded wait gave up), the rest = an index identifying the entry. Synchronises the
+ * device. The kernels skip the offending access instead of faulting. */
+PKV_API int pkv_device_status(int* status_out);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Reference-shaped single-sequence entry points. `table` is ONE slot's row of the block table (device).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* store_rows — src/kernels/ref.hpp:92-100, src/kernels/ref_attn.hip:88-93,377-381.
+ * rows [n][width] bf16 -> logical rows [row0, row0+n): pool + (table[r/rpp]*rpp + r%rpp) * row_stride elements. */
+PKV_API int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* pool, const int32_t* table, int rows_per_page,
+                   int row_stride, int row0, pkv_stream_t stream);
+
+/* store_rows_fp4 — src/kernels/indexer.hpp:20-32, src/kernels/indexer.hip:18-53,802-806.
+ * rows [n][128] bf16 -> MXFP4: page p at pool + p*rows_per_page*68; rows_per_page code rows of 64 B (even column =
+ * low nibble) followed by rows_per_page scale rows of 4 e8m0 bytes. The reference fixes rows_per_page = 64. */
+PKV_API int pkv_store_rows_fp4(const uint16_t* rows, int n, uint8_t* pool, const int32_t* table, int rows_per_page, int row0,
+                       pkv_stream_t stream);
+
+/* load_rows_fp4 — src/kernels/indexer.hpp:34, src/kernels/indexer.hip:55-62. Decodes rows back to bf16 [n][128]. */
+PKV_API int pkv_load_rows_fp4(const uint8_t* pool, const int32_t* table, int rows_per_page, int row0, int n, uint16_t* out,
+                      pkv_stream_t stream);
+
+/* act_quant_fp8 — src/kernels/ref.hpp:22, src/kernels/ref_elem.hip:18-41,282-286. x bf16 [rows][ldx] ->
+ * q e4m3 [rows][cols], s e8m0 [rows][cols/block]; block in {32, 64, 128}. */
+PKV_API int pkv_act_quant_fp8(const uint16_t* x, int ldx, uint8_t* q, uint8_t* s, int rows, int cols, int block,
+                      pkv_stream_t stream);
+/* fake_quant_fp8 / fake_quant_fp4 — src/kernels/ref.hpp:24-25, src/kernels/ref_elem.hip:18-59,287-296. In place. */
+PKV_API int pkv_fake_quant_fp8(uint16_t* x, int ldx, int rows, int cols, int block, pkv_stream_t stream);
+PKV_API int pkv_fake_quant_fp4(uint16_t* x, int ldx, int rows, int cols, int block, pkv_stream_t stream);
+
+/* glm_store_latent — src/kernels/glm_fast.hpp:23-32, src/kernels/glm_fast.hip:29-51,752-756, with the row width,
+ * quantisation block and page size as parameters (the reference fixes 512 / 64 / 256). rows bf16 [n][width] of
+ * positions [s0, s0+n): codes[rid][width] and scales[rid][width/block] at rid = table[p/rpp]*rpp + p%rpp. */
+PKV_API int pkv_store_rows_fp8(const uint16_t* rows, int n, int width, int block, uint8_t* codes, uint8_t* scales,
+                       const int32_t* table, int rows_per_page, int s0, pkv_stream_t stream);
+
+/* copy_kernel — src/kernels/ref.hpp:90, src/kernels/ref_elem.hip:269-278,358-366. A byte copy executed by SMs
+ * (16-byte vectors when dst, src and bytes allow), ordered in `stream` like any kernel. */
+PKV_API int pkv_copy(void* dst, const void* src, size_t bytes, pkv_stream_t stream);
+
+/* The sparse gather as a standalone operation. Replaces the gather loop fused into the reference's attention kernels:
+ * src/kernels/attn_wmma.hip:75-113 (row_of + staging), src/kernels/ref_attn.hip:285-301, src/kernels/glm_fast.hip:190-195.
+ * idx device [T][k]; q_visible device [T]. Entry e of query t = logical row idx[t][e] of the slot; entries < 0 or
+ * >= q_visible[t] are masked and produce a row of zeros (src/kernels/attn_wmma.hip:107,277-291).
+ * out device bf16 [T][k][width], contiguous. */
+PKV_API int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows_per_page, int row_stride, int width,
+                    const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out, pkv_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Batched step: all chunks of a step (src/engine/step.hpp:20-26 Chunk, src/model/forward_ref.hpp:50-60 BatchDesc),
+ * for 1..PKV_MAX_LAYERS layers in ONE launch. Replaces the reference's one launch per (chunk, layer, pool)
+ * (src/model/forward_ref.hip:719-745,843-857) and the gather loops of its attention launches (:951-999).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+typedef struct pkv_chunk { /* src/engine/step.hpp:20-26 */
+  int32_t slot;            /* block-table row */
+  int32_t s0;              /* first logical row written */
+  int32_t n;               /* rows */
+  int32_t t0;              /* first batch row */
+} pkv_chunk;
+
+typedef struct pkv_layer { /* device pointers of one layer; any pair may be NULL to skip that part */
+  const uint16_t* rows;    /* bf16 [T][width]: the step's new KV rows */
+  uint16_t* row_pool;      /* bf16 [num_pages][rows_per_page][row_stride] */
+  const uint16_t* keys;    /* bf16 [T][128]: the step's new indexer keys */
+  uint8_t* key_pool_fp4;   /* MXFP4 pool, layout of pkv_store_rows_fp4 */
+  uint8_t* key_fp8_codes;  /* e4m3 [num_pages*rows_per_page][128] */
+  uint8_t* key_fp8_scales; /* e8m0 [num_pages*rows_per_page][128/fp8_block] */
+  const int32_t* idx;      /* int32 [Q][k] index lists (src/kernels/indexer.hpp:74 format: -1 padded) */
+  uint16_t* gathered;      /* bf16 [Q][k][width] */
+} pkv_layer;
+
+typedef struct pkv_step {
+  int32_t width;             /* bf16 values per KV row */
+  int32_t row_stride;        /* elements between pool rows (>= width) */
+  int32_t rows_per_page;
+  int32_t max_pages_per_seq; /* block-table width */
+  int32_t num_pages;         /* physical pages per pool; ids outside [0, num_pages) are reported, not dereferenced */
+  int32_t fp8_block;         /* 32, 64 or 128 (only read when fp8 key arrays are given) */
+  int32_t nchunks;
+  int32_t T;                 /* batch rows */
+  int32_t Q;                 /* query rows */
+  int32_t k;                 /* index-list width */
+  const int32_t* tables;     /* device [max_slots][max_pages_per_seq] (src/engine/step.hpp:100) */
+  const pkv_chunk* chunks;   /* device [nchunks] */
+  const int32_t* q_chunk;    /* device [Q]: index into chunks of the chunk the query row belongs to */
+  const int32_t* q_visible;  /* device [Q]: logical rows visible to the query (row >= visible is masked) */
+} pkv_step;
+
+enum {
+  PKV_DO_ROWS = 1,     /* append layer.rows into layer.row_pool */
+  PKV_DO_KEYS_FP4 = 2, /* quantise layer.keys into layer.key_pool_fp4 */
+  PKV_DO_KEYS_FP8 = 4, /* quantise layer.keys into layer.key_fp8_codes / key_fp8_scales */
+  PKV_DO_GATHER = 8,   /* gather layer.idx rows into layer.gathered */
+  PKV_VARIANT_BULK = 256 /* gather through the bulk-copy (TMA) pipeline instead of vector loads */
+};
+
+/* `layers` is a HOST array of L structs holding device pointers (copied into the launch parameters).
+ * When PKV_DO_ROWS and PKV_DO_GATHER are both set, an index that falls inside its own chunk's range
+ * [s0, s0+n) is read from layer.rows (the value being appended in this launch), everything else from the pool; the
+ * result equals "append, then gather" (the reference reads in-chunk window rows from the chunk the same way:
+ * src/kernels/attn_wmma.hip:84). Rows of other chunks appended in the same launch must not be gathered. */
+PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags, pkv_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Page moves: copy-on-write duplication, hole-filling compaction, migration between shards. The reference has no
+ * such operation (it never copies page payloads: src/engine/engine.cpp:284-336 shares full pages only); the copy
+ * primitive they generalise is copy_kernel (src/kernels/ref_elem.hip:269-278).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+typedef struct pkv_pool_desc {
+  const void* src_base; /* device (may be a peer device's mapped pool for migration) */
+  void* dst_base;       /* device; == src_base for moves inside one pool */
+  uint64_t page_bytes;  /* multiple of 16 */
+} pkv_pool_desc;
+
+/* For every pool p < npools and i < n: dst_base[p] + dst_ids[i]*page_bytes <- src_base[p] + src_ids[i]*page_bytes.
+ * `pools` is a HOST array (npools <= 128); src_ids/dst_ids are device int32 [n]. Source and destination id sets
+ * must be disjoint when src_base == dst_base. */
+PKV_API int pkv_copy_pages(const pkv_pool_desc* pools, int npools, const int32_t* src_ids, const int32_t* dst_ids, int n,
+                   int num_src_pages, int num_dst_pages, pkv_stream_t stream);
+
+/* Device memory sharing between the one-process-per-GPU shards (migration over NVLink with ordinary loads).
+ * pkv_ipc_export fills a 64-byte handle for a cudaMalloc'd base pointer; pkv_ipc_open maps a peer's handle into this
+ * process; pkv_ipc_close unmaps. pkv_device_alloc / pkv_device_free are cudaMalloc / cudaFree for callers that need
+ * an exportable allocation. */
+PKV_API int pkv_device_alloc(void** ptr_out, size_t bytes);
+PKV_API int pkv_device_free(void* ptr);
+PKV_API int pkv_ipc_export(void* base, unsigned char handle_out[64]);
+PKV_API int pkv_ipc_open(const unsigned char handle[64], void** ptr_out);
+PKV_API int pkv_ipc_close(void* ptr);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Page pool: the block allocator, prefix-cache bookkeeping and block tables of src/engine/engine.{hpp,cpp}
+ * (free_pages_/evictable_/page_by_hash_/page_info_/tables_: engine.hpp:258-306) as a host-side object, plus the
+ * copy-on-write, LRU-free and compaction rules. Host only; single-threaded like the engine thread.
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+typedef struct pkv_pool pkv_pool;
+
+PKV_API pkv_pool* pkv_pool_create(int num_pages, int page_tokens, int max_slots, int max_pages_per_seq, int prefix_cache);
+PKV_API void pkv_pool_destroy(pkv_pool* p);
+
+/* A sequence handle is a small integer owned by the pool. */
+PKV_API int pkv_pool_seq_open(pkv_pool* p);                 /* new empty sequence (no slot yet); returns handle >= 0 */
+/* match_prefix (engine.cpp:284-336) without the snapshot condition: shares every cached full page whose chained
+ * hash matches tokens[0..ntokens), up to (ntokens-1)/page_tokens pages (or `limit_pages` if >= 0). Returns the
+ * number of tokens covered. boundary_ok[i] (may be NULL = all) says whether the sequence may resume at the end of page
+ * i (the reference resumes only where a state snapshot was saved). */
+PKV_API int pkv_pool_match_prefix(pkv_pool* p, int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok);
+PKV_API int pkv_pool_assign_slot(pkv_pool* p, int seq);     /* free_slots_.back(); writes the table row; -1 if none */
+/* alloc_pages (engine.cpp:437-444): pages for positions [0, upto). Returns 1, or 0 (nothing changed) when the pool
+ * cannot supply them. */
+PKV_API int pkv_pool_alloc(pkv_pool* p, int seq, int upto);
+/* register_pages (engine.cpp:340-353): names the sequence's full pages below done_pos by the chained hash of
+ * tokens. */
+PKV_API int pkv_pool_register(pkv_pool* p, int seq, const int32_t* tokens, int ntokens, int done_pos);
+/* release (engine.cpp:208-232): unref pages tail first and give the slot back. The handle stays open and empty (a
+ * preempted request is admitted again later, engine.cpp:428-435); pkv_pool_seq_close releases and retires it. */
+PKV_API int pkv_pool_release(pkv_pool* p, int seq);
+PKV_API int pkv_pool_seq_close(pkv_pool* p, int seq);
+
+/* Copy-on-write fork: the new sequence shares ALL pages of positions [0, ntokens) of `from`, including a partial
+ * last page (refs++ each). Returns the new handle. */
+PKV_API int pkv_pool_fork(pkv_pool* p, int from, int ntokens);
+/* Before writing rows [s0, s0+n) of seq: every touched page with refs > 1 is replaced by take_page() in the
+ * sequence's table (old refs--). Emits the (src, dst) page pairs whose payload must be duplicated with
+ * pkv_copy_pages before the write. Returns the pair count, or -1 when the pool cannot supply the pages. */
+PKV_API int pkv_pool_cow(pkv_pool* p, int seq, int s0, int n, int32_t* src_out, int32_t* dst_out, int cap);
+/* Moves up to `count` pages from the LRU front of the evictable list to the free list (the evict branch of
+ * take_page, engine.cpp:239-245, without handing the page out). Returns how many were freed. */
+PKV_API int pkv_pool_free_lru(pkv_pool* p, int count, int32_t* freed_out, int cap);
+/* Hole-filling compaction: with W live pages, live ids >= W (ascending) move into free ids < W (ascending);
+ * tables, page info, hash map and LRU entries are rewritten and the free list rebuilt descending. Emits the moves for
+ * pkv_copy_pages. Returns the move count. */
+PKV_API int pkv_pool_compact(pkv_pool* p, int32_t* src_out, int32_t* dst_out, int cap);
+
+/* Migration between two pools (shards): the sequence's pages leave `src` (unref) and are taken from `dst` in
+ * logical order; returns the new handle in dst through seq_out and emits the (src page, dst page) pairs. */
+PKV_API int pkv_pool_migrate(pkv_pool* src, int seq, pkv_pool* dst, int* seq_out, int32_t* src_out, int32_t* dst_out,
+                     int cap);
+
+/* Introspection (tests, metrics: src/engine/engine.hpp:134-152 free_pages / cached_pages). */
+PKV_API int pkv_pool_available(const pkv_pool* p);       /* available_pages(): free + evictable (engine.hpp:181) */
+PKV_API int pkv_pool_free_count(const pkv_pool* p);      /* free_pages_.size() */
+PKV_API int pkv_pool_evictable_count(const pkv_pool* p); /* evictable_.size() */
+PKV_API int pkv_pool_cached_count(const pkv_pool* p);    /* page_by_hash_.size() */
+PKV_API int pkv_pool_seq_pages(const pkv_pool* p, int seq, int32_t* out, int cap);
+PKV_API int pkv_pool_seq_slot(const pkv_pool* p, int seq);
+PKV_API int pkv_pool_page_refs(const pkv_pool* p, int page);
+PKV_API uint64_t pkv_pool_page_hash(const pkv_pool* p, int page); /* 0 when not cached */
+PKV_API int pkv_pool_dirty(pkv_pool* p);                 /* tables_dirty_: 1 once since the last pkv_pool_tables call */
+/* tables_ [max_slots][max_pages_per_seq] (host pointer, valid until the pool is destroyed); clears the dirty flag. */
+PKV_API const int32_t* pkv_pool_tables(pkv_pool* p);
+PKV_API int pkv_pool_free_list(const pkv_pool* p, int32_t* out, int cap);      /* in vector order (back is taken next) */
+PKV_API int pkv_pool_evictable_list(const pkv_pool* p, int32_t* out, int cap); /* oldest first */
+/* The chained page hash (engine.cpp:257-280) of page `page_index` of a token sequence. */
+PKV_API uint64_t pkv_page_hash(const int32_t* tokens, int page_tokens, int page_index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UNHOLY_PKV_H */

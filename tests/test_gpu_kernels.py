@@ -1,0 +1,338 @@
+"""Parity of the CUDA kernels with the CPU oracle, bit for bit, through the C ABI.
+
+The shapes follow the reference's own kernel tests: shuffled block tables (tools/kernel_test/indexer.hip:66-69,
+tools/kernel_test/attn.hip:70-121), key rows with per-row magnitudes over several octaves (indexer.hip:57-60), the
+fp4 store -> load round trip equal to fake_quant_fp4 (indexer.hip:82-95), poison-filled outputs (indexer.hip:130)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import pkv_testlib as tl
+from oracle import oracle_lib as orc
+from unholy_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+def special_values(g, n, dim):
+    """bf16 rows full of rounding edge cases: exact ties of both grids at several scales, zeros of both signs,
+    subnormals, the largest finite values."""
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 7.0, 448.0, 480.0, 416.0,
+                     0.001953125, 0.0009765625, 0.0029296875, 17.0, 19.0, 0.0], np.float32)
+    x = g.choice(ties, size=(n, dim)).astype(np.float32)
+    x *= np.ldexp(np.float32(1.0), g.integers(-20, 20, size=(n, 1))).astype(np.float32)
+    x *= g.choice(np.array([-1.0, 1.0], np.float32), size=(n, dim))
+    b = orc.f32_to_bf16_bits(x)
+    b[0, :] = 0                      # all +0: amax floor
+    b[1, :] = 0x8000                 # all -0
+    b[2, :] = 0x0001                 # smallest subnormal
+    b[3, :] = 0x7F7F                 # largest finite
+    b[4, ::2] = 0xFF7F               # mixed signs of the largest
+    b[5, :] = g.integers(0, 0x7F80, size=dim).astype(np.uint16)  # any positive finite pattern
+    b[6, :] = (g.integers(0, 0x7F80, size=dim) | 0x8000).astype(np.uint16)
+    return b
+
+
+def shuffled_table(g, pages):
+    return g.permutation(pages).astype(np.int32)
+
+
+@pytest.mark.parametrize("width,stride,n,row0", [(576, 576, 300, 37), (576, 640, 129, 0), (512, 512, 64, 63),
+                                                 (100, 104, 70, 5), (7, 9, 33, 1), (576, 576, 1, 200)])
+def test_store_rows(pkv, cuda, width, stride, n, row0):
+    g = tl.rng(11)
+    rpp, pages = 64, 8
+    table = shuffled_table(g, pages)
+    rows = tl.normal_bf16(g, (n, width))
+    pool0 = np.full((pages * rpp, stride), 0x5A5A, np.uint16)
+    want = pool0.copy()
+    orc.store_rows(rows, want, table, rpp, stride, row0)
+    d_rows, d_pool, d_table = tl.dev(cuda, rows), tl.dev(cuda, pool0), tl.dev(cuda, table)
+    capi.check(pkv.pkv_store_rows(d_rows.data_ptr(), n, width, d_pool.data_ptr(), d_table.data_ptr(), rpp, stride, row0,
+                                  tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    got = tl.host(d_pool, np.uint16, want.shape)
+    assert np.array_equal(got, want)
+    assert tl.device_status(pkv) == 0
+
+
+def test_store_rows_empty_and_bad_args(pkv, cuda):
+    assert pkv.pkv_store_rows(None, 0, 576, None, None, 64, 576, 0, None) == capi.PKV_OK
+    d = cuda.zeros(64, dtype=cuda.uint8, device="cuda")
+    assert pkv.pkv_store_rows(d.data_ptr(), 1, 576, d.data_ptr(), d.data_ptr(), 64, 100, 0, None) == capi.PKV_ERR_ARG
+    assert b"bad shape" in pkv.pkv_last_error()
+    assert pkv.pkv_act_quant_fp8(d.data_ptr(), 128, d.data_ptr(), d.data_ptr(), 1, 128, 48, None) == capi.PKV_ERR_ARG
+
+
+@pytest.mark.parametrize("kind", ["normal", "special"])
+def test_store_rows_fp4_and_round_trip(pkv, cuda, kind):
+    g = tl.rng(12)
+    rpp, pages, n, row0 = 64, 12, 700, 19
+    table = shuffled_table(g, pages)
+    rows = tl.key_rows(g, n) if kind == "normal" else special_values(g, n, 128)
+    pool0 = np.full(pages * rpp * 68, 0x5A, np.uint8)
+    want = pool0.copy()
+    orc.store_rows_fp4(rows, want, table, rpp, row0)
+    d_rows, d_pool, d_table = tl.dev(cuda, rows), tl.dev(cuda, pool0), tl.dev(cuda, table)
+    st = tl.stream_ptr(cuda)
+    capi.check(pkv.pkv_store_rows_fp4(d_rows.data_ptr(), n, d_pool.data_ptr(), d_table.data_ptr(), rpp, row0, st))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_pool, np.uint8), want)
+    # round trip: decoded rows == fake_quant_fp4 of the inputs (tools/kernel_test/indexer.hip:82-95), on the GPU ...
+    d_back = cuda.empty(n * 128 * 2, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_load_rows_fp4(d_pool.data_ptr(), d_table.data_ptr(), rpp, row0, n, d_back.data_ptr(), st))
+    capi.check(pkv.pkv_fake_quant_fp4(d_rows.data_ptr(), 128, n, 128, 32, st))
+    cuda.cuda.synchronize()
+    back, fake = tl.host(d_back, np.uint16, (n, 128)), tl.host(d_rows, np.uint16, (n, 128))
+    assert np.array_equal(back, fake)
+    # ... and both equal the oracle's
+    want_back = orc.load_rows_fp4(want, table, rpp, 128, row0, n)
+    want_fake = rows.copy()
+    orc.fake_quant_fp4(want_fake, 128, 32)
+    assert np.array_equal(back, want_back)
+    assert np.array_equal(fake, want_fake)
+
+
+@pytest.mark.parametrize("block", [32, 64, 128])
+@pytest.mark.parametrize("kind", ["normal", "outliers", "special"])
+def test_act_quant_fp8(pkv, cuda, block, kind):
+    g = tl.rng(13 + block)
+    rows, cols, ldx = 257, 512, 520
+    x = np.zeros((rows, ldx), np.uint16)
+    x[:, :cols] = {"normal": lambda: tl.normal_bf16(g, (rows, cols)), "outliers": lambda: tl.outlier_rows(g, rows, cols),
+                   "special": lambda: special_values(g, rows, cols)}[kind]()
+    x[:, cols:] = 0x1234
+    wq, ws = orc.act_quant_fp8(x, cols, block)
+    d_x = tl.dev(cuda, x)
+    d_q = cuda.full((rows * cols,), 0x5A, dtype=cuda.uint8, device="cuda")
+    d_s = cuda.full((rows * (cols // block),), 0x5A, dtype=cuda.uint8, device="cuda")
+    st = tl.stream_ptr(cuda)
+    capi.check(pkv.pkv_act_quant_fp8(d_x.data_ptr(), ldx, d_q.data_ptr(), d_s.data_ptr(), rows, cols, block, st))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_q, np.uint8, wq.shape), wq)
+    assert np.array_equal(tl.host(d_s, np.uint8, ws.shape), ws)
+    wf = x.copy()
+    orc.fake_quant_fp8(wf, cols, block)
+    capi.check(pkv.pkv_fake_quant_fp8(d_x.data_ptr(), ldx, rows, cols, block, st))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_x, np.uint16, wf.shape), wf)
+
+
+def test_fake_quant_unaligned(pkv, cuda):
+    """ldx not a multiple of 8 and a base pointer off the 16-byte grid take the scalar load path."""
+    g = tl.rng(14)
+    rows, cols, ldx = 33, 64, 67
+    x = tl.normal_bf16(g, (rows, ldx))
+    for fn, ofn, block in ((pkv.pkv_fake_quant_fp8, orc.fake_quant_fp8, 64), (pkv.pkv_fake_quant_fp4, orc.fake_quant_fp4, 32)):
+        want = x.copy()
+        ofn(want, cols, block)
+        buf = cuda.zeros(x.nbytes + 16, dtype=cuda.uint8, device="cuda")
+        buf[2:2 + x.nbytes] = tl.dev(cuda, x)
+        capi.check(fn(buf.data_ptr() + 2, ldx, rows, cols, block, tl.stream_ptr(cuda)))
+        cuda.cuda.synchronize()
+        assert np.array_equal(tl.host(buf[2:2 + x.nbytes].contiguous(), np.uint16, x.shape), want)
+
+
+@pytest.mark.parametrize("width,block,rpp", [(512, 64, 256), (128, 64, 64), (128, 128, 64), (128, 32, 64)])
+def test_store_rows_fp8(pkv, cuda, width, block, rpp):
+    g = tl.rng(15)
+    pages, n, s0 = 6, 3 * rpp + 17, rpp - 5
+    table = shuffled_table(g, pages)
+    rows = tl.outlier_rows(g, n, width)
+    codes0 = np.full((pages * rpp, width), 0x5A, np.uint8)
+    scales0 = np.full((pages * rpp, width // block), 0x5A, np.uint8)
+    wc, ws = codes0.copy(), scales0.copy()
+    orc.store_rows_fp8(rows, block, wc, ws, table, rpp, s0)
+    d_rows, d_c, d_s, d_t = tl.dev(cuda, rows), tl.dev(cuda, codes0), tl.dev(cuda, scales0), tl.dev(cuda, table)
+    capi.check(pkv.pkv_store_rows_fp8(d_rows.data_ptr(), n, width, block, d_c.data_ptr(), d_s.data_ptr(), d_t.data_ptr(),
+                                      rpp, s0, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_c, np.uint8, wc.shape), wc)
+    assert np.array_equal(tl.host(d_s, np.uint8, ws.shape), ws)
+
+
+@pytest.mark.parametrize("nbytes,off", [(1 << 20, 0), (12345, 0), (4096, 3), (16, 0), (1, 0)])
+def test_copy(pkv, cuda, nbytes, off):
+    g = tl.rng(16)
+    src = g.integers(0, 256, size=nbytes + 32, dtype=np.uint8)
+    d_src = tl.dev(cuda, src)
+    d_dst = cuda.full((nbytes + 32,), 0x5A, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_copy(d_dst.data_ptr() + off, d_src.data_ptr() + off, nbytes, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    got = tl.host(d_dst, np.uint8)
+    assert np.array_equal(got[off:off + nbytes], src[off:off + nbytes])
+    assert (got[:off] == 0x5A).all() and (got[off + nbytes:] == 0x5A).all()
+
+
+def test_gather_rows_single_table(pkv, cuda):
+    """One sequence, one block-table row: the shape of one reference attention call (tools/kernel_test/attn.hip:70-121)."""
+    g = tl.rng(17)
+    rpp, pages, width, T, k = 64, 40, 576, 5, 512
+    nrows = pages * rpp
+    table = shuffled_table(g, pages)
+    pool = tl.normal_bf16(g, (nrows, width))
+    visible = np.array([nrows, nrows - 100, 600, 1, 0], np.int32)
+    idx = np.full((T, k), -1, np.int32)
+    for t in range(T):
+        m = min(k - 7 * t, max(int(visible[t]), 1))
+        idx[t, :m] = g.choice(nrows, size=m, replace=False)  # unsorted, some beyond `visible`: masked
+    want = orc.gather_rows(pool, table.reshape(1, -1), rpp, width, width, idx, np.zeros(T, np.int32), visible)
+    d_pool, d_table, d_idx, d_vis = tl.dev(cuda, pool), tl.dev(cuda, table), tl.dev(cuda, idx), tl.dev(cuda, visible)
+    d_out = cuda.full((T * k * width * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_gather_rows(d_pool.data_ptr(), d_table.data_ptr(), rpp, width, width, d_idx.data_ptr(),
+                                   d_vis.data_ptr(), T, k, d_out.data_ptr(), tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
+
+
+def run_step(pkv, cuda, case, L, flags, fp8_block=64, poison=True):
+    """Runs pkv_step_run over L layers that share the case's tables but own their pools, rows, keys and index lists
+    (layer l's inputs are the case's rotated by l). Returns per-layer device results as numpy arrays."""
+    d_tables, d_chunks = tl.dev(cuda, case.tables), tl.dev(cuda, case.chunks)
+    d_qchunk, d_qvis = tl.dev(cuda, case.q_chunk), tl.dev(cuda, case.q_visible)
+    step = tl.make_step(case, d_tables, d_chunks, d_qchunk, d_qvis, fp8_block=fp8_block)
+    layers = tl.make_layers(L)
+    keep, per_layer = [d_tables, d_chunks, d_qchunk, d_qvis], []
+    nrows = case.num_pages * case.rpp
+    for l in range(L):
+        inp = {
+            "pool": np.roll(case.pool, l, axis=0), "rows": np.roll(case.rows, l, axis=1),
+            "keys": np.roll(case.keys, l, axis=1), "idx": case.idx,
+        }
+        d = {k: tl.dev(cuda, v) for k, v in inp.items()}
+        d["fp4"] = cuda.full((case.num_pages * case.rpp * 68,), 0x5A, dtype=cuda.uint8, device="cuda")
+        d["codes"] = cuda.full((nrows * 128,), 0x5A, dtype=cuda.uint8, device="cuda")
+        d["scales"] = cuda.full((nrows * (128 // fp8_block),), 0x5A, dtype=cuda.uint8, device="cuda")
+        d["out"] = cuda.full((case.idx.shape[0] * case.k * case.width * 2,), 0x5A if poison else 0, dtype=cuda.uint8, device="cuda")
+        y = layers[l]
+        y.rows, y.row_pool, y.keys = d["rows"].data_ptr(), d["pool"].data_ptr(), d["keys"].data_ptr()
+        y.key_pool_fp4, y.key_fp8_codes, y.key_fp8_scales = d["fp4"].data_ptr(), d["codes"].data_ptr(), d["scales"].data_ptr()
+        y.idx, y.gathered = d["idx"].data_ptr(), d["out"].data_ptr()
+        keep.append(d)
+        per_layer.append((inp, d))
+    capi.check(pkv.pkv_step_run(C.byref(step), layers, L, flags, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert tl.device_status(pkv) == 0
+    return per_layer
+
+
+def check_step(case, per_layer, flags, fp8_block=64):
+    nrows = case.num_pages * case.rpp
+    for inp, d in per_layer:
+        pool = inp["pool"].copy()
+        if flags & capi.PKV_DO_ROWS:
+            orc.store_rows_chunks(inp["rows"], pool, case.tables, case.rpp, case.row_stride, case.chunks)
+        assert np.array_equal(tl.host(d["pool"], np.uint16, pool.shape), pool), "row pool"
+        if flags & capi.PKV_DO_KEYS_FP4:
+            fp4 = np.full(case.num_pages * case.rpp * 68, 0x5A, np.uint8)
+            orc.store_rows_fp4_chunks(inp["keys"], fp4, case.tables, case.rpp, case.chunks)
+            assert np.array_equal(tl.host(d["fp4"], np.uint8), fp4), "fp4 key pool"
+        if flags & capi.PKV_DO_KEYS_FP8:
+            codes = np.full((nrows, 128), 0x5A, np.uint8)
+            scales = np.full((nrows, 128 // fp8_block), 0x5A, np.uint8)
+            orc.store_rows_fp8_chunks(inp["keys"], fp8_block, codes, scales, case.tables, case.rpp, case.chunks)
+            assert np.array_equal(tl.host(d["codes"], np.uint8, codes.shape), codes), "fp8 codes"
+            assert np.array_equal(tl.host(d["scales"], np.uint8, scales.shape), scales), "fp8 scales"
+        if flags & capi.PKV_DO_GATHER:
+            want = orc.gather_rows(pool, case.tables, case.rpp, case.row_stride, case.width, inp["idx"], case.q_slot,
+                                   case.q_visible)
+            got = tl.host(d["out"], np.uint16, want.shape)
+            assert np.array_equal(got, want), "gathered rows"
+
+
+ALL = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_KEYS_FP8 | capi.PKV_DO_GATHER
+
+
+@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+def test_step_config1(pkv, cuda, variant):
+    """Benchmark configuration 1: 8 sequences of 1024..8192 rows over a 1024-page pool, one appended row each, then a
+    2048-entry gather per sequence (-1 padded), all in one launch; every byte against the oracle."""
+    case = tl.PagedCase(seed=1)
+    check_step(case, run_step(pkv, cuda, case, 1, ALL | variant), ALL)
+
+
+@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+def test_step_layers_and_prefill_chunks(pkv, cuda, variant):
+    """Several layers in one launch, chunks of different lengths (decode rows and prefill chunks that cross pages),
+    a row stride wider than the row, index lists that include the rows being appended."""
+    case = tl.PagedCase(seed=2, nseq=5, len_lo=300, len_hi=900, num_pages=96, k=160, row_stride=640, append=1)
+    g = tl.rng(22)
+    ns = [1, 37, 128, 211, 1]  # the chunk sizes of tools/batch_test/main.hip:124-192
+    t0 = np.concatenate([[0], np.cumsum(ns)[:-1]])
+    case.chunks = np.array([[s, int(case.lens[s]) - ns[s] + 1, ns[s], int(t0[s])] for s in range(5)], np.int32)
+    case.T = int(sum(ns))
+    case.rows, case.keys = tl.normal_bf16(g, (case.T, case.width)), tl.key_rows(g, case.T)
+    for fp8_block in (32, 128):
+        check_step(case, run_step(pkv, cuda, case, 3, ALL | variant, fp8_block), ALL, fp8_block)
+
+
+@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+def test_gather_only_and_append_only(pkv, cuda, variant):
+    case = tl.PagedCase(seed=3, nseq=4, len_lo=64, len_hi=700, num_pages=64, k=96)
+    check_step(case, run_step(pkv, cuda, case, 2, capi.PKV_DO_GATHER | variant), capi.PKV_DO_GATHER)
+    check_step(case, run_step(pkv, cuda, case, 2, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | variant),
+               capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4)
+
+
+@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+def test_gather_ragged_k(pkv, cuda, variant):
+    """k that is not a multiple of the tile, fully masked queries, a query with nothing visible."""
+    case = tl.PagedCase(seed=4, nseq=3, len_lo=10, len_hi=90, num_pages=16, k=77)
+    case.q_visible[1] = 0
+    case.idx[2, :] = -1
+    check_step(case, run_step(pkv, cuda, case, 1, capi.PKV_DO_GATHER | variant), capi.PKV_DO_GATHER)
+
+
+def test_bad_page_id_is_reported_not_dereferenced(pkv, cuda):
+    """A block-table entry outside the pool is skipped and recorded in the status word; the launch completes."""
+    case = tl.PagedCase(seed=5, nseq=2, len_lo=64, len_hi=128, num_pages=8, k=32)
+    case.tables[1, 0] = 1 << 20
+    d_tables, d_chunks = tl.dev(cuda, case.tables), tl.dev(cuda, case.chunks)
+    d_qchunk, d_qvis = tl.dev(cuda, case.q_chunk), tl.dev(cuda, case.q_visible)
+    step = tl.make_step(case, d_tables, d_chunks, d_qchunk, d_qvis)
+    layers = tl.make_layers(1)
+    d_pool, d_idx = tl.dev(cuda, case.pool), tl.dev(cuda, case.idx)
+    d_out = cuda.zeros(2 * 32 * 576 * 2, dtype=cuda.uint8, device="cuda")
+    layers[0].row_pool, layers[0].idx, layers[0].gathered = d_pool.data_ptr(), d_idx.data_ptr(), d_out.data_ptr()
+    capi.check(pkv.pkv_step_run(C.byref(step), layers, 1, capi.PKV_DO_GATHER, tl.stream_ptr(cuda)))
+    status = tl.device_status(pkv)
+    assert status & 0xFF == 1
+    assert tl.device_status(pkv) == 0  # reading clears it
+
+
+def test_copy_pages(pkv, cuda):
+    g = tl.rng(18)
+    pages, n = 64, 20
+    pools = [g.integers(0, 65536, size=(pages, tl.PAGE_BYTES // 2), dtype=np.uint16),
+             g.integers(0, 256, size=(pages, tl.FP4_PAGE_BYTES), dtype=np.uint8)]
+    perm = g.permutation(pages).astype(np.int32)
+    src, dst = perm[:n].copy(), perm[n:2 * n].copy()
+    want = [p.copy() for p in pools]
+    orc.copy_pages(want[0], tl.PAGE_BYTES, src, dst)
+    orc.copy_pages(want[1], tl.FP4_PAGE_BYTES, src, dst)
+    d_pools = [tl.dev(cuda, p) for p in pools]
+    descs = (capi.PkvPoolDesc * 2)()
+    for i, (d, pb) in enumerate(zip(d_pools, (tl.PAGE_BYTES, tl.FP4_PAGE_BYTES))):
+        descs[i].src_base = descs[i].dst_base = d.data_ptr()
+        descs[i].page_bytes = pb
+    d_src, d_dst = tl.dev(cuda, src), tl.dev(cuda, dst)
+    capi.check(pkv.pkv_copy_pages(descs, 2, d_src.data_ptr(), d_dst.data_ptr(), n, pages, pages, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_pools[0], np.uint16, want[0].shape), want[0])
+    assert np.array_equal(tl.host(d_pools[1], np.uint8, want[1].shape), want[1])
+    assert tl.device_status(pkv) == 0
+
+
+def test_repeat_is_stable(pkv, cuda):
+    """The reference's REPEAT=n race check (tools/kernel_test/indexer.hip:122-140): the same launch, poisoned outputs,
+    identical bytes every time."""
+    case = tl.PagedCase(seed=6, nseq=4, len_lo=500, len_hi=3000, num_pages=256, k=512)
+    first = None
+    for variant in (0, capi.PKV_VARIANT_BULK):
+        for _ in range(3):
+            per_layer = run_step(pkv, cuda, case, 2, ALL | variant)
+            sig = [tl.host(d[k], np.uint8).tobytes() for _, d in per_layer for k in ("pool", "fp4", "codes", "scales", "out")]
+            if first is None:
+                first = sig
+            assert sig == first

@@ -1,0 +1,118 @@
+"""ctypes binding of include/unholy_pkv.h. One declaration per exported function; no logic."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "lib" / "libunholy_pkv.so"
+
+PKV_OK, PKV_ERR_ARG, PKV_ERR_CUDA, PKV_ERR_DEVICE, PKV_ERR_LIMIT = range(5)
+PKV_MAX_LAYERS = 48
+PKV_DO_ROWS, PKV_DO_KEYS_FP4, PKV_DO_KEYS_FP8, PKV_DO_GATHER, PKV_VARIANT_BULK = 1, 2, 4, 8, 256
+
+c_i32p = C.POINTER(C.c_int32)
+c_u8p = C.POINTER(C.c_uint8)
+
+
+class PkvError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"pkv error {code}: {msg}")
+        self.code = code
+
+
+class PkvChunk(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("s0", C.c_int32), ("n", C.c_int32), ("t0", C.c_int32)]
+
+
+class PkvLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in
+                ("rows", "row_pool", "keys", "key_pool_fp4", "key_fp8_codes", "key_fp8_scales", "idx", "gathered")]
+
+
+class PkvStep(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("width", "row_stride", "rows_per_page", "max_pages_per_seq", "num_pages", "fp8_block", "nchunks", "T",
+                 "Q", "k")] + [(n, C.c_void_p) for n in ("tables", "chunks", "q_chunk", "q_visible")]
+
+
+class PkvPoolDesc(C.Structure):
+    _fields_ = [("src_base", C.c_void_p), ("dst_base", C.c_void_p), ("page_bytes", C.c_uint64)]
+
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+_SIGS = {
+    "pkv_last_error": (C.c_char_p, []),
+    "pkv_abi_version": (_i, []),
+    "pkv_device_status": (_i, [C.POINTER(C.c_int)]),
+    "pkv_store_rows": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "pkv_store_rows_fp4": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),
+    "pkv_load_rows_fp4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),
+    "pkv_act_quant_fp8": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "pkv_fake_quant_fp8": (_i, [_vp, _i, _i, _i, _i, _vp]),
+    "pkv_fake_quant_fp4": (_i, [_vp, _i, _i, _i, _i, _vp]),
+    "pkv_store_rows_fp8": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "pkv_copy": (_i, [_vp, _vp, _sz, _vp]),
+    "pkv_gather_rows": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp]),
+    "pkv_step_run": (_i, [C.POINTER(PkvStep), C.POINTER(PkvLayer), _i, _i, _vp]),
+    "pkv_copy_pages": (_i, [C.POINTER(PkvPoolDesc), _i, _vp, _vp, _i, _i, _i, _vp]),
+    "pkv_device_alloc": (_i, [C.POINTER(_vp), _sz]),
+    "pkv_device_free": (_i, [_vp]),
+    "pkv_ipc_export": (_i, [_vp, c_u8p]),
+    "pkv_ipc_open": (_i, [c_u8p, C.POINTER(_vp)]),
+    "pkv_ipc_close": (_i, [_vp]),
+    "pkv_pool_create": (_vp, [_i, _i, _i, _i, _i]),
+    "pkv_pool_destroy": (None, [_vp]),
+    "pkv_pool_seq_open": (_i, [_vp]),
+    "pkv_pool_seq_close": (_i, [_vp, _i]),
+    "pkv_pool_match_prefix": (_i, [_vp, _i, c_i32p, _i, c_u8p]),
+    "pkv_pool_assign_slot": (_i, [_vp, _i]),
+    "pkv_pool_alloc": (_i, [_vp, _i, _i]),
+    "pkv_pool_register": (_i, [_vp, _i, c_i32p, _i, _i]),
+    "pkv_pool_release": (_i, [_vp, _i]),
+    "pkv_pool_fork": (_i, [_vp, _i, _i]),
+    "pkv_pool_cow": (_i, [_vp, _i, _i, _i, c_i32p, c_i32p, _i]),
+    "pkv_pool_free_lru": (_i, [_vp, _i, c_i32p, _i]),
+    "pkv_pool_compact": (_i, [_vp, c_i32p, c_i32p, _i]),
+    "pkv_pool_migrate": (_i, [_vp, _i, _vp, C.POINTER(C.c_int), c_i32p, c_i32p, _i]),
+    "pkv_pool_available": (_i, [_vp]),
+    "pkv_pool_free_count": (_i, [_vp]),
+    "pkv_pool_evictable_count": (_i, [_vp]),
+    "pkv_pool_cached_count": (_i, [_vp]),
+    "pkv_pool_seq_pages": (_i, [_vp, _i, c_i32p, _i]),
+    "pkv_pool_seq_slot": (_i, [_vp, _i]),
+    "pkv_pool_page_refs": (_i, [_vp, _i]),
+    "pkv_pool_page_hash": (C.c_uint64, [_vp, _i]),
+    "pkv_pool_dirty": (_i, [_vp]),
+    "pkv_pool_tables": (c_i32p, [_vp]),
+    "pkv_pool_free_list": (_i, [_vp, c_i32p, _i]),
+    "pkv_pool_evictable_list": (_i, [_vp, c_i32p, _i]),
+    "pkv_page_hash": (C.c_uint64, [c_i32p, _i, _i]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    """The loaded library. Raises when it has not been built: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise FileNotFoundError(
+                f"{_LIB_PATH} is missing: build it with `python -m unholy_b200.build` (needs nvcc). "
+                "There is no CPU or Python fallback for this library.")
+        handle = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != PKV_OK:
+        raise PkvError(rc, lib().pkv_last_error().decode())

@@ -1,0 +1,973 @@
+// sm_100a kernels of the paged KV-cache path and their C ABI (declared in include/unholy_pkv.h).
+//
+// What the kernels replace in ewtodd/unholy: store_rows (src/kernels/ref_attn.hip:88-93), store_rows_fp4 /
+// load_rows_fp4 (src/kernels/indexer.hip:43-62), act_quant_fp8 / fake_quant_* (src/kernels/ref_elem.hip:18-59),
+// glm_store_latent (src/kernels/glm_fast.hip:37-51), copy_kernel (src/kernels/ref_elem.hip:269-278) and the gather
+// loop the attention kernels carry (src/kernels/attn_wmma.hip:75-113). The path is pure data movement plus
+// elementwise quantisation, so it is bound by HBM bandwidth: no tensor cores are used. Design rules:
+//   * every global access is a 16-byte vector, coalesced along a row (a 576-wide bf16 row is 72 vectors = 9 full
+//     128-byte lines when the pool base is 128-byte aligned);
+//   * one launch covers all chunks of a step and up to PKV_MAX_LAYERS layers (the reference launches once per
+//     chunk, layer and pool), with a grid sized from the SM count;
+//   * the gather has two implementations: vector loads with every load of a tile in flight before the first store,
+//     and a bulk-copy pipeline (cp.async.bulk global->shared->global with mbarrier completion) in which one warp
+//     keeps several 16-row tiles in flight and the contiguous output tile leaves as a single bulk store;
+//   * quantisation keeps 8 values per thread and reduces the block maximum with warp shuffles;
+//   * block-table entries are bounds-checked; a bad entry is skipped and recorded in a status word, never dereferenced;
+//     the only device-side wait (an mbarrier) is bounded and records when it gives up.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include "../../include/unholy_pkv.h"
+#include "pkv_numeric.cuh"
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const std::string& msg) {
+  g_err = msg;
+  return code;
+}
+int fail_cuda(const char* what, cudaError_t e) {
+  g_err = std::string(what) + ": " + cudaGetErrorString(e);
+  return PKV_ERR_CUDA;
+}
+#define PKV_LAUNCH_CHECK(name)                                   \
+  do {                                                           \
+    const cudaError_t e_ = cudaGetLastError();                   \
+    if (e_ != cudaSuccess) return fail_cuda(name " launch", e_); \
+  } while (0)
+
+// First failed device-side check (0 = none). Kind in the low byte, an entry index above it.
+__device__ int g_status = 0;
+__device__ __forceinline__ void report(int kind, int index) { atomicCAS(&g_status, 0, kind | (index << 8)); }
+
+struct DeviceInfo {
+  int sms = 0;
+  bool ok = false;
+};
+const DeviceInfo& device_info() {
+  thread_local DeviceInfo info[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    static DeviceInfo none;
+    return none;
+  }
+  if (!info[dev].ok) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+      info[dev].sms = sms;
+      info[dev].ok = true;
+    }
+  }
+  return info[dev];
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Tuning knobs (environment, read once): grid multipliers and the bulk pipeline's shape.
+// ---------------------------------------------------------------------------------------------------------------------
+int env_int(const char* name, int dflt) {
+  const char* v = std::getenv(name);
+  return v && *v ? std::atoi(v) : dflt;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Streaming 16-byte accesses: the pool rows and the gathered output are touched once per launch, so they bypass L1 and
+// are marked evict-first in L2.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, const uint4& v) { __stcs(p, v); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Generic quantisers: one thread per 8 consecutive values of a row. rows x cols values; cols % block == 0,
+// block in {32, 64, 128}. Row r's input starts at x + r * ldx.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 load8(const uint16_t* p, bool vec) {
+  if (vec) return *reinterpret_cast<const uint4*>(p);
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w[i] = uint32_t(p[2 * i]) | (uint32_t(p[2 * i + 1]) << 16);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void store8_bf16(uint16_t* p, const float* v, bool vec) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = uint32_t(pkv::f32_to_bf16_bits(v[2 * i])) | (uint32_t(pkv::f32_to_bf16_bits(v[2 * i + 1])) << 16);
+  if (vec) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[2 * i] = uint16_t(w[i]);
+      p[2 * i + 1] = uint16_t(w[i] >> 16);
+    }
+  }
+}
+
+enum QuantMode { kFp8Codes = 0, kFp8Fake = 1, kFp4Fake = 2 };
+
+// fp8 codes + scales into dense arrays q [rows][cols], s [rows][cols/block]; or fake quantisation in place.
+template <int MODE>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restrict__ x, int ldx, uint8_t* __restrict__ q,
+                                                         uint8_t* __restrict__ s, int rows, int cols, int block,
+                                                         bool vec) {
+  const int per_row = cols >> 3, group = block >> 3;
+  const long long total = (long long)rows * per_row;
+  const long long span = ((total + 31) / 32) * 32;  // whole warps stay in the loop: the shuffles need every lane
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < span; u += (long long)gridDim.x * blockDim.x) {
+    const bool live = u < total;
+    const int r = live ? int(u / per_row) : 0, j = live ? int(u % per_row) : 0;
+    uint16_t* xr = const_cast<uint16_t*>(x) + size_t(r) * ldx + size_t(j) * 8;
+    float v[8];
+    if (live) pkv::unpack8(load8(xr, vec), v);
+    else
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    const float amax = pkv::group_max(pkv::absmax8(v), group);
+    if (MODE == kFp4Fake) {
+      const float sc = pkv::e8m0_bits_to_f32(pkv::fp4_scale_exp(amax));
+      if (live) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          o[i] = pkv::e2m1_bits_to_f32(pkv::e2m1_nibble(fminf(fmaxf(v[i] / sc, -6.0f), 6.0f))) * sc;
+        store8_bf16(xr, o, vec);
+      }
+    } else {
+      const uint32_t se = pkv::fp8_scale_exp(amax);
+      const float sc = pkv::e8m0_bits_to_f32(se);
+      if (!live) continue;
+      const uint2 codes = pkv::fp8_pack8(v, sc);
+      if (MODE == kFp8Fake) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          o[i] = pkv::e4m3_bits_to_f32(((i < 4 ? codes.x : codes.y) >> (8 * (i & 3))) & 0xffu) * sc;
+        store8_bf16(xr, o, vec);
+      } else {
+        uint8_t* qp = q + size_t(r) * cols + size_t(j) * 8;
+        if ((reinterpret_cast<uintptr_t>(qp) & 7u) == 0) {
+          *reinterpret_cast<uint2*>(qp) = codes;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) qp[i] = uint8_t((i < 4 ? codes.x : codes.y) >> (8 * (i & 3)));
+        }
+        if (j % group == 0) s[size_t(r) * (cols / block) + j / group] = uint8_t(se);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Step kernels. Parameters travel by value (one struct < 4 KB).
+// ---------------------------------------------------------------------------------------------------------------------
+struct StepParams {
+  pkv_step s;
+  int L;
+  int flags;
+  int append_tiles;  // per layer
+  int gather_tiles;  // per layer
+  int tiles_per_q;
+  pkv_layer layers[PKV_MAX_LAYERS];
+};
+
+// The chunk holding batch row t (chunks ordered by t0, disjoint); -1 if none.
+__device__ __forceinline__ int find_chunk(const pkv_chunk* __restrict__ chunks, int n, int t) {
+  int lo = 0, hi = n;  // last chunk with t0 <= t
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(&chunks[mid].t0) <= t) lo = mid;
+    else hi = mid;
+  }
+  if (n == 0) return -1;
+  const int t0 = __ldg(&chunks[lo].t0), cn = __ldg(&chunks[lo].n);
+  return (t >= t0 && t < t0 + cn) ? lo : -1;
+}
+
+// Physical row id of logical row `lr` of `slot`, or -1 (recorded) when the table entry is unusable.
+__device__ __forceinline__ long long physical_row(const pkv_step& s, int slot, int lr, int tag) {
+  const int pg = lr / s.rows_per_page;
+  if (lr < 0 || pg >= s.max_pages_per_seq) {
+    report(2, tag);
+    return -1;
+  }
+  const int page = __ldg(&s.tables[size_t(slot) * s.max_pages_per_seq + pg]);
+  if (page < 0 || (s.num_pages > 0 && page >= s.num_pages)) {
+    report(1, tag);
+    return -1;
+  }
+  return (long long)page * s.rows_per_page + (lr - pg * s.rows_per_page);
+}
+
+constexpr int kVecThreads = 384;            // 12 warps
+constexpr int kAppendRows = kVecThreads / 16;  // batch rows per append tile: 16 threads quantise one 128-wide key row
+constexpr int kGatherRows = 32;             // index entries per gather tile
+constexpr int kGatherUnroll = 6;            // 32 rows x 72 vectors = 384 threads x 6
+
+// One append tile: batch rows [t_first, t_first + kAppendRows) of one layer. Copies the bf16 rows into the pool and
+// quantises the keys (MXFP4 and/or fp8) to the same physical rows.
+__device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_first, long long* s_rid) {
+  const pkv_step& s = P.s;
+  const int tid = threadIdx.x;
+  const int nrows = min(kAppendRows, s.T - t_first);
+  if (tid < kAppendRows) {
+    long long rid = -1;
+    if (tid < nrows) {
+      const int t = t_first + tid;
+      const int c = find_chunk(s.chunks, s.nchunks, t);
+      if (c >= 0) {
+        const pkv_chunk ch = s.chunks[c];
+        rid = physical_row(s, ch.slot, ch.s0 + (t - ch.t0), t);
+      }
+    }
+    s_rid[tid] = rid;
+  }
+  __syncthreads();
+  if ((P.flags & PKV_DO_ROWS) && ly.rows && ly.row_pool) {
+    const int vpr = s.width >> 3;
+    const int total = nrows * vpr;
+    const uint4* src = reinterpret_cast<const uint4*>(ly.rows + size_t(t_first) * s.width);
+    for (int u = tid; u < total; u += kVecThreads) {
+      const int r = u / vpr, c = u - r * vpr;
+      const long long rid = s_rid[r];
+      if (rid >= 0) st_stream(reinterpret_cast<uint4*>(ly.row_pool + size_t(rid) * s.row_stride) + c, ld_stream(src + u));
+    }
+  }
+  const bool fp4 = (P.flags & PKV_DO_KEYS_FP4) && ly.keys && ly.key_pool_fp4;
+  const bool fp8 = (P.flags & PKV_DO_KEYS_FP8) && ly.keys && ly.key_fp8_codes && ly.key_fp8_scales;
+  if (fp4 || fp8) {
+    // 16 threads per key row, 8 values each; every lane runs the shuffles.
+    const int r = tid >> 4, j = tid & 15;
+    const long long rid = r < nrows ? s_rid[r] : -1;
+    float v[8];
+    if (rid >= 0) {
+      pkv::unpack8(*reinterpret_cast<const uint4*>(ly.keys + size_t(t_first + r) * PKV_FP4_ROW_DIM + j * 8), v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    const float a8 = pkv::absmax8(v);
+    if (fp4) {
+      const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
+      const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
+      // The four block scales of the row meet in the row's first lane.
+      const int base = (tid & 31) & 16;
+      const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
+                     s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
+      if (rid >= 0) {
+        const long long page = rid / s.rows_per_page;
+        const int slot = int(rid - page * s.rows_per_page);
+        uint8_t* pg = ly.key_pool_fp4 + size_t(page) * size_t(s.rows_per_page) * 68u;
+        *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
+        if (j == 0)
+          *reinterpret_cast<uint32_t*>(pg + size_t(s.rows_per_page) * 64u + size_t(slot) * 4u) =
+              s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+      }
+    }
+    if (fp8) {
+      const int group = s.fp8_block >> 3;
+      const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(a8, group));
+      const uint2 codes = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
+      if (rid >= 0) {
+        *reinterpret_cast<uint2*>(ly.key_fp8_codes + size_t(rid) * PKV_FP4_ROW_DIM + j * 8) = codes;
+        if (j % group == 0) ly.key_fp8_scales[size_t(rid) * (PKV_FP4_ROW_DIM / s.fp8_block) + j / group] = uint8_t(se);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// Source row of entry `e` of query `q`: the pool row, the row being appended in this launch when the entry falls in
+// the query's own chunk and rows are appended by the same launch, or nullptr when masked.
+__device__ __forceinline__ const uint4* gather_source(const StepParams& P, const pkv_layer& ly, int q, int e) {
+  const pkv_step& s = P.s;
+  if (e >= s.k) return nullptr;
+  const int row = __ldg(&ly.idx[size_t(q) * s.k + e]);
+  if (row < 0 || row >= __ldg(&s.q_visible[q])) return nullptr;
+  const pkv_chunk ch = s.chunks[__ldg(&s.q_chunk[q])];
+  if ((P.flags & PKV_DO_ROWS) && ly.rows && row >= ch.s0 && row < ch.s0 + ch.n)
+    return reinterpret_cast<const uint4*>(ly.rows + size_t(ch.t0 + (row - ch.s0)) * s.width);
+  const long long rid = physical_row(s, ch.slot, row, q);
+  if (rid < 0) return nullptr;
+  return reinterpret_cast<const uint4*>(ly.row_pool + size_t(rid) * s.row_stride);
+}
+
+// Copies one resolved tile (rows s_src[0..nrows), nullptr = zeros) to its contiguous place in the output. All of a
+// thread's loads are issued before its first store.
+__device__ __forceinline__ void copy_tile_vec(const uint4* const* s_src, uint4* out, int nrows, int vpr) {
+  const int tid = threadIdx.x;
+  const int total = nrows * vpr;
+  for (int base = 0; base < total; base += kVecThreads * kGatherUnroll) {
+    uint4 v[kGatherUnroll];
+#pragma unroll
+    for (int i = 0; i < kGatherUnroll; ++i) {
+      const int u = base + i * kVecThreads + tid;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (u < total) {
+        const int r = u / vpr, c = u - r * vpr;
+        const uint4* p = s_src[r];
+        if (p) v[i] = ld_stream(p + c);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kGatherUnroll; ++i) {
+      const int u = base + i * kVecThreads + tid;
+      if (u < total) st_stream(out + u, v[i]);
+    }
+  }
+}
+
+// One gather tile with vector loads: 32 entries of one query.
+__device__ void gather_tile_vec(const StepParams& P, const pkv_layer& ly, int tile, const uint4** s_src) {
+  const pkv_step& s = P.s;
+  const int q = tile / P.tiles_per_q, e0 = (tile - q * P.tiles_per_q) * kGatherRows;
+  if (threadIdx.x < kGatherRows) s_src[threadIdx.x] = gather_source(P, ly, q, e0 + int(threadIdx.x));
+  __syncthreads();
+  copy_tile_vec(s_src, reinterpret_cast<uint4*>(ly.gathered + (size_t(q) * s.k + e0) * s.width), min(kGatherRows, s.k - e0),
+                s.width >> 3);
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kVecThreads) step_vec_kernel(const __grid_constant__ StepParams P) {
+  __shared__ long long s_rid[kAppendRows];
+  __shared__ const uint4* s_src[kGatherRows];
+  const int per_layer = P.append_tiles + P.gather_tiles;
+  const long long total = (long long)per_layer * P.L;
+  for (long long w = blockIdx.x; w < total; w += gridDim.x) {
+    const int layer = int(w / per_layer), r = int(w - (long long)layer * per_layer);
+    const pkv_layer& ly = P.layers[layer];
+    if (r < P.append_tiles) append_tile(P, ly, r * kAppendRows, s_rid);
+    else gather_tile_vec(P, ly, r - P.append_tiles, s_src);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Bulk-copy gather pipeline. One warp per CTA. A tile is ROWS index entries of one query: each lane of the warp owns
+// entries and issues a cp.async.bulk (global -> shared) per row, all completing on the stage's mbarrier; the finished
+// tile is contiguous in the output and leaves with ONE cp.async.bulk (shared -> global). STAGES tiles rotate, so
+// (STAGES - 2) tiles of loads and up to 2 stores are in flight per warp at any time.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// A wait that cannot hang: gives up after ~2^22 polls (seconds), reports, and tells the caller to stop.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int tag) {
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 64) __nanosleep(64);
+  }
+  report(3, tag);
+  return false;
+}
+
+template <int STAGES, int ROWS>
+__global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__ StepParams P) {
+  static_assert(ROWS <= 32 && STAGES >= 3, "one lane per row; two stages drain while the others fill");
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[STAGES];
+  const pkv_step& s = P.s;
+  const int lane = threadIdx.x;
+  const uint32_t row_bytes = uint32_t(s.width) * 2u;
+  const uint32_t stage_bytes = row_bytes * ROWS;
+  const int tiles_per_q = (s.k + ROWS - 1) / ROWS;
+  const long long per_layer = (long long)s.Q * tiles_per_q;
+  const long long total = per_layer * P.L;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) mbar_init(smem_addr(&bars[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const long long first = blockIdx.x, stride = gridDim.x;
+  const long long mine = first < total ? (total - first + stride - 1) / stride : 0;
+
+  // Fills stage (j % STAGES) with tile j of this CTA: resolve each lane's row, zero masked rows, start the loads.
+  auto produce = [&](long long j) {
+    const long long w = first + j * stride;
+    const int layer = int(w / per_layer);
+    const long long r = w - (long long)layer * per_layer;
+    const int q = int(r / tiles_per_q), e0 = int(r - (long long)q * tiles_per_q) * ROWS;
+    const pkv_layer& ly = P.layers[layer];
+    const int st = int(j % STAGES);
+    unsigned char* stage = smem + size_t(st) * stage_bytes;
+    const uint32_t bar = smem_addr(&bars[st]);
+    const uint4* src = lane < ROWS ? gather_source(P, ly, q, e0 + lane) : nullptr;
+    const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
+    if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(valid)) * row_bytes);
+    // Masked rows (and rows past k, which are never stored) are zero-filled by the whole warp, one row at a time.
+    unsigned masked = ~valid & (ROWS == 32 ? 0xffffffffu : ((1u << ROWS) - 1u));
+    while (masked) {
+      const int r = __ffs(masked) - 1;
+      masked &= masked - 1;
+      uint4* z = reinterpret_cast<uint4*>(stage + size_t(r) * row_bytes);
+      for (uint32_t i = lane; i < row_bytes / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncwarp();
+    if (src) bulk_load(smem_addr(stage + size_t(lane) * row_bytes), src, row_bytes, bar);
+  };
+
+  const long long ahead = STAGES - 2;
+  for (long long j = 0; j < ahead && j < mine; ++j) produce(j);
+  bool alive = true;
+  long long j_fail = 0;
+  for (long long j = 0; j < mine; ++j) {
+    // Stage (j + ahead) % STAGES was stored by tile j - 2; its store must have finished reading shared memory.
+    if (j + ahead < mine) {
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+      produce(j + ahead);
+    }
+    const int st = int(j % STAGES);
+    const uint32_t parity = uint32_t(j / STAGES) & 1u;
+    alive = mbar_wait_bounded(smem_addr(&bars[st]), parity, int(blockIdx.x));
+    alive = __all_sync(0xffffffffu, alive);
+    if (!alive) {
+      j_fail = j;
+      break;
+    }
+    const long long w = first + j * stride;
+    const int layer = int(w / per_layer);
+    const long long r = w - (long long)layer * per_layer;
+    const int q = int(r / tiles_per_q), e0 = int(r - (long long)q * tiles_per_q) * ROWS;
+    const int nrows = min(ROWS, s.k - e0);
+    fence_async_smem();  // the zero rows were written through the generic proxy
+    __syncwarp();
+    if (lane == 0) {
+      bulk_store(P.layers[layer].gathered + (size_t(q) * s.k + e0) * s.width, smem_addr(smem + size_t(st) * stage_bytes),
+                 uint32_t(nrows) * row_bytes);
+      bulk_commit();
+    }
+  }
+  if (!alive) {
+    // Gave up on tile j_fail: give the loads of the tiles already started a second, bounded chance to land before the
+    // CTA's shared memory is released.
+    for (long long jj = j_fail; jj < mine && jj <= j_fail + ahead; ++jj) {
+      const uint32_t bar = smem_addr(&bars[int(jj % STAGES)]), parity = uint32_t(jj / STAGES) & 1u;
+      for (int spin = 0; spin < (1 << 18); ++spin) {
+        if (mbar_try_wait(bar, parity)) break;
+        __nanosleep(256);
+      }
+    }
+  }
+  if (lane == 0) bulk_wait_all();
+  __syncwarp();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Reference-shaped single-sequence kernels.
+// ---------------------------------------------------------------------------------------------------------------------
+struct OneTable {
+  const int32_t* table;
+  int rows_per_page;
+};
+__device__ __forceinline__ size_t one_row(const OneTable& t, int r) {
+  const int pg = r / t.rows_per_page;
+  return size_t(__ldg(&t.table[pg])) * size_t(t.rows_per_page) + size_t(r - pg * t.rows_per_page);
+}
+
+// Rows of 16-byte vectors (width % 8 == 0, aligned): one thread per vector.
+__global__ void __launch_bounds__(256) store_rows_vec_kernel(const uint4* __restrict__ rows, long long total, int vpr,
+                                                             uint16_t* pool, OneTable tb, int row_stride, int row0) {
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+    const int r = int(u / vpr), c = int(u - (long long)r * vpr);
+    st_stream(reinterpret_cast<uint4*>(pool + one_row(tb, row0 + r) * size_t(row_stride)) + c, ld_stream(rows + u));
+  }
+}
+// Any width / alignment: one thread per element.
+__global__ void __launch_bounds__(256) store_rows_elem_kernel(const uint16_t* __restrict__ rows, long long total, int width,
+                                                              uint16_t* pool, OneTable tb, int row_stride, int row0) {
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+    const int r = int(u / width), c = int(u - (long long)r * width);
+    pool[one_row(tb, row0 + r) * size_t(row_stride) + c] = rows[u];
+  }
+}
+
+// MXFP4 append of 128-wide rows: 16 threads per row.
+__global__ void __launch_bounds__(256) store_rows_fp4_kernel(const uint16_t* __restrict__ rows, int n, uint8_t* pool,
+                                                             OneTable tb, int row0) {
+  const long long span = ((long long)n * 16 + 31) / 32 * 32;
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < span; u += (long long)gridDim.x * blockDim.x) {
+    const int r = int(u >> 4), j = int(u & 15);
+    const bool live = r < n;
+    float v[8];
+    if (live) pkv::unpack8(*reinterpret_cast<const uint4*>(rows + size_t(r) * PKV_FP4_ROW_DIM + j * 8), v);
+    else
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(pkv::absmax8(v), 4));
+    const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
+    const int base = (threadIdx.x & 31) & 16;
+    const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
+                   s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
+    if (!live) continue;
+    const int lr = row0 + r, pgi = lr / tb.rows_per_page, slot = lr - pgi * tb.rows_per_page;
+    uint8_t* pg = pool + size_t(__ldg(&tb.table[pgi])) * size_t(tb.rows_per_page) * 68u;
+    *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
+    if (j == 0)
+      *reinterpret_cast<uint32_t*>(pg + size_t(tb.rows_per_page) * 64u + size_t(slot) * 4u) =
+          s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+  }
+}
+
+// MXFP4 decode: one thread per 8 values (4 code bytes), 16-byte bf16 store.
+__global__ void __launch_bounds__(256) load_rows_fp4_kernel(const uint8_t* __restrict__ pool, OneTable tb, int row0, int n,
+                                                            uint16_t* __restrict__ out) {
+  const long long total = (long long)n * 16;
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < total; u += (long long)gridDim.x * blockDim.x) {
+    const int r = int(u >> 4), j = int(u & 15);
+    const int lr = row0 + r, pgi = lr / tb.rows_per_page, slot = lr - pgi * tb.rows_per_page;
+    const uint8_t* pg = pool + size_t(__ldg(&tb.table[pgi])) * size_t(tb.rows_per_page) * 68u;
+    const uint32_t codes = *reinterpret_cast<const uint32_t*>(pg + size_t(slot) * 64u + j * 4);
+    const float sc = pkv::e8m0_bits_to_f32(pg[size_t(tb.rows_per_page) * 64u + size_t(slot) * 4u + (j >> 2)]);
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = pkv::e2m1_bits_to_f32((codes >> (4 * i)) & 15u) * sc;
+    store8_bf16(out + size_t(r) * PKV_FP4_ROW_DIM + j * 8, o, true);
+  }
+}
+
+// fp8 append into the two-array layout: one thread per 8 values.
+__global__ void __launch_bounds__(256) store_rows_fp8_kernel(const uint16_t* __restrict__ rows, int n, int width, int block,
+                                                             uint8_t* codes, uint8_t* scales, OneTable tb, int s0) {
+  const int per_row = width >> 3, group = block >> 3, nb = width / block;
+  const long long total = (long long)n * per_row;
+  const long long span = (total + 31) / 32 * 32;
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < span; u += (long long)gridDim.x * blockDim.x) {
+    const bool live = u < total;
+    const int r = live ? int(u / per_row) : 0, j = live ? int(u - (long long)r * per_row) : 0;
+    float v[8];
+    if (live) pkv::unpack8(*reinterpret_cast<const uint4*>(rows + size_t(r) * width + j * 8), v);
+    else
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(pkv::absmax8(v), group));
+    if (!live) continue;
+    const uint2 c8 = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
+    const size_t rid = one_row(tb, s0 + r);
+    *reinterpret_cast<uint2*>(codes + rid * size_t(width) + j * 8) = c8;
+    if (j % group == 0) scales[rid * size_t(nb) + j / group] = uint8_t(se);
+  }
+}
+
+// The gather for one sequence (one block-table row), the shape of one reference attention call.
+__global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t* __restrict__ pool, OneTable tb, int max_pages,
+                                                                int num_rows_limit, int row_stride, int width,
+                                                                const int32_t* __restrict__ idx,
+                                                                const int32_t* __restrict__ q_visible, int T, int k,
+                                                                uint16_t* __restrict__ out) {
+  __shared__ const uint4* s_src[kGatherRows];
+  (void)max_pages, (void)num_rows_limit;
+  const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows;
+  const long long total = (long long)T * tiles_per_q;
+  for (long long w = blockIdx.x; w < total; w += gridDim.x) {
+    const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
+    if (threadIdx.x < kGatherRows) {
+      const int e = e0 + int(threadIdx.x);
+      const uint4* p = nullptr;
+      if (e < k) {
+        const int row = __ldg(&idx[size_t(t) * k + e]);
+        if (row >= 0 && row < __ldg(&q_visible[t]))
+          p = reinterpret_cast<const uint4*>(pool + one_row(tb, row) * size_t(row_stride));
+      }
+      s_src[threadIdx.x] = p;
+    }
+    __syncthreads();
+    copy_tile_vec(s_src, reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width), min(kGatherRows, k - e0), width >> 3);
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < n; i += 4 * stride) {
+    const uint4 a = ld_stream(src + i), b = ld_stream(src + i + stride), c = ld_stream(src + i + 2 * stride),
+                d = ld_stream(src + i + 3 * stride);
+    st_stream(dst + i, a);
+    st_stream(dst + i + stride, b);
+    st_stream(dst + i + 2 * stride, c);
+    st_stream(dst + i + 3 * stride, d);
+  }
+  for (; i < n; i += stride) st_stream(dst + i, ld_stream(src + i));
+}
+__global__ void __launch_bounds__(256) copy1_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) dst[i] = src[i];
+}
+
+// Page moves: work item = (pool, pair, 16 KB piece of the page).
+struct PageCopyParams {
+  int npools, n, num_src_pages, num_dst_pages;
+  const int32_t* src_ids;
+  const int32_t* dst_ids;
+  pkv_pool_desc pools[128];
+};
+constexpr int kPieceVecs = 1024;  // 16 KB
+__global__ void __launch_bounds__(256) copy_pages_kernel(const __grid_constant__ PageCopyParams P) {
+  long long pieces_total = 0;
+  // Pools may differ in page size: enumerate (pool, pair, piece) with per-pool piece counts.
+  for (int p = 0; p < P.npools; ++p)
+    pieces_total += (long long)P.n * ((P.pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
+  for (long long w = blockIdx.x; w < pieces_total; w += gridDim.x) {
+    long long rest = w;
+    int p = 0;
+    long long per_page = 0;
+    for (; p < P.npools; ++p) {
+      per_page = (long long)((P.pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
+      if (rest < per_page * P.n) break;
+      rest -= per_page * P.n;
+    }
+    const int pair = int(rest / per_page), piece = int(rest - (long long)pair * per_page);
+    const int sp = __ldg(&P.src_ids[pair]), dp = __ldg(&P.dst_ids[pair]);
+    if (sp < 0 || dp < 0 || (P.num_src_pages > 0 && sp >= P.num_src_pages) || (P.num_dst_pages > 0 && dp >= P.num_dst_pages)) {
+      if (threadIdx.x == 0) report(1, pair);
+      continue;
+    }
+    const size_t vecs = size_t(P.pools[p].page_bytes / 16);
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.pools[p].src_base) + size_t(sp) * P.pools[p].page_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(P.pools[p].dst_base) + size_t(dp) * P.pools[p].page_bytes);
+    const size_t lo = size_t(piece) * kPieceVecs, hi = min(vecs, lo + kPieceVecs);
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t u = lo + size_t(i) * 256 + threadIdx.x;
+      if (u < hi) v[i] = ld_stream(src + u);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t u = lo + size_t(i) * 256 + threadIdx.x;
+      if (u < hi) st_stream(dst + u, v[i]);
+    }
+  }
+}
+
+int grid_for(long long work_items, int threads, int per_sm) {
+  const DeviceInfo& d = device_info();
+  const long long cap = (long long)(d.ok ? d.sms : 148) * per_sm;
+  const long long want = (work_items + threads - 1) / threads;
+  return int(std::max<long long>(1, std::min(want, cap)));
+}
+
+int check_quant_shape(int rows, int cols, int block, const char* name) {
+  if (rows < 0 || cols < 0) return fail(PKV_ERR_ARG, std::string(name) + ": negative shape");
+  if (block != 32 && block != 64 && block != 128) return fail(PKV_ERR_ARG, std::string(name) + ": block must be 32, 64 or 128");
+  if (cols % block != 0) return fail(PKV_ERR_ARG, std::string(name) + ": cols must be a multiple of block");
+  return PKV_OK;
+}
+
+template <int STAGES, int ROWS>
+int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
+  const size_t smem = size_t(STAGES) * ROWS * size_t(P.s.width) * 2u;
+  if (smem > 227u * 1024u - 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
+  static thread_local bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(gather_bulk_kernel<STAGES, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    configured[dev] = true;
+  }
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  int per_sm = ctas_per_sm > 0 ? ctas_per_sm : int((227u * 1024u) / (smem + 1024u));
+  per_sm = std::max(1, std::min(per_sm, 32));
+  const long long tiles = (long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS);
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * per_sm)));
+  gather_bulk_kernel<STAGES, ROWS><<<grid, 32, smem, st>>>(P);
+  PKV_LAUNCH_CHECK("gather_bulk_kernel");
+  return PKV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* pkv_last_error(void) { return g_err.c_str(); }
+int pkv_abi_version(void) { return 1; }
+
+int pkv_device_status(int* status_out) {
+  if (!status_out) return fail(PKV_ERR_ARG, "pkv_device_status: null output");
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda("cudaDeviceSynchronize", e);
+  e = cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+  if (e != cudaSuccess) return fail_cuda("cudaMemcpyFromSymbol", e);
+  const int zero = 0;
+  e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return fail_cuda("cudaMemcpyToSymbol", e);
+  *status_out = v;
+  return PKV_OK;
+}
+
+int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* pool, const int32_t* table, int rows_per_page,
+                   int row_stride, int row0, pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (!rows || !pool || !table) return fail(PKV_ERR_ARG, "pkv_store_rows: null pointer");
+  if (width <= 0 || rows_per_page <= 0 || row_stride < width || row0 < 0) return fail(PKV_ERR_ARG, "pkv_store_rows: bad shape");
+  const OneTable tb{table, rows_per_page};
+  const bool vec = width % 8 == 0 && row_stride % 8 == 0 && aligned16(rows) && aligned16(pool);
+  if (vec) {
+    const long long total = (long long)n * (width / 8);
+    store_rows_vec_kernel<<<grid_for(total, 256, 16), 256, 0, stream>>>(reinterpret_cast<const uint4*>(rows), total, width / 8,
+                                                                        pool, tb, row_stride, row0);
+  } else {
+    const long long total = (long long)n * width;
+    store_rows_elem_kernel<<<grid_for(total, 256, 16), 256, 0, stream>>>(rows, total, width, pool, tb, row_stride, row0);
+  }
+  PKV_LAUNCH_CHECK("store_rows");
+  return PKV_OK;
+}
+
+int pkv_store_rows_fp4(const uint16_t* rows, int n, uint8_t* pool, const int32_t* table, int rows_per_page, int row0,
+                       pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (!rows || !pool || !table) return fail(PKV_ERR_ARG, "pkv_store_rows_fp4: null pointer");
+  if (rows_per_page <= 0 || row0 < 0) return fail(PKV_ERR_ARG, "pkv_store_rows_fp4: bad shape");
+  if (!aligned16(rows) || (reinterpret_cast<uintptr_t>(pool) & 3u)) return fail(PKV_ERR_ARG, "pkv_store_rows_fp4: rows must be 16-byte and pool 4-byte aligned");
+  store_rows_fp4_kernel<<<grid_for((long long)n * 16, 256, 16), 256, 0, stream>>>(rows, n, pool, OneTable{table, rows_per_page}, row0);
+  PKV_LAUNCH_CHECK("store_rows_fp4");
+  return PKV_OK;
+}
+
+int pkv_load_rows_fp4(const uint8_t* pool, const int32_t* table, int rows_per_page, int row0, int n, uint16_t* out,
+                      pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (!pool || !table || !out) return fail(PKV_ERR_ARG, "pkv_load_rows_fp4: null pointer");
+  if (rows_per_page <= 0 || row0 < 0) return fail(PKV_ERR_ARG, "pkv_load_rows_fp4: bad shape");
+  if (!aligned16(out) || (reinterpret_cast<uintptr_t>(pool) & 3u)) return fail(PKV_ERR_ARG, "pkv_load_rows_fp4: out must be 16-byte and pool 4-byte aligned");
+  load_rows_fp4_kernel<<<grid_for((long long)n * 16, 256, 16), 256, 0, stream>>>(pool, OneTable{table, rows_per_page}, row0, n, out);
+  PKV_LAUNCH_CHECK("load_rows_fp4");
+  return PKV_OK;
+}
+
+static int quant_launch(int mode, const uint16_t* x, int ldx, uint8_t* q, uint8_t* s, int rows, int cols, int block,
+                        pkv_stream_t stream, const char* name) {
+  if (const int rc = check_quant_shape(rows, cols, block, name)) return rc;
+  if (rows == 0 || cols == 0) return PKV_OK;
+  if (!x || ldx < cols) return fail(PKV_ERR_ARG, std::string(name) + ": bad input");
+  const bool vec = aligned16(x) && ldx % 8 == 0;
+  const long long total = (long long)rows * (cols / 8);
+  const int grid = grid_for(total, 256, 16);
+  if (mode == kFp8Codes) quant_rows_kernel<kFp8Codes><<<grid, 256, 0, stream>>>(x, ldx, q, s, rows, cols, block, vec);
+  else if (mode == kFp8Fake) quant_rows_kernel<kFp8Fake><<<grid, 256, 0, stream>>>(x, ldx, nullptr, nullptr, rows, cols, block, vec);
+  else quant_rows_kernel<kFp4Fake><<<grid, 256, 0, stream>>>(x, ldx, nullptr, nullptr, rows, cols, block, vec);
+  PKV_LAUNCH_CHECK("quant_rows_kernel");
+  return PKV_OK;
+}
+
+int pkv_act_quant_fp8(const uint16_t* x, int ldx, uint8_t* q, uint8_t* s, int rows, int cols, int block,
+                      pkv_stream_t stream) {
+  if (rows > 0 && cols > 0 && (!q || !s)) return fail(PKV_ERR_ARG, "pkv_act_quant_fp8: null output");
+  return quant_launch(kFp8Codes, x, ldx, q, s, rows, cols, block, stream, "pkv_act_quant_fp8");
+}
+int pkv_fake_quant_fp8(uint16_t* x, int ldx, int rows, int cols, int block, pkv_stream_t stream) {
+  return quant_launch(kFp8Fake, x, ldx, nullptr, nullptr, rows, cols, block, stream, "pkv_fake_quant_fp8");
+}
+int pkv_fake_quant_fp4(uint16_t* x, int ldx, int rows, int cols, int block, pkv_stream_t stream) {
+  return quant_launch(kFp4Fake, x, ldx, nullptr, nullptr, rows, cols, block, stream, "pkv_fake_quant_fp4");
+}
+
+int pkv_store_rows_fp8(const uint16_t* rows, int n, int width, int block, uint8_t* codes, uint8_t* scales,
+                       const int32_t* table, int rows_per_page, int s0, pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (const int rc = check_quant_shape(n, width, block, "pkv_store_rows_fp8")) return rc;
+  if (!rows || !codes || !scales || !table) return fail(PKV_ERR_ARG, "pkv_store_rows_fp8: null pointer");
+  if (rows_per_page <= 0 || s0 < 0) return fail(PKV_ERR_ARG, "pkv_store_rows_fp8: bad shape");
+  if (!aligned16(rows) || (reinterpret_cast<uintptr_t>(codes) & 7u)) return fail(PKV_ERR_ARG, "pkv_store_rows_fp8: rows must be 16-byte and codes 8-byte aligned");
+  store_rows_fp8_kernel<<<grid_for((long long)n * (width / 8), 256, 16), 256, 0, stream>>>(rows, n, width, block, codes, scales,
+                                                                                         OneTable{table, rows_per_page}, s0);
+  PKV_LAUNCH_CHECK("store_rows_fp8");
+  return PKV_OK;
+}
+
+int pkv_copy(void* dst, const void* src, size_t bytes, pkv_stream_t stream) {
+  if (bytes == 0) return PKV_OK;
+  if (!dst || !src) return fail(PKV_ERR_ARG, "pkv_copy: null pointer");
+  const bool v16 = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | bytes) & 15u) == 0;
+  if (v16) {
+    const size_t n = bytes / 16;
+    copy16_kernel<<<grid_for((long long)((n + 3) / 4), 256, 8), 256, 0, stream>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), n);
+  } else {
+    copy1_kernel<<<grid_for((long long)bytes, 256, 8), 256, 0, stream>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), bytes);
+  }
+  PKV_LAUNCH_CHECK("copy_kernel");
+  return PKV_OK;
+}
+
+int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags, pkv_stream_t stream) {
+  if (!step || !layers) return fail(PKV_ERR_ARG, "pkv_step_run: null argument");
+  if (L <= 0) return PKV_OK;
+  if (L > PKV_MAX_LAYERS) return fail(PKV_ERR_LIMIT, "pkv_step_run: more than PKV_MAX_LAYERS layers in one launch");
+  const pkv_step& s = *step;
+  if (s.width <= 0 || s.width % 8 != 0 || s.row_stride < s.width || s.row_stride % 8 != 0)
+    return fail(PKV_ERR_ARG, "pkv_step_run: width and row_stride must be positive multiples of 8 with row_stride >= width");
+  if (s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks < 0 || s.T < 0 || s.Q < 0 || s.k < 0)
+    return fail(PKV_ERR_ARG, "pkv_step_run: bad geometry");
+  const bool append = (flags & (PKV_DO_ROWS | PKV_DO_KEYS_FP4 | PKV_DO_KEYS_FP8)) != 0 && s.T > 0 && s.nchunks > 0;
+  const bool gather = (flags & PKV_DO_GATHER) != 0 && s.Q > 0 && s.k > 0;
+  if (!append && !gather) return PKV_OK;
+  if (!s.tables || !s.chunks) return fail(PKV_ERR_ARG, "pkv_step_run: tables and chunks are required");
+  if (gather && (!s.q_chunk || !s.q_visible)) return fail(PKV_ERR_ARG, "pkv_step_run: q_chunk and q_visible are required for a gather");
+  if ((flags & PKV_DO_KEYS_FP8) && s.fp8_block != 32 && s.fp8_block != 64 && s.fp8_block != 128)
+    return fail(PKV_ERR_ARG, "pkv_step_run: fp8_block must be 32, 64 or 128");
+  for (int l = 0; l < L; ++l) {
+    const pkv_layer& y = layers[l];
+    if (!aligned16(y.rows) || !aligned16(y.row_pool) || !aligned16(y.keys) || !aligned16(y.gathered) ||
+        (reinterpret_cast<uintptr_t>(y.key_pool_fp4) & 3u) || (reinterpret_cast<uintptr_t>(y.key_fp8_codes) & 7u))
+      return fail(PKV_ERR_ARG, "pkv_step_run: layer pointers must be 16-byte aligned (fp4 pool 4, fp8 codes 8)");
+    if (gather && (!y.idx || !y.gathered || !y.row_pool)) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks idx, gathered or row_pool");
+  }
+  static const int grid_mult = env_int("PKV_VEC_CTAS_PER_SM", 5);
+  static const int bulk_shape = env_int("PKV_BULK_SHAPE", 416);     // STAGES * 100 + ROWS
+  static const int bulk_ctas = env_int("PKV_BULK_CTAS_PER_SM", 0);  // 0: as many as shared memory allows
+
+  StepParams P;
+  std::memset(&P, 0, sizeof(P));
+  P.s = s;
+  P.L = L;
+  P.flags = flags;
+  std::memcpy(P.layers, layers, sizeof(pkv_layer) * size_t(L));
+  const bool bulk = gather && (flags & PKV_VARIANT_BULK);
+  P.append_tiles = append ? (s.T + kAppendRows - 1) / kAppendRows : 0;
+  P.tiles_per_q = (s.k + kGatherRows - 1) / kGatherRows;
+  P.gather_tiles = gather && !bulk ? s.Q * P.tiles_per_q : 0;
+  const long long vec_work = (long long)(P.append_tiles + P.gather_tiles) * L;
+  if (vec_work > 0) {
+    const DeviceInfo& d = device_info();
+    const int sms = d.ok ? d.sms : 148;
+    const int grid = int(std::max<long long>(1, std::min<long long>(vec_work, (long long)sms * grid_mult)));
+    step_vec_kernel<<<grid, kVecThreads, 0, stream>>>(P);
+    PKV_LAUNCH_CHECK("step_vec_kernel");
+  }
+  if (bulk) {
+    switch (bulk_shape) {
+      case 316: return launch_bulk<3, 16>(P, bulk_ctas, stream);
+      case 416: return launch_bulk<4, 16>(P, bulk_ctas, stream);
+      case 616: return launch_bulk<6, 16>(P, bulk_ctas, stream);
+      case 332: return launch_bulk<3, 32>(P, bulk_ctas, stream);
+      case 432: return launch_bulk<4, 32>(P, bulk_ctas, stream);
+      case 632: return launch_bulk<6, 32>(P, bulk_ctas, stream);
+      case 408: return launch_bulk<4, 8>(P, bulk_ctas, stream);
+      case 808: return launch_bulk<8, 8>(P, bulk_ctas, stream);
+      default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape");
+    }
+  }
+  return PKV_OK;
+}
+
+int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows_per_page, int row_stride, int width,
+                    const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out, pkv_stream_t stream) {
+  if (T <= 0 || k <= 0) return PKV_OK;
+  if (!pool || !table || !idx || !q_visible || !out) return fail(PKV_ERR_ARG, "pkv_gather_rows: null pointer");
+  if (width <= 0 || width % 8 != 0 || row_stride < width || row_stride % 8 != 0 || rows_per_page <= 0)
+    return fail(PKV_ERR_ARG, "pkv_gather_rows: width and row_stride must be positive multiples of 8 with row_stride >= width");
+  if (!aligned16(pool) || !aligned16(out)) return fail(PKV_ERR_ARG, "pkv_gather_rows: pool and out must be 16-byte aligned");
+  const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 5)));
+  gather_one_kernel<<<grid, kVecThreads, 0, stream>>>(pool, OneTable{table, rows_per_page}, 0, 0, row_stride, width, idx,
+                                                      q_visible, T, k, out);
+  PKV_LAUNCH_CHECK("gather_one_kernel");
+  return PKV_OK;
+}
+
+int pkv_copy_pages(const pkv_pool_desc* pools, int npools, const int32_t* src_ids, const int32_t* dst_ids, int n,
+                   int num_src_pages, int num_dst_pages, pkv_stream_t stream) {
+  if (n <= 0 || npools <= 0) return PKV_OK;
+  if (!pools || !src_ids || !dst_ids) return fail(PKV_ERR_ARG, "pkv_copy_pages: null pointer");
+  if (npools > 128) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: more than 128 pools in one call");
+  PageCopyParams P;
+  std::memset(&P, 0, sizeof(P));
+  P.npools = npools;
+  P.n = n;
+  P.num_src_pages = num_src_pages;
+  P.num_dst_pages = num_dst_pages;
+  P.src_ids = src_ids;
+  P.dst_ids = dst_ids;
+  long long pieces = 0;
+  for (int p = 0; p < npools; ++p) {
+    if (!pools[p].src_base || !pools[p].dst_base || pools[p].page_bytes == 0 || pools[p].page_bytes % 16 != 0 ||
+        !aligned16(pools[p].src_base) || !aligned16(pools[p].dst_base))
+      return fail(PKV_ERR_ARG, "pkv_copy_pages: pool bases must be 16-byte aligned and page_bytes a multiple of 16");
+    P.pools[p] = pools[p];
+    pieces += (long long)n * (long long)((pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
+  }
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  const int grid = int(std::max<long long>(1, std::min<long long>(pieces, (long long)sms * 8)));
+  copy_pages_kernel<<<grid, 256, 0, stream>>>(P);
+  PKV_LAUNCH_CHECK("copy_pages_kernel");
+  return PKV_OK;
+}
+
+int pkv_device_alloc(void** ptr_out, size_t bytes) {
+  if (!ptr_out) return fail(PKV_ERR_ARG, "pkv_device_alloc: null output");
+  const cudaError_t e = cudaMalloc(ptr_out, bytes);
+  return e == cudaSuccess ? PKV_OK : fail_cuda("cudaMalloc", e);
+}
+int pkv_device_free(void* ptr) {
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? PKV_OK : fail_cuda("cudaFree", e);
+}
+int pkv_ipc_export(void* base, unsigned char handle_out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  if (!base || !handle_out) return fail(PKV_ERR_ARG, "pkv_ipc_export: null argument");
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, base);
+  if (e != cudaSuccess) return fail_cuda("cudaIpcGetMemHandle", e);
+  std::memcpy(handle_out, &h, 64);
+  return PKV_OK;
+}
+int pkv_ipc_open(const unsigned char handle[64], void** ptr_out) {
+  if (!handle || !ptr_out) return fail(PKV_ERR_ARG, "pkv_ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? PKV_OK : fail_cuda("cudaIpcOpenMemHandle", e);
+}
+int pkv_ipc_close(void* ptr) {
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? PKV_OK : fail_cuda("cudaIpcCloseMemHandle", e);
+}
+
+}  // extern "C"
