@@ -1,0 +1,147 @@
+// Drives the reference's own, unmodified engine (src/engine/engine.cpp + sampler.cpp, compiled where they lie under
+// the reference checkout by oracle/build_oracle.py) through a recording StepModel, and exposes what crosses the
+// scheduler<->model boundary (src/engine/step.hpp:76-106) behind a C interface: every set_block_tables() call, every
+// submitted chunk and state save, every finished request, and the allocator counters after each iterate(). The
+// page-pool tests replay that trace into the from-scratch allocator and compare block tables entry for entry.
+// TEST INFRASTRUCTURE ONLY; output goes to oracle/_ref/.
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "engine/engine.hpp"
+
+using namespace unholy::engine;
+
+namespace {
+
+uint64_t mix(uint64_t x) {
+  x ^= x >> 33;
+  x *= 0xff51afd7ed558ccdull;
+  x ^= x >> 33;
+  return x;
+}
+
+constexpr int kVocab = 512;
+
+// Event log: flat int64 records, first word = kind.
+//   1 nchunks {seq slot s0 n}* nsaves {slot}*     a submitted step
+//   2 table_index                                  set_block_tables (the table itself in tables[table_index])
+//   3 seq                                          request finished (its pages were released)
+//   4 running waiting free_pages cached_pages preemptions    after one iterate()
+struct Trace {
+  std::vector<int64_t> ev;
+  std::vector<std::vector<int32_t>> tables;
+};
+
+class RecordingModel final : public StepModel {
+ public:
+  RecordingModel(int pages, int page_tokens, int slots, int pps, int max_tokens, int snapshots, Trace& tr)
+      : pages_(pages), page_(page_tokens), slots_(slots), pps_(pps), max_tokens_(max_tokens), snaps_(snapshots), tr_(tr) {}
+  int vocab() const override { return kVocab; }
+  int max_tokens() const override { return max_tokens_; }
+  int max_logit_rows() const override { return 256; }
+  int max_slots() const override { return slots_; }
+  int max_pages_per_seq() const override { return pps_; }
+  int num_pages() const override { return pages_; }
+  int page_tokens() const override { return page_; }
+  int num_snapshots() const override { return snaps_; }
+  void set_block_tables(const std::vector<int32_t>& t) override {
+    tr_.ev.push_back(2);
+    tr_.ev.push_back(int64_t(tr_.tables.size()));
+    tr_.tables.push_back(t);
+  }
+  uint64_t submit(const StepInput& in) override {
+    tr_.ev.push_back(1);
+    tr_.ev.push_back(int64_t(in.chunks.size()));
+    for (const Chunk& c : in.chunks) {
+      tr_.ev.push_back(int64_t(c.seq));
+      tr_.ev.push_back(c.slot);
+      tr_.ev.push_back(c.s0);
+      tr_.ev.push_back(c.n);
+    }
+    tr_.ev.push_back(int64_t(in.save.size()));
+    for (const StateOp& s : in.save) tr_.ev.push_back(s.slot);
+    // Logits: one-hot on a token that depends only on (request, position), never EOS (id 1).
+    logits_.assign(in.logit_rows.size() * size_t(kVocab), 0.0f);
+    for (size_t r = 0; r < in.logit_rows.size(); ++r) {
+      const int row = in.logit_rows[r];
+      uint64_t seq = 0;
+      for (const Chunk& c : in.chunks)
+        if (row >= c.t0 && row < c.t0 + c.n) seq = c.seq;
+      const int tok = 2 + int(mix(seq * 1000003ull + uint64_t(in.pos[size_t(row)])) % uint64_t(kVocab - 2));
+      logits_[r * size_t(kVocab) + size_t(tok)] = 1.0f;
+    }
+    return ++ticket_;
+  }
+  void wait(uint64_t, std::vector<float>& logits) override { logits = logits_; }
+
+ private:
+  int pages_, page_, slots_, pps_, max_tokens_, snaps_;
+  Trace& tr_;
+  std::vector<float> logits_;
+  uint64_t ticket_ = 0;
+};
+
+struct Driver {
+  Trace tr;
+  std::unique_ptr<RecordingModel> model;
+  std::unique_ptr<Engine> engine;
+};
+
+}  // namespace
+
+extern "C" {
+
+void* refeng_create(int num_pages, int page_tokens, int max_slots, int max_pages_per_seq, int max_batch_tokens,
+                    int num_snapshots) {
+  auto* d = new Driver;
+  d->model = std::make_unique<RecordingModel>(num_pages, page_tokens, max_slots, max_pages_per_seq, max_batch_tokens,
+                                              num_snapshots, d->tr);
+  EngineConfig cfg;
+  cfg.max_batch_tokens = max_batch_tokens;
+  cfg.prefix_cache = true;
+  cfg.on_finish = [d](const RequestLog& l) {
+    d->tr.ev.push_back(3);
+    d->tr.ev.push_back(int64_t(l.id));
+  };
+  d->engine = std::make_unique<Engine>(*d->model, cfg, false);
+  return d;
+}
+
+void refeng_destroy(void* h) { delete static_cast<Driver*>(h); }
+
+uint64_t refeng_submit(void* h, const int32_t* prompt, int n, int max_tokens) {
+  auto* d = static_cast<Driver*>(h);
+  GenRequest r;
+  r.prompt.assign(prompt, prompt + n);
+  r.max_tokens = max_tokens;
+  r.ignore_eos = true;
+  r.sampling.temperature = 0.0f;
+  return d->engine->submit(std::move(r), [](GenOutput&&) {});
+}
+
+int refeng_iterate(void* h) {
+  auto* d = static_cast<Driver*>(h);
+  const bool did = d->engine->iterate();
+  const EngineStats s = d->engine->stats();
+  for (int64_t v : {int64_t(4), int64_t(s.running), int64_t(s.waiting), int64_t(s.free_pages), int64_t(s.cached_pages),
+                    int64_t(s.preemptions)})
+    d->tr.ev.push_back(v);
+  return did ? 1 : 0;
+}
+
+long refeng_trace_len(void* h) { return long(static_cast<Driver*>(h)->tr.ev.size()); }
+void refeng_trace_copy(void* h, int64_t* out) {
+  auto& ev = static_cast<Driver*>(h)->tr.ev;
+  std::memcpy(out, ev.data(), ev.size() * sizeof(int64_t));
+}
+int refeng_num_tables(void* h) { return int(static_cast<Driver*>(h)->tr.tables.size()); }
+void refeng_table_copy(void* h, int index, int32_t* out) {
+  auto& t = static_cast<Driver*>(h)->tr.tables[size_t(index)];
+  std::memcpy(out, t.data(), t.size() * sizeof(int32_t));
+}
+// The token the recording model makes the engine sample for (request, position): position p's logits give token p + 1.
+int refeng_token(uint64_t seq, int pos) { return 2 + int(mix(seq * 1000003ull + uint64_t(pos)) % uint64_t(kVocab - 2)); }
+
+}  // extern "C"

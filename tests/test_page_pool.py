@@ -1,0 +1,218 @@
+"""The from-scratch page pool against the reference's own engine, on the CPU.
+
+oracle/_ref/libref_engine.so is the reference's unmodified src/engine/engine.cpp + sampler.cpp driven through a
+recording StepModel (oracle/ref_engine_driver.cpp). Its trace — every set_block_tables() table, every chunk, state
+save and finished request, and the allocator counters after each iterate() — is replayed into pkv_pool_* and the block
+tables must match entry for entry (stale tails included), as must the free / cached page counts. This is the
+reference's own test method (tools/sched_test/main.cpp drives iterate() on a fake model) turned into a differential.
+
+Copy-on-write, LRU freeing and compaction have no reference counterpart (parity unpinned): their tests check the
+stated rules and invariants.
+"""
+import ctypes as C
+from collections import deque
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import pkv_testlib as tl
+from oracle import build_oracle
+from unholy_b200 import capi
+
+i32p = C.POINTER(C.c_int32)
+
+
+def ptr(a):
+    return a.ctypes.data_as(i32p)
+
+
+@pytest.fixture(scope="module")
+def refeng():
+    libs = build_oracle.build_reference()
+    if not libs["engine"]:
+        pytest.skip("oracle/_ref/libref_engine.so not built (no reference checkout here)")
+    h = C.CDLL(str(libs["engine"]))
+    h.refeng_create.restype, h.refeng_create.argtypes = C.c_void_p, [C.c_int] * 6
+    h.refeng_destroy.argtypes = [C.c_void_p]
+    h.refeng_submit.restype, h.refeng_submit.argtypes = C.c_uint64, [C.c_void_p, i32p, C.c_int, C.c_int]
+    h.refeng_iterate.restype, h.refeng_iterate.argtypes = C.c_int, [C.c_void_p]
+    h.refeng_trace_len.restype, h.refeng_trace_len.argtypes = C.c_long, [C.c_void_p]
+    h.refeng_trace_copy.argtypes = [C.c_void_p, C.c_void_p]
+    h.refeng_num_tables.restype, h.refeng_num_tables.argtypes = C.c_int, [C.c_void_p]
+    h.refeng_table_copy.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+    h.refeng_token.restype, h.refeng_token.argtypes = C.c_int, [C.c_uint64, C.c_int]
+    return h
+
+
+class Replay:
+    """Feeds the reference engine and the page pool the same requests; after every iterate() of the engine replays
+    the new trace records into the pool and compares."""
+
+    def __init__(self, pkv, refeng, num_pages, page_tokens, slots, pps, budget):
+        self.pkv, self.ref = pkv, refeng
+        self.pt, self.slots, self.pps, self.budget, self.num_pages = page_tokens, slots, pps, budget, num_pages
+        self.eng = refeng.refeng_create(num_pages, page_tokens, slots, pps, budget, 8192)
+        self.pool = pkv.pkv_pool_create(num_pages, page_tokens, slots, pps, 1)
+        self.tokens, self.handle, self.computed = {}, {}, {}
+        self.waiting, self.running = deque(), []
+        self.saved = set()
+        self.cursor = 0
+        self.tables_checked = 0
+        self.max_cached = 0
+
+    def close(self):
+        self.ref.refeng_destroy(self.eng)
+        self.pkv.pkv_pool_destroy(self.pool)
+
+    def submit(self, prompt, max_tokens):
+        a = np.ascontiguousarray(prompt, np.int32)
+        rid = int(self.ref.refeng_submit(self.eng, ptr(a), len(a), max_tokens))
+        self.tokens[rid] = list(map(int, a))
+        self.waiting.append(rid)
+        return rid
+
+    def page_hash(self, rid, page_index):
+        t = np.asarray(self.tokens[rid][:(page_index + 1) * self.pt], np.int32)
+        return int(self.pkv.pkv_page_hash(ptr(t), self.pt, page_index))
+
+    def admit(self):
+        pkv, pool = self.pkv, self.pool
+        while self.waiting and len(self.running) < self.slots:
+            rid = self.waiting[0]
+            if rid not in self.handle:
+                self.handle[rid] = pkv.pkv_pool_seq_open(pool)
+            h = self.handle[rid]
+            toks = np.asarray(self.tokens[rid], np.int32)
+            limit = (len(toks) - 1) // self.pt
+            ok = np.zeros(max(limit, 1), np.uint8)
+            hh = None
+            for i in range(limit):  # a boundary can be resumed only where some sequence saved its state
+                hh = int(pkv.pkv_page_hash(ptr(toks), self.pt, i))
+                ok[i] = hh in self.saved
+            computed = pkv.pkv_pool_match_prefix(pool, h, ptr(toks), len(toks), ok.ctypes.data_as(C.POINTER(C.c_uint8)))
+            first = min(len(toks) - computed, self.budget)
+            npages = pkv.pkv_pool_seq_pages(pool, h, None, 0)
+            need = -(-(computed + first) // self.pt) - npages + len(self.running)
+            if need > pkv.pkv_pool_available(pool):
+                pkv.pkv_pool_release(pool, h)
+                break
+            assert pkv.pkv_pool_assign_slot(pool, h) >= 0
+            self.computed[rid] = computed
+            self.running.append(rid)
+            self.waiting.popleft()
+
+    def iterate(self):
+        did = self.ref.refeng_iterate(self.eng)
+        n = self.ref.refeng_trace_len(self.eng)
+        ev = np.empty(n, np.int64)
+        self.ref.refeng_trace_copy(self.eng, ev.ctypes.data)
+        self.admit()
+        pkv, pool = self.pkv, self.pool
+        i, pending_table = self.cursor, None
+        while i < n:
+            kind = int(ev[i])
+            if kind == 2:
+                pending_table = int(ev[i + 1])
+                i += 2
+            elif kind == 1:
+                nch = int(ev[i + 1])
+                chunks = ev[i + 2:i + 2 + 4 * nch].reshape(nch, 4)
+                i += 2 + 4 * nch
+                nsave = int(ev[i])
+                saves = [int(x) for x in ev[i + 1:i + 1 + nsave]]
+                i += 1 + nsave
+                for seq, slot, s0, cn in chunks:
+                    h = self.handle[int(seq)]
+                    assert pkv.pkv_pool_seq_slot(pool, h) == slot, "slot assignment differs"
+                    assert self.computed[int(seq)] == s0, "prefix-hit length differs"
+                    assert pkv.pkv_pool_alloc(pool, h, int(s0 + cn)) == 1
+                if pending_table is not None:
+                    want = np.empty(self.slots * self.pps, np.int32)
+                    self.ref.refeng_table_copy(self.eng, pending_table, want.ctypes.data)
+                    got = np.ctypeslib.as_array(pkv.pkv_pool_tables(pool), shape=(self.slots * self.pps,))
+                    assert np.array_equal(got, want), f"block tables differ at set_block_tables #{pending_table}"
+                    self.tables_checked += 1
+                    pending_table = None
+                else:
+                    assert not pkv.pkv_pool_dirty(pool), "the pool changed a table the engine did not upload"
+                # completion, in plan order: register full pages, commit saves, sample
+                for seq, slot, s0, cn in chunks:
+                    rid, end = int(seq), int(s0 + cn)
+                    self.computed[rid] = end
+                    toks = np.asarray(self.tokens[rid], np.int32)
+                    capi.check(pkv.pkv_pool_register(pool, self.handle[rid], ptr(toks), len(toks), end))
+                    if slot in saves:
+                        assert end % self.pt == 0
+                        self.saved.add(self.page_hash(rid, end // self.pt - 1))
+                    if end == len(self.tokens[rid]):
+                        self.tokens[rid].append(int(self.ref.refeng_token(rid, end - 1)))
+            elif kind == 3:
+                rid = int(ev[i + 1])
+                i += 2
+                capi.check(pkv.pkv_pool_seq_close(pool, self.handle.pop(rid)))
+                self.running.remove(rid)
+            elif kind == 4:
+                running, waiting, free_pages, cached, preempt = (int(x) for x in ev[i + 1:i + 6])
+                i += 6
+                assert preempt == 0, "scenario sized to avoid preemption"
+                assert (running, waiting) == (len(self.running), len(self.waiting))
+                assert free_pages == pkv.pkv_pool_available(pool)
+                assert cached == pkv.pkv_pool_cached_count(pool)
+                self.max_cached = max(self.max_cached, cached)
+            else:
+                raise AssertionError(f"unknown trace record {kind}")
+        self.cursor = n
+        return did
+
+    def drain(self, limit=200000):
+        for _ in range(limit):
+            if not self.iterate() and not self.running and not self.waiting:
+                return
+        raise AssertionError("engine did not go idle")
+
+
+def test_prefix_churn_matches_reference_engine(pkv, refeng):
+    """Benchmark configuration 4, mode A (reference semantics), at 1/12 scale: prefixes written and released (cached),
+    requests that extend a prefix (fork = match_prefix on shared full pages, no payload copy) and decode 512 tokens,
+    then a filler request that forces LRU evictions of a quarter of the pool."""
+    g = tl.rng(4)
+    num_pages, pt = 2048, 64
+    r = Replay(pkv, refeng, num_pages, pt, slots=8, pps=320, budget=2048)
+    try:
+        prefixes = [g.integers(2, 500, size=int(n)).astype(np.int32) for n in g.integers(170, 5462, size=24)]
+        for p in prefixes:  # one at a time: each finishes, its full pages stay cached and evictable tail-first
+            r.submit(p, 1)
+            r.drain()
+        assert r.max_cached > 0
+        picks = g.choice(len(prefixes), size=8, replace=False)
+        for j in picks:  # eight live requests fork distinct prefixes and append 512 tokens each
+            ext = g.integers(2, 500, size=100).astype(np.int32)
+            r.submit(np.concatenate([prefixes[j], ext]), 512)
+        r.drain()
+        r.submit(g.integers(2, 500, size=num_pages // 4 * pt).astype(np.int32), 1)  # evicts >= 25 % from the LRU front
+        r.drain()
+        assert r.tables_checked > 100
+        assert pkv.pkv_pool_available(r.pool) == num_pages  # no leak (tools/sched_test/main.cpp:1113-1116)
+    finally:
+        r.close()
+
+
+def test_concurrent_admission_matches_reference_engine(pkv, refeng):
+    """More requests than slots, shared and repeated prompts, small pages: admission order, headroom rule and
+    duplicate-hash pages (a page whose name is already cached stays private)."""
+    g = tl.rng(41)
+    r = Replay(pkv, refeng, num_pages=192, page_tokens=16, slots=4, pps=64, budget=256)
+    try:
+        base = [g.integers(2, 500, size=int(n)).astype(np.int32) for n in g.integers(40, 400, size=6)]
+        for rounds in range(3):
+            for j in g.permutation(len(base)):
+                tail = g.integers(2, 500, size=int(g.integers(1, 40))).astype(np.int32)
+                r.submit(np.concatenate([base[j], tail]) if rounds else base[j], int(g.integers(1, 48)))
+            for _ in range(int(g.integers(1, 6))):
+                r.iterate()
+        r.drain()
+        assert r.tables_checked > 20
+        assert pkv.pkv_pool_available(r.pool) == 192
+    finally:
+        r.close()

@@ -183,6 +183,10 @@ struct StepParams {
 
 // The chunk holding batch row t (chunks ordered by t0, disjoint); -1 if none.
 __device__ __forceinline__ int find_chunk(const pkv_chunk* __restrict__ chunks, int n, int t) {
+  if (t < n) {  // a decode step: chunk t is batch row t
+    const int t0 = __ldg(&chunks[t].t0);
+    if (t0 == t && __ldg(&chunks[t].n) >= 1) return t;
+  }
   int lo = 0, hi = n;  // last chunk with t0 <= t
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -216,11 +220,13 @@ constexpr int kGatherUnroll = 6;            // 32 rows x 72 vectors = 384 thread
 
 // One append tile: batch rows [t_first, t_first + kAppendRows) of one layer. Copies the bf16 rows into the pool and
 // quantises the keys (MXFP4 and/or fp8) to the same physical rows.
+template <int NT>
 __device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_first, long long* s_rid) {
+  constexpr int kRows = NT / 16;
   const pkv_step& s = P.s;
   const int tid = threadIdx.x;
-  const int nrows = min(kAppendRows, s.T - t_first);
-  if (tid < kAppendRows) {
+  const int nrows = min(kRows, s.T - t_first);
+  if (tid < kRows) {
     long long rid = -1;
     if (tid < nrows) {
       const int t = t_first + tid;
@@ -237,10 +243,22 @@ __device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_firs
     const int vpr = s.width >> 3;
     const int total = nrows * vpr;
     const uint4* src = reinterpret_cast<const uint4*>(ly.rows + size_t(t_first) * s.width);
-    for (int u = tid; u < total; u += kVecThreads) {
-      const int r = u / vpr, c = u - r * vpr;
-      const long long rid = s_rid[r];
-      if (rid >= 0) st_stream(reinterpret_cast<uint4*>(ly.row_pool + size_t(rid) * s.row_stride) + c, ld_stream(src + u));
+    for (int base = 0; base < total; base += NT * 5) {  // five loads in flight per thread before the first store
+      uint4 v[5];
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        const int u = base + i * NT + tid;
+        if (u < total) v[i] = ld_stream(src + u);
+      }
+#pragma unroll
+      for (int i = 0; i < 5; ++i) {
+        const int u = base + i * NT + tid;
+        if (u < total) {
+          const int r = u / vpr, c = u - r * vpr;
+          const long long rid = s_rid[r];
+          if (rid >= 0) st_stream(reinterpret_cast<uint4*>(ly.row_pool + size_t(rid) * s.row_stride) + c, v[i]);
+        }
+      }
     }
   }
   const bool fp4 = (P.flags & PKV_DO_KEYS_FP4) && ly.keys && ly.key_pool_fp4;
@@ -343,10 +361,12 @@ __global__ void __launch_bounds__(kVecThreads) step_vec_kernel(const __grid_cons
   __shared__ const uint4* s_src[kGatherRows];
   const int per_layer = P.append_tiles + P.gather_tiles;
   const long long total = (long long)per_layer * P.L;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (long long w = blockIdx.x; w < total; w += gridDim.x) {
     const int layer = int(w / per_layer), r = int(w - (long long)layer * per_layer);
     const pkv_layer& ly = P.layers[layer];
-    if (r < P.append_tiles) append_tile(P, ly, r * kAppendRows, s_rid);
+    if (r < P.append_tiles) append_tile<kVecThreads>(P, ly, r * kAppendRows, s_rid);
     else gather_tile_vec(P, ly, r - P.append_tiles, s_src);
   }
 }
@@ -418,6 +438,22 @@ __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
+  // Programmatic dependent launch: this grid may have been scheduled while the previous kernel of the stream was still
+  // draining. Nothing above touches global memory; everything below waits for that kernel's writes to be visible.
+  // The next kernel of the stream may be scheduled as soon as SM resources free up (it waits the same way).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Fused append: the step's new rows and keys are written by the CTAs at the END of the grid, which own one gather
+  // tile fewer than the others whenever the tile count does not divide evenly. In-chunk index entries read the row
+  // from its source (gather_source), so the gather does not depend on these writes.
+  if (P.append_tiles > 0) {
+    __shared__ long long s_rid[2];
+    const long long atotal = (long long)P.append_tiles * P.L;
+    for (long long a = gridDim.x - 1 - blockIdx.x; a < atotal; a += gridDim.x) {
+      const int layer = int(a / P.append_tiles), tile = int(a - (long long)layer * P.append_tiles);
+      append_tile<32>(P, P.layers[layer], tile * 2, s_rid);
+    }
+  }
   const long long first = blockIdx.x, stride = gridDim.x;
   const long long mine = first < total ? (total - first + stride - 1) / stride : 0;
 
@@ -712,9 +748,32 @@ int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   per_sm = std::max(1, std::min(per_sm, 32));
   const long long tiles = (long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS);
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * per_sm)));
-  gather_bulk_kernel<STAGES, ROWS><<<grid, 32, smem, st>>>(P);
-  PKV_LAUNCH_CHECK("gather_bulk_kernel");
+  static const int pdl = env_int("PKV_PDL", 1);
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel<STAGES, ROWS>, P);
+  if (le != cudaSuccess) return fail_cuda("gather_bulk_kernel launch", le);
   return PKV_OK;
+}
+
+int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t st) {
+  switch (shape) {
+    case 316: return launch_bulk<3, 16>(P, ctas_per_sm, st);
+    case 416: return launch_bulk<4, 16>(P, ctas_per_sm, st);
+    case 332: return launch_bulk<3, 32>(P, ctas_per_sm, st);
+    case 308: return launch_bulk<3, 8>(P, ctas_per_sm, st);
+    case 408: return launch_bulk<4, 8>(P, ctas_per_sm, st);
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape (316, 416, 332, 308, 408)");
+  }
 }
 
 }  // namespace
@@ -857,7 +916,7 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
     if (gather && (!y.idx || !y.gathered || !y.row_pool)) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks idx, gathered or row_pool");
   }
   static const int grid_mult = env_int("PKV_VEC_CTAS_PER_SM", 5);
-  static const int bulk_shape = env_int("PKV_BULK_SHAPE", 416);     // STAGES * 100 + ROWS
+  static const int bulk_shape = env_int("PKV_BULK_SHAPE", 316);     // STAGES * 100 + ROWS
   static const int bulk_ctas = env_int("PKV_BULK_CTAS_PER_SM", 0);  // 0: as many as shared memory allows
 
   StepParams P;
@@ -867,6 +926,15 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   P.flags = flags;
   std::memcpy(P.layers, layers, sizeof(pkv_layer) * size_t(L));
   const bool bulk = gather && (flags & PKV_VARIANT_BULK);
+  // With the bulk pipeline a small append (a decode step) rides inside the gather launch, two rows per 32-thread tile.
+  const bool fuse_append = bulk && append && (long long)((s.T + 1) / 2) * L <= 148;
+  if (fuse_append) {
+    StepParams B = P;
+    B.append_tiles = (s.T + 1) / 2;
+    B.tiles_per_q = 0;
+    B.gather_tiles = 0;
+    return dispatch_bulk(B, bulk_shape, bulk_ctas, stream);
+  }
   P.append_tiles = append ? (s.T + kAppendRows - 1) / kAppendRows : 0;
   P.tiles_per_q = (s.k + kGatherRows - 1) / kGatherRows;
   P.gather_tiles = gather && !bulk ? s.Q * P.tiles_per_q : 0;
@@ -879,17 +947,8 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
     PKV_LAUNCH_CHECK("step_vec_kernel");
   }
   if (bulk) {
-    switch (bulk_shape) {
-      case 316: return launch_bulk<3, 16>(P, bulk_ctas, stream);
-      case 416: return launch_bulk<4, 16>(P, bulk_ctas, stream);
-      case 616: return launch_bulk<6, 16>(P, bulk_ctas, stream);
-      case 332: return launch_bulk<3, 32>(P, bulk_ctas, stream);
-      case 432: return launch_bulk<4, 32>(P, bulk_ctas, stream);
-      case 632: return launch_bulk<6, 32>(P, bulk_ctas, stream);
-      case 408: return launch_bulk<4, 8>(P, bulk_ctas, stream);
-      case 808: return launch_bulk<8, 8>(P, bulk_ctas, stream);
-      default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape");
-    }
+    P.append_tiles = 0;
+    return dispatch_bulk(P, bulk_shape, bulk_ctas, stream);
   }
   return PKV_OK;
 }
