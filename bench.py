@@ -46,6 +46,8 @@ FP4_PAGE_BYTES = RPP * 68             # 4,352
 APPEND_BYTES = 2 * ROW_BYTES + (KEY_DIM * 2 + 68)      # 2304 + 324
 GATHER_BYTES = K_SEL * 2 * ROW_BYTES                   # 2048 rows read and written
 STEP_BYTES_PER_GPU = LAYERS * NSEQ * (APPEND_BYTES + GATHER_BYTES)
+# dram__bytes_read.sum + dram__bytes_write.sum of one per-layer launch (ncu capture summarised under profiles/).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 248_560_000
 WORKLOAD_NAME = "decode43: 64 seq x 128k ctx per GPU, page 64, 43 layers, bf16 576 rows + MXFP4 128 keys, top-2048 gather"
 
 
@@ -429,7 +431,10 @@ def run_ours(args):
             "pct_of_measured_peak_per_gpu": round(per_gpu / peak * 100, 2),
             "bit_exact_check": {"ok": all_ok, "what": why},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": "of " + peak_kind,
+                         "frac": round(achieved / peak, 4),
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and wl.lpl == 1) else None,
+                         "traffic_source": "profiles/gather_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
+                         "peak_kind": "of " + peak_kind,
                          "kernel": "gather_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
                          "algorithmic_bytes_per_launch": int(call_bytes)},
             "gpu_launches": launches, "clocks": clocks,

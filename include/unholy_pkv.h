@@ -43,6 +43,10 @@ enum {
 
 PKV_API const char* pkv_last_error(void);
 PKV_API int pkv_abi_version(void);
+/* Performance knobs (no counterpart in the reference; results never depend on them). knob 0: bulk pipeline shape
+ * STAGES*100+ROWS; 1: bulk CTAs per SM (0 = fill shared memory); 2: programmatic dependent launch on/off; 3: CTAs per
+ * SM of the vector kernels; 4: index prefetch on/off. The defaults come from PKV_* environment variables. */
+PKV_API int pkv_tune(int knob, int value);
 
 /* First failed device-side check since the last call (0 = none): bit 0..7 = kind (1 page id out of range,
  * 2 chunk row out of range, 3 bounded wait gave up), the rest = an index identifying the entry. Synchronises the

@@ -44,6 +44,7 @@ _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 _SIGS = {
     "pkv_last_error": (C.c_char_p, []),
     "pkv_abi_version": (_i, []),
+    "pkv_tune": (_i, [_i, _i]),
     "pkv_device_status": (_i, [C.POINTER(C.c_int)]),
     "pkv_store_rows": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_store_rows_fp4": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),

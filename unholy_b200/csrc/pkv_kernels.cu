@@ -79,6 +79,17 @@ int env_int(const char* name, int dflt) {
   const char* v = std::getenv(name);
   return v && *v ? std::atoi(v) : dflt;
 }
+struct Tuning {
+  int bulk_shape = env_int("PKV_BULK_SHAPE", 308);       // STAGES * 100 + ROWS of the bulk gather pipeline
+  int bulk_ctas_per_sm = env_int("PKV_BULK_CTAS_PER_SM", 0);  // 0: as many as shared memory allows
+  int pdl = env_int("PKV_PDL", 1);                       // programmatic dependent launch of the bulk kernel
+  int vec_ctas_per_sm = env_int("PKV_VEC_CTAS_PER_SM", 5);
+  int prefetch = env_int("PKV_BULK_PREFETCH", 0);        // resolve index entries one tile ahead of the copies
+};
+Tuning& tuning() {
+  static Tuning t;
+  return t;
+}
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Streaming 16-byte accesses: the pool rows and the gathered output are touched once per launch, so they bypass L1 and
@@ -420,7 +431,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
-template <int STAGES, int ROWS>
+template <int STAGES, int ROWS, bool PREFETCH>
 __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__ StepParams P) {
   static_assert(ROWS <= 32 && STAGES >= 3, "one lane per row; two stages drain while the others fill");
   extern __shared__ __align__(128) unsigned char smem[];
@@ -457,17 +468,46 @@ __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__
   const long long first = blockIdx.x, stride = gridDim.x;
   const long long mine = first < total ? (total - first + stride - 1) / stride : 0;
 
-  // Fills stage (j % STAGES) with tile j of this CTA: resolve each lane's row, zero masked rows, start the loads.
-  auto produce = [&](long long j) {
+  // Address resolution is split in two so that its dependent loads overlap the copies: fetch(j) issues the loads that
+  // do not depend on anything (the lane's index entry, the query's visibility and chunk) one tile before issue(j)
+  // uses them for the block-table lookup and starts the row copies into stage j % STAGES.
+  struct Staged {
+    int row, vis;
+    pkv_chunk ch;
+  };
+  auto locate = [&](long long j, int& layer, int& q, int& e0) {
     const long long w = first + j * stride;
-    const int layer = int(w / per_layer);
+    layer = int(w / per_layer);
     const long long r = w - (long long)layer * per_layer;
-    const int q = int(r / tiles_per_q), e0 = int(r - (long long)q * tiles_per_q) * ROWS;
+    q = int(r / tiles_per_q);
+    e0 = int(r - (long long)q * tiles_per_q) * ROWS;
+  };
+  auto fetch = [&](long long j) {
+    int layer, q, e0;
+    locate(j, layer, q, e0);
+    Staged g;
+    const int e = e0 + lane;
+    g.row = (lane < ROWS && e < s.k) ? __ldg(&P.layers[layer].idx[size_t(q) * s.k + e]) : -1;
+    g.vis = __ldg(&s.q_visible[q]);
+    g.ch = s.chunks[__ldg(&s.q_chunk[q])];
+    return g;
+  };
+  auto issue = [&](long long j, const Staged& g) {
+    int layer, q, e0;
+    locate(j, layer, q, e0);
     const pkv_layer& ly = P.layers[layer];
     const int st = int(j % STAGES);
     unsigned char* stage = smem + size_t(st) * stage_bytes;
     const uint32_t bar = smem_addr(&bars[st]);
-    const uint4* src = lane < ROWS ? gather_source(P, ly, q, e0 + lane) : nullptr;
+    const uint4* src = nullptr;
+    if (g.row >= 0 && g.row < g.vis) {
+      if ((P.flags & PKV_DO_ROWS) && ly.rows && g.row >= g.ch.s0 && g.row < g.ch.s0 + g.ch.n) {
+        src = reinterpret_cast<const uint4*>(ly.rows + size_t(g.ch.t0 + (g.row - g.ch.s0)) * s.width);
+      } else {
+        const long long rid = physical_row(s, g.ch.slot, g.row, q);
+        if (rid >= 0) src = reinterpret_cast<const uint4*>(ly.row_pool + size_t(rid) * s.row_stride);
+      }
+    }
     const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
     if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(valid)) * row_bytes);
     // Masked rows (and rows past k, which are never stored) are zero-filled by the whole warp, one row at a time.
@@ -483,7 +523,16 @@ __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__
   };
 
   const long long ahead = STAGES - 2;
-  for (long long j = 0; j < ahead && j < mine; ++j) produce(j);
+  Staged next_g;
+  next_g.row = -1;
+  next_g.vis = 0;
+  next_g.ch = pkv_chunk{0, 0, 0, 0};
+  if (PREFETCH && mine > 0) next_g = fetch(0);
+  for (long long j = 0; j < ahead && j < mine; ++j) {
+    const Staged g = PREFETCH ? next_g : fetch(j);
+    if (PREFETCH && j + 1 < mine) next_g = fetch(j + 1);
+    issue(j, g);
+  }
   bool alive = true;
   long long j_fail = 0;
   for (long long j = 0; j < mine; ++j) {
@@ -491,7 +540,9 @@ __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__
     if (j + ahead < mine) {
       if (lane == 0) bulk_wait_read<1>();
       __syncwarp();
-      produce(j + ahead);
+      const Staged g = PREFETCH ? next_g : fetch(j + ahead);
+      if (PREFETCH && j + ahead + 1 < mine) next_g = fetch(j + ahead + 1);
+      issue(j + ahead, g);
     }
     const int st = int(j % STAGES);
     const uint32_t parity = uint32_t(j / STAGES) & 1u;
@@ -730,15 +781,15 @@ int check_quant_shape(int rows, int cols, int block, const char* name) {
   return PKV_OK;
 }
 
-template <int STAGES, int ROWS>
-int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
+template <int STAGES, int ROWS, bool PREFETCH>
+int launch_bulk_impl(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   const size_t smem = size_t(STAGES) * ROWS * size_t(P.s.width) * 2u;
   if (smem > 227u * 1024u - 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
   static thread_local bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(gather_bulk_kernel<STAGES, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    const cudaError_t e = cudaFuncSetAttribute(gather_bulk_kernel<STAGES, ROWS, PREFETCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     configured[dev] = true;
   }
@@ -748,7 +799,7 @@ int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   per_sm = std::max(1, std::min(per_sm, 32));
   const long long tiles = (long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS);
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * per_sm)));
-  static const int pdl = env_int("PKV_PDL", 1);
+  const int pdl = tuning().pdl;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(grid));
@@ -760,9 +811,15 @@ int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel<STAGES, ROWS>, P);
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel<STAGES, ROWS, PREFETCH>, P);
   if (le != cudaSuccess) return fail_cuda("gather_bulk_kernel launch", le);
   return PKV_OK;
+}
+
+template <int STAGES, int ROWS>
+int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
+  return tuning().prefetch ? launch_bulk_impl<STAGES, ROWS, true>(P, ctas_per_sm, st)
+                           : launch_bulk_impl<STAGES, ROWS, false>(P, ctas_per_sm, st);
 }
 
 int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t st) {
@@ -771,8 +828,12 @@ int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t 
     case 416: return launch_bulk<4, 16>(P, ctas_per_sm, st);
     case 332: return launch_bulk<3, 32>(P, ctas_per_sm, st);
     case 308: return launch_bulk<3, 8>(P, ctas_per_sm, st);
+    case 304: return launch_bulk<3, 4>(P, ctas_per_sm, st);
+    case 404: return launch_bulk<4, 4>(P, ctas_per_sm, st);
+    case 604: return launch_bulk<6, 4>(P, ctas_per_sm, st);
+    case 508: return launch_bulk<5, 8>(P, ctas_per_sm, st);
     case 408: return launch_bulk<4, 8>(P, ctas_per_sm, st);
-    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape (316, 416, 332, 308, 408)");
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape (316, 416, 332, 308, 408, 508, 304, 404, 604)");
   }
 }
 
@@ -782,6 +843,18 @@ extern "C" {
 
 const char* pkv_last_error(void) { return g_err.c_str(); }
 int pkv_abi_version(void) { return 1; }
+
+int pkv_tune(int knob, int value) {
+  Tuning& t = tuning();
+  switch (knob) {
+    case 0: t.bulk_shape = value; return PKV_OK;
+    case 1: t.bulk_ctas_per_sm = value; return PKV_OK;
+    case 2: t.pdl = value; return PKV_OK;
+    case 3: t.vec_ctas_per_sm = value > 0 ? value : 5; return PKV_OK;
+    case 4: t.prefetch = value; return PKV_OK;
+    default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
+  }
+}
 
 int pkv_device_status(int* status_out) {
   if (!status_out) return fail(PKV_ERR_ARG, "pkv_device_status: null output");
@@ -915,9 +988,7 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
       return fail(PKV_ERR_ARG, "pkv_step_run: layer pointers must be 16-byte aligned (fp4 pool 4, fp8 codes 8)");
     if (gather && (!y.idx || !y.gathered || !y.row_pool)) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks idx, gathered or row_pool");
   }
-  static const int grid_mult = env_int("PKV_VEC_CTAS_PER_SM", 5);
-  static const int bulk_shape = env_int("PKV_BULK_SHAPE", 316);     // STAGES * 100 + ROWS
-  static const int bulk_ctas = env_int("PKV_BULK_CTAS_PER_SM", 0);  // 0: as many as shared memory allows
+  const int grid_mult = tuning().vec_ctas_per_sm, bulk_shape = tuning().bulk_shape, bulk_ctas = tuning().bulk_ctas_per_sm;
 
   StepParams P;
   std::memset(&P, 0, sizeof(P));
