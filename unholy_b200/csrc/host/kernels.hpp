@@ -1,0 +1,91 @@
+// C++ face of the paged KV-cache kernels with the reference's names, argument order and error behaviour, so that the
+// reference's call sites (src/model/forward_ref.hip:719-745,843-857; src/model/glm5_fast.hip:229-250) compile against
+// it unchanged apart from hipStream_t -> cudaStream_t. Every function forwards to the C ABI (include/unholy_pkv.h) and
+// turns a non-zero status into std::runtime_error, the reference's convention (src/rt/hip.hpp:11-19). Launches are
+// asynchronous on `st`; nullptr is the default stream. Header-only; link with libunholy_pkv.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "../../../include/unholy_pkv.h"
+
+namespace unholy::kernels {
+
+using bf16 = uint16_t;
+
+inline void pkv_throw(int rc, const char* what) {
+  if (rc != PKV_OK) throw std::runtime_error(std::string(what) + ": " + pkv_last_error());
+}
+
+// src/kernels/ref.hpp:92-99.
+struct PagedRows {
+  bf16* pool = nullptr;
+  const int32_t* table = nullptr;
+  int rows_per_page = 0;
+  int row_stride = 0;
+};
+// src/kernels/ref.hpp:100.
+inline void store_rows(const bf16* rows, int n, int width, PagedRows dst, int row0, cudaStream_t st) {
+  pkv_throw(pkv_store_rows(rows, n, width, dst.pool, dst.table, dst.rows_per_page, dst.row_stride, row0,
+                           reinterpret_cast<pkv_stream_t>(st)), "store_rows");
+}
+
+// src/kernels/indexer.hpp:20-34.
+constexpr int kFp4RowsPerPage = 64;
+constexpr int kFp4RowBytes = 64;
+constexpr int kFp4PageBytes = kFp4RowsPerPage * (kFp4RowBytes + 4);
+struct PagedFp4 {
+  uint8_t* pool = nullptr;
+  const int32_t* table = nullptr;
+};
+inline void store_rows_fp4(const bf16* rows, int n, PagedFp4 dst, int row0, cudaStream_t st) {
+  pkv_throw(pkv_store_rows_fp4(rows, n, dst.pool, dst.table, kFp4RowsPerPage, row0, reinterpret_cast<pkv_stream_t>(st)),
+            "store_rows_fp4");
+}
+inline void load_rows_fp4(PagedFp4 src, int row0, int n, bf16* out, cudaStream_t st) {
+  pkv_throw(pkv_load_rows_fp4(src.pool, src.table, kFp4RowsPerPage, row0, n, out, reinterpret_cast<pkv_stream_t>(st)),
+            "load_rows_fp4");
+}
+
+// src/kernels/ref.hpp:22-25.
+inline void act_quant_fp8(const bf16* x, int ldx, uint8_t* q, uint8_t* s, int rows, int cols, int block, cudaStream_t st) {
+  pkv_throw(pkv_act_quant_fp8(x, ldx, q, s, rows, cols, block, reinterpret_cast<pkv_stream_t>(st)), "act_quant_fp8");
+}
+inline void fake_quant_fp8(bf16* x, int ldx, int rows, int cols, int block, cudaStream_t st) {
+  pkv_throw(pkv_fake_quant_fp8(x, ldx, rows, cols, block, reinterpret_cast<pkv_stream_t>(st)), "fake_quant_fp8");
+}
+inline void fake_quant_fp4(bf16* x, int ldx, int rows, int cols, int block, cudaStream_t st) {
+  pkv_throw(pkv_fake_quant_fp4(x, ldx, rows, cols, block, reinterpret_cast<pkv_stream_t>(st)), "fake_quant_fp4");
+}
+
+// src/kernels/glm_fast.hpp:21-32 (the pooled-key array of the reference's struct belongs to a kernel outside this path).
+constexpr int kGlmPageRows = 256;
+struct GlmPaged {
+  uint8_t* lat = nullptr;    // e4m3 [pages][256][512]
+  uint8_t* lat_s = nullptr;  // e8m0 [pages][256][8]
+  bf16* pk = nullptr;        // kept for layout compatibility; not touched here
+  const int32_t* table = nullptr;
+};
+inline void glm_store_latent(const bf16* lat, GlmPaged pg, int s0, int n, cudaStream_t st) {
+  pkv_throw(pkv_store_rows_fp8(lat, n, 512, 64, pg.lat, pg.lat_s, pg.table, kGlmPageRows, s0,
+                               reinterpret_cast<pkv_stream_t>(st)), "glm_store_latent");
+}
+
+// src/kernels/ref.hpp:90.
+inline void copy_kernel(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  pkv_throw(pkv_copy(dst, src, bytes, reinterpret_cast<pkv_stream_t>(st)), "copy_kernel");
+}
+
+// The gather the reference carries inside its attention kernels (src/kernels/attn_wmma.hip:75-113), as a call of its
+// own: idx [T][k] entries of the sequence behind `src`, masked entries (< 0 or >= visible[t]) give zero rows.
+inline void gather_rows(PagedRows src, int width, const int32_t* idx, const int32_t* visible, int T, int k, bf16* out,
+                        cudaStream_t st) {
+  pkv_throw(pkv_gather_rows(src.pool, src.table, src.rows_per_page, src.row_stride, width, idx, visible, T, k, out,
+                            reinterpret_cast<pkv_stream_t>(st)), "gather_rows");
+}
+
+}  // namespace unholy::kernels
