@@ -336,3 +336,78 @@ def test_repeat_is_stable(pkv, cuda):
             if first is None:
                 first = sig
             assert sig == first
+
+
+@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+def test_config3_chunked_prefill(pkv, cuda, variant):
+    """Benchmark configuration 3, reduced: one sequence grows in chunks (the first short, then 4096 rows each) over
+    freshly allocated non-contiguous pages; every chunk appends bf16 rows with 1 % outliers at +-20 and quantises its
+    128-wide keys to BOTH fp8 e4m3 (two-array layout, block 64) and MXFP4; 8 query rows at the chunk's last 8 positions
+    gather 2048 positions skewed toward recent tokens (cur - 1 - Geometric(1e-4), distinct, sorted; -1 padded while
+    fewer exist). Pools persist across chunks on the device and in the oracle mirror; everything is compared after
+    every chunk."""
+    g = tl.rng(3)
+    L, k, rpp, W = 2, 2048, tl.RPP, tl.W
+    chunk_sizes = [1000, 4096, 4096, 4096]
+    total = sum(chunk_sizes)
+    pages = -(-total // rpp) + 7
+    pps = pages
+    perm = g.permutation(pages).astype(np.int32)
+    tables = np.zeros((1, pps), np.int32)
+    nrows = pages * rpp
+    h_pool = [np.zeros((nrows, W), np.uint16) for _ in range(L)]
+    h_fp4 = [np.zeros(pages * tl.FP4_PAGE_BYTES, np.uint8) for _ in range(L)]
+    h_codes = [np.zeros((nrows, 128), np.uint8) for _ in range(L)]
+    h_scales = [np.zeros((nrows, 2), np.uint8) for _ in range(L)]
+    d_pool, d_fp4 = [tl.dev(cuda, a) for a in h_pool], [tl.dev(cuda, a) for a in h_fp4]
+    d_codes, d_scales = [tl.dev(cuda, a) for a in h_codes], [tl.dev(cuda, a) for a in h_scales]
+    s0 = 0
+    for n in chunk_sizes:
+        end = s0 + n
+        have = -(-end // rpp)
+        tables[0, :have] = perm[:have]                       # pages for the chunk are taken as it arrives
+        chunks = np.array([[0, s0, n, 0]], np.int32)
+        qpos = np.arange(end - 8, end, dtype=np.int32)
+        q_visible = qpos + 1
+        idx = np.full((8, k), -1, np.int32)
+        for i, p in enumerate(qpos):
+            want = min(k, int(p) + 1)
+            chosen = set()
+            while len(chosen) < want:
+                cand = int(p) - (g.geometric(1e-4, size=2 * k) - 1)
+                chosen.update(int(c) for c in cand[cand >= 0][: want - len(chosen)])
+            idx[i, :want] = np.sort(np.fromiter(chosen, np.int32))
+        d_tables, d_chunks = tl.dev(cuda, tables), tl.dev(cuda, chunks)
+        d_qc, d_qv = tl.dev(cuda, np.zeros(8, np.int32)), tl.dev(cuda, q_visible)
+        step = capi.PkvStep()
+        step.width = step.row_stride = W
+        step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = rpp, pps, pages, 64
+        step.nchunks, step.T, step.Q, step.k = 1, n, 8, k
+        step.tables, step.chunks, step.q_chunk, step.q_visible = (d_tables.data_ptr(), d_chunks.data_ptr(),
+                                                                  d_qc.data_ptr(), d_qv.data_ptr())
+        layers = tl.make_layers(L)
+        keep, outs, wants = [], [], []
+        for l in range(L):
+            rows, keys = tl.outlier_rows(g, n, W), tl.key_rows(g, n)
+            d_r, d_k, d_i = tl.dev(cuda, rows), tl.dev(cuda, keys), tl.dev(cuda, idx)
+            d_o = cuda.full((8 * k * W * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+            keep += [d_r, d_k, d_i]
+            outs.append(d_o)
+            y = layers[l]
+            y.rows, y.row_pool, y.keys, y.key_pool_fp4 = d_r.data_ptr(), d_pool[l].data_ptr(), d_k.data_ptr(), d_fp4[l].data_ptr()
+            y.key_fp8_codes, y.key_fp8_scales, y.idx, y.gathered = (d_codes[l].data_ptr(), d_scales[l].data_ptr(),
+                                                                    d_i.data_ptr(), d_o.data_ptr())
+            orc.store_rows_chunks(rows, h_pool[l], tables, rpp, W, chunks)
+            orc.store_rows_fp4_chunks(keys, h_fp4[l], tables, rpp, chunks)
+            orc.store_rows_fp8_chunks(keys, 64, h_codes[l], h_scales[l], tables, rpp, chunks)
+            wants.append(orc.gather_rows(h_pool[l], tables, rpp, W, W, idx, np.zeros(8, np.int32), q_visible))
+        capi.check(pkv.pkv_step_run(C.byref(step), layers, L, ALL | variant, tl.stream_ptr(cuda)))
+        cuda.cuda.synchronize()
+        assert tl.device_status(pkv) == 0
+        for l in range(L):
+            assert np.array_equal(tl.host(d_pool[l], np.uint16, h_pool[l].shape), h_pool[l]), ("rows", s0, l)
+            assert np.array_equal(tl.host(d_fp4[l], np.uint8), h_fp4[l]), ("fp4", s0, l)
+            assert np.array_equal(tl.host(d_codes[l], np.uint8, h_codes[l].shape), h_codes[l]), ("fp8 codes", s0, l)
+            assert np.array_equal(tl.host(d_scales[l], np.uint8, h_scales[l].shape), h_scales[l]), ("fp8 scales", s0, l)
+            assert np.array_equal(tl.host(outs[l], np.uint16, wants[l].shape), wants[l]), ("gather", s0, l)
+        s0 = end
