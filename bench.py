@@ -63,6 +63,8 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="a reduced pool (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded"], default="decode43",
+                    help="decode43 is the benchmark line; the others measure the remaining operations of the path")
     return ap.parse_args()
 
 
@@ -457,10 +459,517 @@ def run_ours(args):
         sys.exit(3)
 
 
+def _cuda_setup():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    from unholy_b200 import capi
+    return torch, capi, capi.lib()
+
+
+def _emit(name, value, ms, extra):
+    peak, kind = load_peaks()
+    line = {"metric": "paged_kv_" + name + "_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
+            "ms_total": round(ms, 3), "higher_is_better": True, "data": "synthetic",
+            "pct_of_8TBps": round(value / 80, 2), "pct_of_measured_peak": round(value / peak * 100, 2),
+            "peak": peak, "peak_kind": "of " + kind}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def run_prefill(args):
+    """Configuration 3: one sequence filled 0 -> 512k tokens in 4096-token chunks across 43 layers. Per chunk and layer
+    ONE library call: 4096 bf16 rows appended into freshly taken, non-contiguous pages, their 128-wide keys quantised to
+    fp8 e4m3 (block 64) and MXFP4, and 8 query rows at the chunk's end gathering 2048 positions skewed toward recent
+    tokens. All 43 layers' pools are resident (30 GB)."""
+    torch, capi, lib = _cuda_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    chunk, total = 4096, (32768 if args.small else 524288)
+    nchunks, pages = total // chunk, total // RPP
+    perm = torch.randperm(pages, generator=g, device=dev).to(torch.int32).view(1, pages).contiguous()
+    rows_pool = [torch.zeros(pages * PAGE_BYTES // 2, dtype=torch.bfloat16, device=dev) for _ in range(LAYERS)]
+    fp4 = [torch.zeros(pages * FP4_PAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(LAYERS)]
+    codes = [torch.zeros(pages * RPP * KEY_DIM, dtype=torch.uint8, device=dev) for _ in range(LAYERS)]
+    scales = [torch.zeros(pages * RPP * 2, dtype=torch.uint8, device=dev) for _ in range(LAYERS)]
+    x = torch.randn(LAYERS, chunk, W, generator=g, device=dev)
+    m = torch.rand(LAYERS, chunk, W, generator=g, device=dev) < 0.01       # 1 % outliers at +-20
+    x[m] = torch.where(torch.rand(int(m.sum()), generator=g, device=dev) < 0.5, -20.0, 20.0)
+    rows = x.to(torch.bfloat16)
+    del x, m
+    keys = torch.randn(LAYERS, chunk, KEY_DIM, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty(LAYERS, 8, K_SEL, W, dtype=torch.bfloat16, device=dev)
+    # per chunk: the chunk descriptor, the 8 queries' visibility, their index lists (shared by the layers)
+    chunks = torch.tensor([[0, c * chunk, chunk, 0] for c in range(nchunks)], dtype=torch.int32, device=dev)
+    q_vis = torch.stack([torch.arange((c + 1) * chunk - 7, (c + 1) * chunk + 1, device=dev) for c in range(nchunks)]).to(torch.int32)
+    q_chunk = torch.zeros(8, dtype=torch.int32, device=dev)
+    idx = torch.full((nchunks, 8, K_SEL), -1, dtype=torch.int32, device=dev)
+    for c in range(nchunks):
+        for i in range(8):
+            p = int(q_vis[c, i]) - 1
+            cand = p - (torch.empty(6 * K_SEL, device=dev).geometric_(1e-4, generator=g).long() - 1)
+            u = torch.unique(cand[cand >= 0])                               # duplicates dropped (resampled by oversampling)
+            if u.numel() > K_SEL:
+                u = u[torch.randperm(u.numel(), generator=g, device=dev)[:K_SEL]].sort().values
+            idx[c, i, :u.numel()] = u.to(torch.int32)
+    valid_entries = int((idx >= 0).sum())
+    step = capi.PkvStep()
+    step.width = step.row_stride = W
+    step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pages, pages, 64
+    step.nchunks, step.T, step.Q, step.k = 1, chunk, 8, K_SEL
+    step.tables, step.q_chunk = perm.data_ptr(), q_chunk.data_ptr()
+    layers = (capi.PkvLayer * LAYERS)()
+    for l in range(LAYERS):
+        y = layers[l]
+        y.rows, y.row_pool, y.keys, y.key_pool_fp4 = rows[l].data_ptr(), rows_pool[l].data_ptr(), keys[l].data_ptr(), fp4[l].data_ptr()
+        y.key_fp8_codes, y.key_fp8_scales, y.gathered = codes[l].data_ptr(), scales[l].data_ptr(), out[l].data_ptr()
+    flags = (capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_KEYS_FP8 | capi.PKV_DO_GATHER |
+             (capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0))
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(LAYERS)]
+
+    def run_all():
+        for c in range(nchunks):
+            step.chunks = chunks[c].data_ptr()
+            step.q_visible = q_vis[c].data_ptr()
+            for l in range(LAYERS):
+                layers[l].idx = idx[c].data_ptr()
+                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, flags, sp))
+
+    run_all()  # warm-up pass (also the pass that is verified)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run_all()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    nbytes = nchunks * LAYERS * chunk * (2 * ROW_BYTES + KEY_DIM * 2 + 68 + KEY_DIM + 2) + LAYERS * valid_entries * 2 * ROW_BYTES
+    # check: the last chunk's rows are where the table says, and the last query's tile equals the pool rows it names
+    st = C.c_int(0)
+    capi.check(lib.pkv_device_status(C.byref(st)))
+    ok = st.value == 0
+    for l in (0, LAYERS - 1):
+        pool = rows_pool[l].view(-1, W)
+        pos = torch.arange((nchunks - 1) * chunk, total, device=dev)
+        phys = perm[0].long()[pos // RPP] * RPP + pos % RPP
+        ok &= torch.equal(pool[phys].view(torch.int16), rows[l].view(torch.int16))
+        sel = idx[nchunks - 1, 7].long()
+        ph = perm[0].long()[sel.clamp(min=0) // RPP] * RPP + sel.clamp(min=0) % RPP
+        want = pool[ph].clone()
+        want[sel < 0] = 0
+        ok &= torch.equal(out[l, 7].view(torch.int16), want.view(torch.int16))
+    _emit("prefill", nbytes / (ms * 1e-3) / 1e9, ms, {
+        "config": {"workload": f"chunked prefill 0->{total} tokens, {nchunks} chunks x 43 layers, bf16 rows + fp8 + MXFP4 keys, 8 queries x 2048 per chunk",
+                   "gather_variant": args.variant},
+        "algorithmic_GB": round(nbytes / 1e9, 2), "calls": nchunks * LAYERS, "us_per_call": round(ms * 1e3 / (nchunks * LAYERS), 2),
+        "bit_exact_check": {"ok": bool(ok)}})
+
+
+def run_churn(args):
+    """Configuration 4: prefix-cache churn on a 1.5M-token pool (24,576 pages, 43 layers of bf16 row + MXFP4 key pools,
+    82.5 GB). 64 prefixes of 2k..64k tokens are written and released (their full pages stay cached, later ones evict
+    earlier ones LRU-first); 8 live requests take the 8 newest prefixes from the cache (shared full pages), are forked
+    once each at their unaligned end (copy-on-write of the shared partial page on the first append), and all 16
+    sequences append 512 rows; a quarter of the pool is freed from the LRU front and the pool is compacted. Rows carry a
+    pattern derived from (writer, position, layer), so every live sequence is verified after compaction by reading it
+    back through its block table. Fork/COW/compaction have no reference counterpart (parity unpinned)."""
+    torch, capi, lib = _cuda_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    N = 2048 if args.small else 24576
+    lo, hi = (256, 4096) if args.small else (2048, 65536)
+    L, slots = LAYERS, 32
+    pps = (hi + 2048) // RPP
+    pool = lib.pkv_pool_create(N, RPP, slots, pps, 1)
+    rng = np.random.Generator(np.random.MT19937(4))
+    rows_pool = [torch.zeros(N * PAGE_BYTES // 2, dtype=torch.int16, device=dev) for _ in range(L)]
+    fp4 = [torch.zeros(N * FP4_PAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(L)]
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    i32p = C.POINTER(C.c_int32)
+    CH = 4096
+    cols = torch.arange(W, device=dev, dtype=torch.int64) * 31
+    stage = torch.empty(L, CH, W, dtype=torch.int16, device=dev)
+    keys = torch.randn(CH, KEY_DIM, device=dev).to(torch.bfloat16)
+    d_tables = torch.zeros(slots * pps, dtype=torch.int32, device=dev)
+    layers = (capi.PkvLayer * L)()
+    for l in range(L):
+        layers[l].rows, layers[l].row_pool = stage[l].data_ptr(), rows_pool[l].data_ptr()
+        layers[l].keys, layers[l].key_pool_fp4 = keys.data_ptr(), fp4[l].data_ptr()
+    lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(L)]
+    step = capi.PkvStep()
+    step.width = step.row_stride = W
+    step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
+    step.tables = d_tables.data_ptr()
+    timers = {}
+
+    def timed(name, fn, nbytes):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = timers.setdefault(name, [0.0, 0])
+        t[0] += e0.elapsed_time(e1)
+        t[1] += nbytes
+
+    def pattern(writer, s0, n, layer):
+        v = (writer * 40503 + (torch.arange(s0, s0 + n, device=dev, dtype=torch.int64) * 9973)[:, None] + layer * 613 + cols[None, :])
+        return (v & 0x7FFF).to(torch.int16)
+
+    def upload_tables():
+        t = np.ctypeslib.as_array(lib.pkv_pool_tables(pool), shape=(slots * pps,))
+        d_tables.copy_(torch.from_numpy(t.copy()), non_blocking=False)
+
+    def append(items, name):
+        """items: [(handle, writer, s0, n)], n <= CH in total per call group; all layers, one call per layer."""
+        chunk_list, t0 = [], 0
+        for h, writer, s0, n in items:
+            chunk_list.append([lib.pkv_pool_seq_slot(pool, h), s0, n, t0])
+            for l in range(L):
+                stage[l, t0:t0 + n] = pattern(writer, s0, n, l)
+            t0 += n
+        upload_tables()
+        d_chunks = torch.tensor(chunk_list, dtype=torch.int32, device=dev)
+        step.nchunks, step.T, step.Q, step.k = len(chunk_list), t0, 0, 0
+        step.chunks = d_chunks.data_ptr()
+
+        def go():
+            for l in range(L):
+                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4, sp))
+        timed(name, go, L * t0 * (2 * ROW_BYTES + KEY_DIM * 2 + 68))
+
+    def copy_pages(src, dst, name):
+        descs = (capi.PkvPoolDesc * (2 * L))()
+        for l in range(L):
+            descs[2 * l].src_base = descs[2 * l].dst_base = rows_pool[l].data_ptr()
+            descs[2 * l].page_bytes = PAGE_BYTES
+            descs[2 * l + 1].src_base = descs[2 * l + 1].dst_base = fp4[l].data_ptr()
+            descs[2 * l + 1].page_bytes = FP4_PAGE_BYTES
+        ids = torch.tensor(np.concatenate([src, dst]).astype(np.int32), device=dev)
+        n = len(src)
+        timed(name, lambda: capi.check(lib.pkv_copy_pages(descs, 2 * L, ids.data_ptr(), ids.data_ptr() + 4 * n, n, N, N, sp)),
+              2 * n * L * (PAGE_BYTES + FP4_PAGE_BYTES))
+
+    def write_range(h, writer, s0, end, name):
+        while s0 < end:
+            n = min(CH, end - s0)
+            assert lib.pkv_pool_alloc(pool, h, s0 + n) == 1
+            append([(h, writer, s0, n)], name)
+            s0 += n
+
+    # phase 1: prefixes written, named, released
+    lengths = rng.integers(lo, hi + 1, size=64)
+    toks = [rng.integers(2, 50000, size=int(n)).astype(np.int32) for n in lengths]
+    for j, n in enumerate(lengths):
+        h = lib.pkv_pool_seq_open(pool)
+        assert lib.pkv_pool_assign_slot(pool, h) >= 0
+        write_range(h, j, 0, int(n), "prefix_append")
+        capi.check(lib.pkv_pool_register(pool, h, toks[j].ctypes.data_as(i32p), int(n), int(n)))
+        capi.check(lib.pkv_pool_seq_close(pool, h))
+    # phase 2: 8 live requests on the 8 newest prefixes; each is forked at its unaligned end
+    live = []   # (handle, segments [(writer, start, end)], length)
+    src, dst = np.zeros(64, np.int32), np.zeros(64, np.int32)
+    for r in range(8):
+        j = 63 - r
+        prompt = np.concatenate([toks[j], rng.integers(2, 50000, size=37 + r).astype(np.int32)])
+        h = lib.pkv_pool_seq_open(pool)
+        hit = lib.pkv_pool_match_prefix(pool, h, prompt.ctypes.data_as(i32p), len(prompt), None)
+        assert lib.pkv_pool_assign_slot(pool, h) >= 0
+        write_range(h, 100 + r, hit, len(prompt), "request_prefill")
+        segs = [(j, 0, hit), (100 + r, hit, len(prompt))]
+        c = lib.pkv_pool_fork(pool, h, len(prompt))
+        assert c >= 0 and lib.pkv_pool_assign_slot(pool, c) >= 0
+        live += [[h, list(segs), len(prompt), 100 + r], [c, list(segs), len(prompt), 200 + r]]
+    cow_pairs = 0
+    for rec in live:   # the first append into the shared partial page duplicates it
+        h, segs, n, writer = rec
+        assert lib.pkv_pool_alloc(pool, h, n + 512) == 1
+        m = lib.pkv_pool_cow(pool, h, n, 512, src.ctypes.data_as(i32p), dst.ctypes.data_as(i32p), 64)
+        assert m >= 0
+        if m:
+            copy_pages(src[:m].copy(), dst[:m].copy(), "cow_copy")
+            cow_pairs += m
+    for g0 in range(0, len(live), 8):   # 8 sequences x 512 rows = one 4096-row call per layer
+        append([(rec[0], rec[3], rec[2], 512) for rec in live[g0:g0 + 8]], "append_512")
+    for rec in live:
+        rec[1].append((rec[3], rec[2], rec[2] + 512))
+        rec[2] += 512
+    # phase 3: free a quarter of the pool from the LRU front, compact
+    freed = np.zeros(N, np.int32)
+    nfreed = lib.pkv_pool_free_lru(pool, -(-N // 4), freed.ctypes.data_as(i32p), N)
+    ms_, md_ = np.zeros(N, np.int32), np.zeros(N, np.int32)
+    t_host = time.perf_counter()
+    moves = lib.pkv_pool_compact(pool, ms_.ctypes.data_as(i32p), md_.ctypes.data_as(i32p), N)
+    t_host = time.perf_counter() - t_host
+    if moves:
+        copy_pages(ms_[:moves].copy(), md_[:moves].copy(), "compaction_copy")
+    upload_tables()
+    # verification: every live sequence read back through its table, three layers
+    ok = True
+    for h, segs, n, _ in live:
+        slot = lib.pkv_pool_seq_slot(pool, h)
+        idx = torch.arange(n, dtype=torch.int32, device=dev)
+        vis = torch.tensor([n], dtype=torch.int32, device=dev)
+        got = torch.empty(n, W, dtype=torch.int16, device=dev)
+        for l in (0, L // 2, L - 1):
+            capi.check(lib.pkv_gather_rows(rows_pool[l].data_ptr(), d_tables.data_ptr() + slot * pps * 4, RPP, W, W,
+                                           idx.data_ptr(), vis.data_ptr(), 1, n, got.data_ptr(), sp))
+            want = torch.cat([pattern(wr, a, b - a, l) for wr, a, b in segs if b > a])
+            ok &= bool(torch.equal(got, want))
+    st = C.c_int(0)
+    capi.check(lib.pkv_device_status(C.byref(st)))
+    ok &= st.value == 0
+    ops = {k: {"ms": round(v[0], 3), "GB": round(v[1] / 1e9, 3), "GBps": round(v[1] / max(v[0], 1e-9) / 1e6, 1)} for k, v in timers.items()}
+    comp = timers.get("compaction_copy", [1.0, 0])
+    _emit("page_compaction", comp[1] / (comp[0] * 1e-3) / 1e9, comp[0], {
+        "config": {"workload": f"prefix churn: {N}-page pool, 43 layers (rows + MXFP4), 64 prefixes {lo}..{hi}, 8 forks + COW, 512-row appends, free 25 % LRU, compact"},
+        "operations": ops, "pages_freed_lru": int(nfreed), "compaction_moves": int(moves), "cow_pages": int(cow_pairs),
+        "compaction_host_ms": round(t_host * 1e3, 3), "bit_exact_check": {"ok": bool(ok), "what": "all 16 live sequences read back through their block tables after compaction, 3 layers"}})
+    lib.pkv_pool_destroy(pool)
+
+
+def run_sharded(args):
+    """Configuration 5: the pool sharded over the GPUs of one box by request ownership. 64 requests with log-uniform
+    lengths (redrawn until their sum fits ONE GPU's pools, so the same workload runs at every GPU count), 43 layers of
+    bf16 rows, owner = request mod G. A step = per layer one appended row and one 2048-row gather for every local
+    request (one library call per layer). After the timed steps one migration event moves 6 requests to another GPU:
+    the destination pulls the pages of all 43 layers from the source's pool through a CUDA IPC mapping. Strong scaling:
+    the total work per step is the same at every G."""
+    import torch
+    import torch.distributed as dist
+
+    from unholy_b200 import capi, shard
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl" if world > 1 else "gloo", rank=rank, world_size=world,
+                            **({"device_id": torch.device("cuda", local)} if world > 1 else {}))
+    lib = capi.lib()
+    dev = torch.device("cuda", local)
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    i32p = C.POINTER(C.c_int32)
+    L, NREQ = LAYERS, 64
+    budget_tokens = 160_000 if args.small else 2_800_000
+    lo, hi = (512, 16384) if args.small else (2048, 1 << 20)
+    rng = np.random.Generator(np.random.MT19937(5))
+    # Log-uniform lengths; 64 such draws sum to ~10M tokens, which no single GPU holds, so the draw is scaled down to the
+    # token budget of one GPU (the shape of the distribution is kept, the longest request shrinks with the rest).
+    lengths0 = np.exp(rng.uniform(np.log(lo), np.log(hi), size=NREQ))
+    room = budget_tokens - NREQ * 256
+    if lengths0.sum() > room:
+        lengths0 = lengths0 * (room / lengths0.sum())
+    lengths0 = np.maximum(lengths0.astype(np.int64), 64)
+    steps = args.steps
+    N = int(-(-(budget_tokens + NREQ * RPP) // RPP))          # pages per GPU: room for every request (G = 1 holds all)
+    pps = int(-(-(lengths0.max() + steps + args.warmup + 64) // RPP)) + 1
+    slots = NREQ
+    pool = lib.pkv_pool_create(N, RPP, slots, pps, 0)
+    raw = []
+    for _ in range(L):
+        ptr = C.c_void_p()
+        capi.check(lib.pkv_device_alloc(C.byref(ptr), N * PAGE_BYTES))
+        raw.append(ptr.value)
+    peers = shard.PeerPools(dist, rank, world, raw)
+    transport = shard.DevicePull(torch, peers, [PAGE_BYTES] * L, N)
+    cols = torch.arange(W, device=dev, dtype=torch.int64) * 31
+    CH = 4096
+    stage = torch.empty(CH, W, dtype=torch.int16, device=dev)
+    d_tables = torch.zeros(slots * pps, dtype=torch.int32, device=dev)
+
+    def pattern(writer, s0, n, layer):
+        v = (writer * 40503 + (torch.arange(s0, s0 + n, device=dev, dtype=torch.int64) * 9973)[:, None] + layer * 613 + cols[None, :])
+        return (v & 0x7FFF).to(torch.int16)
+
+    pinned = [torch.empty(slots * pps, dtype=torch.int32).pin_memory() for _ in range(2)]
+    pin_done = [torch.cuda.Event(), torch.cuda.Event()]
+    pin_turn = [0]
+
+    def upload_tables():
+        """set_block_tables (src/engine/engine.cpp:745-748): the whole table, through pinned staging, on the stream."""
+        i = pin_turn[0] = pin_turn[0] ^ 1
+        pin_done[i].synchronize()
+        t = np.ctypeslib.as_array(lib.pkv_pool_tables(pool), shape=(slots * pps,))
+        pinned[i].numpy()[:] = t
+        d_tables.copy_(pinned[i], non_blocking=True)
+        pin_done[i].record()
+
+    seqs, lengths = {}, {}
+    for r in range(NREQ):                                    # owners write their requests (a prefill through the library)
+        if shard.owner(r, world) != rank:
+            continue
+        h = lib.pkv_pool_seq_open(pool)
+        n = int(lengths0[r])
+        assert lib.pkv_pool_assign_slot(pool, h) >= 0 and lib.pkv_pool_alloc(pool, h, n) == 1
+        seqs[r], lengths[r] = h, n
+    upload_tables()
+    for r, h in seqs.items():
+        slot = lib.pkv_pool_seq_slot(pool, h)
+        for l in range(L):
+            for s0 in range(0, lengths[r], CH):
+                n = min(CH, lengths[r] - s0)
+                stage[:n] = pattern(r, s0, n, l)
+                capi.check(lib.pkv_store_rows(stage.data_ptr(), n, W, raw[l], d_tables.data_ptr() + slot * pps * 4, RPP, W, s0, sp))
+    torch.cuda.synchronize()
+    qcap = NREQ if world == 1 else NREQ // world + 16
+    out = torch.empty(L, qcap, K_SEL, W, dtype=torch.int16, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(50 + rank)
+    idx_of = {}                                              # request -> [L][2048] sorted distinct positions below its length
+
+    def make_idx(r):
+        n = lengths[r]
+        t = torch.empty(L, K_SEL, dtype=torch.int32, device=dev)
+        for l in range(L):
+            t[l] = torch.randperm(n, generator=g, device=dev)[:K_SEL].sort().values.to(torch.int32) if n >= K_SEL else \
+                torch.cat([torch.arange(n, device=dev), torch.full((K_SEL - n,), -1, device=dev)]).to(torch.int32)
+        return t
+
+    for r in seqs:
+        idx_of[r] = make_idx(r)
+    step = capi.PkvStep()
+    step.width = step.row_stride = W
+    step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
+    step.k = K_SEL
+    step.tables = d_tables.data_ptr()
+    layers = (capi.PkvLayer * L)()
+    lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(L)]
+    flags = capi.PKV_DO_ROWS | capi.PKV_DO_GATHER | (capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0)
+    keep = {}
+
+    def prepare():
+        """Device-side descriptors of the local request set (rebuilt after a migration)."""
+        order = sorted(seqs)
+        Q = len(order)
+        keep["order"] = order
+        keep["idx"] = torch.stack([idx_of[r] for r in order], dim=1).contiguous() if Q else torch.empty(L, 0, K_SEL, dtype=torch.int32, device=dev)
+        keep["rows"] = torch.stack([torch.stack([pattern(r, 0, 1, l)[0] for r in order]) for l in range(L)]) if Q else None
+        keep["q_chunk"] = torch.arange(Q, dtype=torch.int32, device=dev)
+        step.nchunks = step.T = step.Q = Q
+        step.q_chunk = keep["q_chunk"].data_ptr()
+        for l in range(L):
+            y = layers[l]
+            y.row_pool, y.gathered = raw[l], out[l].data_ptr()
+            y.idx = keep["idx"][l].data_ptr()
+            y.rows = keep["rows"][l].data_ptr() if Q else None
+
+    def one_step():
+        order = keep["order"]
+        for r in order:                                     # positions advance: a new page now and then
+            assert lib.pkv_pool_alloc(pool, seqs[r], lengths[r] + 1) == 1
+        if lib.pkv_pool_dirty(pool):
+            upload_tables()
+        ch = torch.tensor([[lib.pkv_pool_seq_slot(pool, seqs[r]), lengths[r], 1, i] for i, r in enumerate(order)],
+                          dtype=torch.int32).pin_memory()
+        keep["chunks"] = ch.to(dev, non_blocking=True)
+        keep["vis"] = (keep["chunks"][:, 1] + 1).contiguous()
+        step.chunks, step.q_visible = keep["chunks"].data_ptr(), keep["vis"].data_ptr()
+        if order:
+            for l in range(L):
+                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, flags, sp))
+        for r in order:
+            lengths[r] += 1
+
+    prepare()
+    for _ in range(max(3, args.warmup)):
+        one_step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    step_bytes = L * NREQ * (2 * ROW_BYTES + K_SEL * 2 * ROW_BYTES)    # summed over all GPUs, independent of G
+    # one migration event: 6 requests (seeded choice), dst = (owner + 1 + U) mod G
+    mig = {"GB": 0.0, "ms": 0.0}
+    if world > 1:
+        mrng = np.random.Generator(np.random.MT19937(55))
+        movers = mrng.choice(NREQ, size=6, replace=False)
+        plan = {int(r): int((shard.owner(int(r), world) + 1 + mrng.integers(0, world - 1)) % world) for r in movers}
+        outgoing = [(r, d) for r, d in plan.items() if r in seqs and d != rank]
+        moved_len = {r: lengths[r] for r, _ in outgoing}
+        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        m0.record()
+        arrived = shard.migrate(dist, rank, world, pool, seqs, lengths, outgoing, transport, sp, torch.cuda.synchronize)
+        m1.record()
+        torch.cuda.synchronize()
+        mt = torch.tensor([m0.elapsed_time(m1), float(transport.bytes_pulled)], dtype=torch.float64, device=dev)
+        mx = mt.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(mt, op=dist.ReduceOp.SUM)
+        mig = {"GB": round(float(mt[1]) / 1e9, 3), "ms": round(float(mx[0]), 3),
+               "GBps_aggregate": round(float(mt[1]) / max(float(mx[0]), 1e-9) / 1e6, 1),
+               "note": "event time includes the host handshake (object all-gather, barrier) around the pull kernels"}
+        upload_tables()
+        for r, h, n in arrived:
+            idx_of[r] = make_idx(r)
+        for r, _ in outgoing:
+            idx_of.pop(r, None)
+        prepare()
+        one_step()                                           # the migrated requests keep decoding on their new owner
+    # verification: every local request read back through its table (2 layers) equals the pattern its writers left
+    ok = True
+    upload_tables()
+    for r in sorted(seqs)[:6] + [x for x in seqs if world > 1 and x in plan]:
+        n = lengths[r]
+        slot = lib.pkv_pool_seq_slot(pool, seqs[r])
+        idx = torch.arange(n, dtype=torch.int32, device=dev)
+        vis = torch.tensor([n], dtype=torch.int32, device=dev)
+        got = torch.empty(n, W, dtype=torch.int16, device=dev)
+        for l in (0, L - 1):
+            capi.check(lib.pkv_gather_rows(raw[l], d_tables.data_ptr() + slot * pps * 4, RPP, W, W, idx.data_ptr(),
+                                           vis.data_ptr(), 1, n, got.data_ptr(), sp))
+            want = pattern(r, 0, n, l)
+            n0 = int(lengths0[r])
+            want[n0:] = pattern(r, 0, 1, l)[0]               # every decode step appended the same pattern row
+            ok &= bool(torch.equal(got, want))
+    st = C.c_int(0)
+    capi.check(lib.pkv_device_status(C.byref(st)))
+    ok &= st.value == 0
+    okt = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        value = step_bytes * steps / (ms * 1e-3) / 1e9
+        peak, kind = load_peaks()
+        print(json.dumps({
+            "metric": "paged_kv_sharded_gather_append_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": steps, "ms_per_step": round(ms / steps, 4), "scaling": "strong", "higher_is_better": True, "data": "synthetic",
+            "per_gpu_GBps": round(value / world, 1), "pct_of_8TBps_per_gpu": round(value / world / 80, 2),
+            "pct_of_measured_peak_per_gpu": round(value / world / peak * 100, 2),
+            "config": {"workload": f"sharded pool: 64 requests, lengths log-uniform {lo}..{hi} scaled to fit one GPU (sum {int(lengths0.sum())} tokens, longest {int(lengths0.max())}), 43 layers bf16 rows, owner = request mod G, append + top-2048 gather per request and layer",
+                       "pages_per_gpu": N, "step_GB_total": round(step_bytes / 1e9, 3)},
+            "migration": mig, "bit_exact_check": {"ok": bool(int(okt[0]))}}), flush=True)
+    dist.barrier()
+    peers.close()
+    dist.barrier()
+    for ptr in raw:
+        lib.pkv_device_free(C.c_void_p(ptr))
+    lib.pkv_pool_destroy(pool)
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
+    elif args.workload == "churn":
+        run_churn(args)
+    elif args.workload == "sharded":
+        run_sharded(args)
     else:
         run_ours(args)
 

@@ -85,6 +85,7 @@ struct Tuning {
   int pdl = env_int("PKV_PDL", 1);                       // programmatic dependent launch of the bulk kernel
   int vec_ctas_per_sm = env_int("PKV_VEC_CTAS_PER_SM", 5);
   int prefetch = env_int("PKV_BULK_PREFETCH", 0);        // resolve index entries one tile ahead of the copies
+  int fuse_limit = env_int("PKV_FUSE_LIMIT", 148);       // append tiles (2 rows each) the bulk launch may carry itself
 };
 Tuning& tuning() {
   static Tuning t;
@@ -728,40 +729,32 @@ struct PageCopyParams {
   const int32_t* dst_ids;
   pkv_pool_desc pools[128];
 };
-constexpr int kPieceVecs = 1024;  // 16 KB
+constexpr int kPieceVecs = 1536;  // 24 KB = a third of a 73,728-byte row page; six 16-byte vectors per thread
+// grid.y = pool; the CTAs of a pool stride over its (pair, piece) items.
 __global__ void __launch_bounds__(256) copy_pages_kernel(const __grid_constant__ PageCopyParams P) {
-  long long pieces_total = 0;
-  // Pools may differ in page size: enumerate (pool, pair, piece) with per-pool piece counts.
-  for (int p = 0; p < P.npools; ++p)
-    pieces_total += (long long)P.n * ((P.pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
-  for (long long w = blockIdx.x; w < pieces_total; w += gridDim.x) {
-    long long rest = w;
-    int p = 0;
-    long long per_page = 0;
-    for (; p < P.npools; ++p) {
-      per_page = (long long)((P.pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
-      if (rest < per_page * P.n) break;
-      rest -= per_page * P.n;
-    }
-    const int pair = int(rest / per_page), piece = int(rest - (long long)pair * per_page);
+  const pkv_pool_desc d = P.pools[blockIdx.y];
+  const unsigned vecs = unsigned(d.page_bytes / 16);
+  const unsigned per_page = (vecs + kPieceVecs - 1) / kPieceVecs;
+  const unsigned items = unsigned(P.n) * per_page;
+  for (unsigned w = blockIdx.x; w < items; w += gridDim.x) {
+    const unsigned pair = w / per_page, piece = w - pair * per_page;
     const int sp = __ldg(&P.src_ids[pair]), dp = __ldg(&P.dst_ids[pair]);
     if (sp < 0 || dp < 0 || (P.num_src_pages > 0 && sp >= P.num_src_pages) || (P.num_dst_pages > 0 && dp >= P.num_dst_pages)) {
-      if (threadIdx.x == 0) report(1, pair);
+      if (threadIdx.x == 0) report(1, int(pair));
       continue;
     }
-    const size_t vecs = size_t(P.pools[p].page_bytes / 16);
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.pools[p].src_base) + size_t(sp) * P.pools[p].page_bytes);
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(P.pools[p].dst_base) + size_t(dp) * P.pools[p].page_bytes);
-    const size_t lo = size_t(piece) * kPieceVecs, hi = min(vecs, lo + kPieceVecs);
-    uint4 v[4];
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(d.src_base) + size_t(sp) * d.page_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(d.dst_base) + size_t(dp) * d.page_bytes);
+    const unsigned lo = piece * kPieceVecs, hi = min(vecs, lo + kPieceVecs);
+    uint4 v[6];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const size_t u = lo + size_t(i) * 256 + threadIdx.x;
+    for (int i = 0; i < 6; ++i) {
+      const unsigned u = lo + unsigned(i) * 256u + threadIdx.x;
       if (u < hi) v[i] = ld_stream(src + u);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const size_t u = lo + size_t(i) * 256 + threadIdx.x;
+    for (int i = 0; i < 6; ++i) {
+      const unsigned u = lo + unsigned(i) * 256u + threadIdx.x;
       if (u < hi) st_stream(dst + u, v[i]);
     }
   }
@@ -797,7 +790,7 @@ int launch_bulk_impl(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   const int sms = d.ok ? d.sms : 148;
   int per_sm = ctas_per_sm > 0 ? ctas_per_sm : int((227u * 1024u) / (smem + 1024u));
   per_sm = std::max(1, std::min(per_sm, 32));
-  const long long tiles = (long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS);
+  const long long tiles = std::max((long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS), (long long)P.L * P.append_tiles);
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * per_sm)));
   const int pdl = tuning().pdl;
   cudaLaunchConfig_t cfg;
@@ -852,6 +845,7 @@ int pkv_tune(int knob, int value) {
     case 2: t.pdl = value; return PKV_OK;
     case 3: t.vec_ctas_per_sm = value > 0 ? value : 5; return PKV_OK;
     case 4: t.prefetch = value; return PKV_OK;
+    case 5: t.fuse_limit = value; return PKV_OK;
     default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
   }
 }
@@ -998,10 +992,11 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   std::memcpy(P.layers, layers, sizeof(pkv_layer) * size_t(L));
   const bool bulk = gather && (flags & PKV_VARIANT_BULK);
   // With the bulk pipeline a small append (a decode step) rides inside the gather launch, two rows per 32-thread tile.
-  const bool fuse_append = bulk && append && (long long)((s.T + 1) / 2) * L <= 148;
+  const bool fuse_append = (flags & PKV_VARIANT_BULK) && append && (long long)((s.T + 1) / 2) * L <= tuning().fuse_limit;
   if (fuse_append) {
     StepParams B = P;
     B.append_tiles = (s.T + 1) / 2;
+    if (!gather) B.s.Q = 0;
     B.tiles_per_q = 0;
     B.gather_tiles = 0;
     return dispatch_bulk(B, bulk_shape, bulk_ctas, stream);
@@ -1054,17 +1049,20 @@ int pkv_copy_pages(const pkv_pool_desc* pools, int npools, const int32_t* src_id
   P.num_dst_pages = num_dst_pages;
   P.src_ids = src_ids;
   P.dst_ids = dst_ids;
-  long long pieces = 0;
+  long long max_items = 0;
   for (int p = 0; p < npools; ++p) {
     if (!pools[p].src_base || !pools[p].dst_base || pools[p].page_bytes == 0 || pools[p].page_bytes % 16 != 0 ||
         !aligned16(pools[p].src_base) || !aligned16(pools[p].dst_base))
       return fail(PKV_ERR_ARG, "pkv_copy_pages: pool bases must be 16-byte aligned and page_bytes a multiple of 16");
+    if (pools[p].page_bytes > (1ull << 30)) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: page_bytes above 1 GiB");
     P.pools[p] = pools[p];
-    pieces += (long long)n * (long long)((pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs);
+    max_items = std::max<long long>(max_items, (long long)n * (long long)((pools[p].page_bytes / 16 + kPieceVecs - 1) / kPieceVecs));
   }
+  if (max_items > 0x7fffffffLL) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: too many pages in one call");
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(pieces, (long long)sms * 8)));
+  const long long per_pool = std::max<long long>(1, ((long long)sms * 8 + npools - 1) / npools);
+  const dim3 grid(unsigned(std::min<long long>(max_items, per_pool)), unsigned(npools));
   copy_pages_kernel<<<grid, 256, 0, stream>>>(P);
   PKV_LAUNCH_CHECK("copy_pages_kernel");
   return PKV_OK;
