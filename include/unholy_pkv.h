@@ -155,6 +155,20 @@ enum {
 PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags, pkv_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------------------------
+ * Index-list producer (the step before the gather).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* topk_bf16 / topk_bf16_batch with scratch — src/kernels/indexer.hpp:74-94, src/kernels/indexer.hip:408-560,878-902.
+ * scores device bf16 [T][ld] (n <= ld keys per row); idx device int32 [T][k]: per row the min(k, #valid) largest
+ * scores ordered (score descending, index ascending), ties at the threshold to the lowest indices, -1 padded; -inf is
+ * never selected. k <= 4096. Rows are split over several CTAs; `scratch` is device memory of at least
+ * pkv_topk_scratch_words(T, n, k) uint32 words, 8-byte aligned (the reference's topk_split_scratch_words). Its
+ * contents need not be initialised and are garbage afterwards; two calls that overlap on the GPU must not share it. */
+PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
+PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
+                          size_t scratch_words, pkv_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
  * Page moves: copy-on-write duplication, hole-filling compaction, migration between shards. The reference has no
  * such operation (it never copies page payloads: src/engine/engine.cpp:284-336 shares full pages only); the copy
  * primitive they generalise is copy_kernel (src/kernels/ref_elem.hip:269-278).

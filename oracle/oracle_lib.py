@@ -37,6 +37,7 @@ _SIGS = {
     "orc_copy_pages": (None, [_vp, _sz, _vp, _vp, _i, _i]),
     "orc_move_pages": (None, [_vp, _vp, _sz, _vp, _vp, _i, _i]),
     "orc_copy": (None, [_vp, _vp, _sz]),
+    "orc_topk_bf16": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_hardware_threads": (_i, []),
 }
 _lib = None
@@ -137,6 +138,13 @@ def copy_pages(pool, page_bytes, src, dst, threads=1):
 
 def move_pages(src_pool, dst_pool, page_bytes, src, dst, threads=1):
     lib().orc_move_pages(_p(src_pool), _p(dst_pool), page_bytes, _p(src), _p(dst), len(src), threads)
+
+
+def topk_bf16(scores, n, k, threads=1):
+    T, ld = scores.shape
+    idx = np.empty((T, k), np.int32)
+    lib().orc_topk_bf16(_p(scores), T, n, ld, k, _p(idx), threads)
+    return idx
 
 
 def hardware_threads() -> int:

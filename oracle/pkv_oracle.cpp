@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <thread>
 #include <vector>
 
@@ -328,6 +329,27 @@ void orc_move_pages(const uint8_t* src_pool, uint8_t* dst_pool, size_t page_byte
 
 // src/kernels/ref_elem.hip:269-278,358-366 (copy_kernel) — a byte copy.
 void orc_copy(void* dst, const void* src, size_t bytes) { std::memcpy(dst, src, bytes); }
+
+// src/kernels/indexer.hip:408-560 (topk_bf16; the fp32 twin is src/kernels/ref_attn.hip:143-240): per row the
+// want = min(k, #valid) largest scores, valid meaning key16(score) > key16(-inf) (indexer.hip:409,424-437); ties at the
+// threshold to the lowest indices; output ordered (score descending, index ascending), -1 padded. The contract fixes
+// every output element, so it is restated as a full sort of the valid keys.
+void orc_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, int threads) {
+  parallel_for(T, threads, [&](int t) {
+    const uint16_t* row = scores + size_t(t) * size_t(ld);
+    std::vector<uint64_t> keys;
+    keys.reserve(size_t(n));
+    for (int i = 0; i < n; ++i) {
+      const uint32_t b = row[i];
+      const uint32_t key = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);  // indexer.hip:409
+      if (key > 0x007Fu) keys.push_back((uint64_t(key) << 32) | (0xffffffffu - uint32_t(i)));
+    }
+    const size_t want = std::min(size_t(k), keys.size());
+    std::partial_sort(keys.begin(), keys.begin() + ptrdiff_t(want), keys.end(), std::greater<uint64_t>());
+    for (int j = 0; j < k; ++j)
+      idx[size_t(t) * k + j] = size_t(j) < want ? int32_t(0xffffffffu - uint32_t(keys[size_t(j)] & 0xffffffffu)) : -1;
+  });
+}
 
 int orc_hardware_threads() { return int(std::thread::hardware_concurrency()); }
 

@@ -1,0 +1,105 @@
+"""Top-k index lists (the producer of the gather's input): the CPU oracle against an independent numpy statement of
+the reference's contract, and the CUDA kernels against the oracle, bit for bit (src/kernels/indexer.hpp:74:
+"ordered (score desc, index asc); -1 padded; -inf never selected"; the reference's own check compares the fast and the
+reference index lists for equality: tools/kernel_test/indexer.hip:166-188)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import pkv_testlib as tl
+from oracle import oracle_lib as orc
+from unholy_b200 import capi
+
+NEG_INF = 0xFF80
+
+
+def scores_case(g, T, n, ld, kind):
+    s = np.full((T, ld), 0x1234, np.uint16)
+    if kind == "normal":
+        s[:, :n] = tl.normal_bf16(g, (T, n))
+    elif kind == "ties":            # few distinct values: the threshold is always a tie
+        s[:, :n] = orc.f32_to_bf16_bits(g.integers(-3, 4, size=(T, n)).astype(np.float32) * np.float32(0.5))
+    elif kind == "masked":          # most keys invisible (-inf), as for early queries of a chunk
+        s[:, :n] = tl.normal_bf16(g, (T, n))
+        for t in range(T):
+            s[t, int(g.integers(0, n)):n] = NEG_INF
+        s[0, :n] = NEG_INF           # a row with nothing to select
+    elif kind == "special":         # +-0, +-inf, NaN patterns of both signs, subnormals, all bit patterns
+        s[:, :n] = g.integers(0, 65536, size=(T, n)).astype(np.uint16)
+    return s
+
+
+def numpy_topk(scores, n, k):
+    T = scores.shape[0]
+    out = np.full((T, k), -1, np.int32)
+    for t in range(T):
+        b = scores[t, :n].astype(np.uint32)
+        key = np.where(b & 0x8000, ~b & 0xFFFF, b | 0x8000)
+        valid = np.flatnonzero(key > 0x7F)
+        order = valid[np.lexsort((valid, -key[valid].astype(np.int64)))]
+        want = min(k, len(order))
+        out[t, :want] = order[:want]
+    return out
+
+
+@pytest.mark.parametrize("kind", ["normal", "ties", "masked", "special"])
+def test_oracle_topk_matches_contract(kind):
+    g = tl.rng(70)
+    for T, n, ld, k in ((5, 3000, 3008, 512), (3, 100, 100, 512), (2, 20000, 20000, 2048), (1, 1, 8, 4)):
+        s = scores_case(g, T, n, ld, kind)
+        assert np.array_equal(orc.topk_bf16(s, n, k), numpy_topk(s, n, k)), (kind, T, n, k)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["normal", "ties", "masked", "special"])
+@pytest.mark.parametrize("T,n,ld,k", [(37, 5000, 5000, 512), (64, 131072, 131072, 2048), (3, 8192, 8200, 2048),
+                                      (4, 8193, 8193, 100), (2, 300, 304, 2048), (1, 1, 8, 1), (5, 40000, 40000, 2051)])
+def test_topk_bf16_gpu(pkv, cuda, kind, T, n, ld, k):
+    g = tl.rng(71)
+    s = scores_case(g, T, n, ld, kind)
+    want = orc.topk_bf16(s, n, k, threads=8)
+    d_s = tl.dev(cuda, s)
+    words = pkv.pkv_topk_scratch_words(T, n, k)
+    d_scratch = cuda.full((words * 4,), 0x5A, dtype=cuda.uint8, device="cuda")   # poison: nothing relies on zeroes
+    d_idx = cuda.full((T * k * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+    for _ in range(2):   # the second call reuses dirty scratch
+        capi.check(pkv.pkv_topk_bf16(d_s.data_ptr(), T, n, ld, k, d_idx.data_ptr(), d_scratch.data_ptr(), words,
+                                     tl.stream_ptr(cuda)))
+        cuda.cuda.synchronize()
+        assert np.array_equal(tl.host(d_idx, np.int32, (T, k)), want)
+
+
+@pytest.mark.gpu
+def test_topk_feeds_the_gather(pkv, cuda):
+    """Producer and consumer together: index lists from pkv_topk_bf16 drive pkv_gather_rows; the result equals the
+    oracle's gather of the oracle's top-k."""
+    g = tl.rng(72)
+    rpp, pages, W, T, k = 64, 64, 576, 6, 512
+    n = pages * rpp
+    table = g.permutation(pages).astype(np.int32)
+    pool = tl.normal_bf16(g, (n, W))
+    s = scores_case(g, T, n, n, "masked")
+    vis = np.full(T, n, np.int32)
+    idx = orc.topk_bf16(s, n, k)
+    want = orc.gather_rows(pool, table.reshape(1, -1), rpp, W, W, idx, np.zeros(T, np.int32), vis)
+    d_s, d_pool, d_table, d_vis = tl.dev(cuda, s), tl.dev(cuda, pool), tl.dev(cuda, table), tl.dev(cuda, vis)
+    words = pkv.pkv_topk_scratch_words(T, n, k)
+    d_scratch = cuda.empty(words * 4, dtype=cuda.uint8, device="cuda")
+    d_idx = cuda.empty(T * k * 4, dtype=cuda.uint8, device="cuda")
+    d_out = cuda.full((T * k * W * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    st = tl.stream_ptr(cuda)
+    capi.check(pkv.pkv_topk_bf16(d_s.data_ptr(), T, n, n, k, d_idx.data_ptr(), d_scratch.data_ptr(), words, st))
+    capi.check(pkv.pkv_gather_rows(d_pool.data_ptr(), d_table.data_ptr(), rpp, W, W, d_idx.data_ptr(), d_vis.data_ptr(), T, k,
+                                   d_out.data_ptr(), st))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
+
+
+def test_topk_argument_errors(pkv):
+    assert pkv.pkv_topk_scratch_words(64, 131072, 2048) == 64 * 16 * 512 + 64 * 2048 * 2
+    assert pkv.pkv_topk_bf16(None, 0, 10, 10, 4, None, None, 0, None) == capi.PKV_OK
+    assert pkv.pkv_topk_bf16(16, 1, 10, 10, 5000, 16, 16, 1 << 20, None) == capi.PKV_ERR_LIMIT
+    assert pkv.pkv_topk_bf16(16, 1, 10, 4, 4, 16, 16, 1 << 20, None) == capi.PKV_ERR_ARG
+    assert pkv.pkv_topk_bf16(16, 1, 10, 10, 4, 16, None, 0, None) == capi.PKV_ERR_ARG
+    assert b"scratch" in pkv.pkv_last_error()

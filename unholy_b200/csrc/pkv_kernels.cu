@@ -27,9 +27,12 @@
 #include "../../include/unholy_pkv.h"
 #include "pkv_numeric.cuh"
 
+// The calling thread's last error message (shared by every translation unit of the library).
+thread_local std::string pkv_g_err;
+
 namespace {
 
-thread_local std::string g_err;
+std::string& g_err = pkv_g_err;
 
 int fail(int code, const std::string& msg) {
   g_err = msg;
