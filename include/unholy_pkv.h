@@ -168,6 +168,21 @@ PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
 PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                           size_t scratch_words, pkv_stream_t stream);
 
+/* pkv_topk_bf16 for callers that cannot hand the library any device memory of their own and cannot let it allocate
+ * either — an engine thread that is recording its step into a CUDA graph (cudaMalloc is illegal while a stream is
+ * capturing), a latency-critical decode loop (cudaMalloc/cudaFree synchronise the whole device), or a plugin host that
+ * owns every allocation and hands none to plugins. This entry point has no counterpart in the reference. It takes
+ * only inputs and outputs; the scratch is a 4 MiB array compiled into the library (pkv_topk_static_scratch_words()
+ * uint32 words = 1,048,576), which every GPU that loads the library keeps until the process exits. It calls no
+ * cudaMalloc, cudaFree or other allocating routine. Shapes whose pkv_topk_scratch_words(T, n, k) exceeds the built-in
+ * size are refused with PKV_ERR_LIMIT (64 rows x 131,072 keys x k = 2048 needs 786,432 words and fits). The first
+ * call on each device looks the array's device address up (cudaGetSymbolAddress), so make that first call outside any
+ * stream capture. Every call on a device shares the one array: it keeps the previous call's contents (harmless: each
+ * call overwrites what it reads), and two calls that overlap on the GPU (different streams) race — serialise them.
+ * Results are identical to pkv_topk_bf16's. */
+PKV_API size_t pkv_topk_static_scratch_words(void);
+PKV_API int pkv_topk_bf16_static(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Page moves: copy-on-write duplication, hole-filling compaction, migration between shards. The reference has no
  * such operation (it never copies page payloads: src/engine/engine.cpp:284-336 shares full pages only); the copy

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <mutex>
 #include <string>
 
 #include "../../include/unholy_pkv.h"
@@ -241,6 +242,40 @@ __global__ void __launch_bounds__(kThreads) sort_kernel(const uint32_t* __restri
 
 extern thread_local std::string pkv_g_err;  // defined in pkv_kernels.cu: what pkv_last_error() returns
 
+// Scratch for pkv_topk_bf16_static: 4 MiB that every GPU which loads the library holds until the process exits.
+// In host code this name is only a handle for the runtime (not a device address): the device address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+constexpr size_t kStaticScratchWords = size_t(1) << 20;
+static __device__ __align__(256) uint32_t g_topk_static_scratch[kStaticScratchWords];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint32_t* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+// The device address of the static scratch on the CURRENT device; looked up on the first call per device.
+int static_scratch(uint32_t** out, std::string& err) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    err = std::string("pkv_topk_bf16_static: cudaGetDevice: ") + cudaGetErrorString(e);
+    return PKV_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_topk_static_scratch);
+    if (e != cudaSuccess || !p) {
+      err = std::string("pkv_topk_bf16_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
+      return PKV_ERR_CUDA;
+    }
+    g_static_ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return PKV_OK;
+}
+}  // namespace
+
 extern "C" {
 
 size_t pkv_topk_scratch_words(int T, int n, int k) {
@@ -294,6 +329,22 @@ int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int
     pkv_g_err = "pkv_topk_bf16: scratch must be 8-byte aligned and hold pkv_topk_scratch_words(T, n, k) words";
     return PKV_ERR_ARG;
   }
+  return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
+}
+
+size_t pkv_topk_static_scratch_words(void) { return kStaticScratchWords; }
+
+int pkv_topk_bf16_static(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream) {
+  if (const int rc = pkv_topk_check(scores, T, n, ld, k, idx, pkv_g_err)) return rc;
+  if (T == 0) return PKV_OK;
+  const size_t need = pkv_topk::layout(T, n > 0 ? n : 1, k).total_words;
+  if (need > kStaticScratchWords) {
+    pkv_g_err = "pkv_topk_bf16_static: this shape needs " + std::to_string(need) + " scratch words, the built-in scratch holds " +
+                std::to_string(kStaticScratchWords) + " (use pkv_topk_bf16 with your own scratch)";
+    return PKV_ERR_LIMIT;
+  }
+  uint32_t* scratch = nullptr;
+  if (const int rc = static_scratch(&scratch, pkv_g_err)) return rc;
   return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
 }
 
