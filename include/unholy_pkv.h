@@ -179,7 +179,7 @@ PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, in
  * call on each device looks the array's device address up (cudaGetSymbolAddress), so make that first call outside any
  * stream capture. Every call on a device shares the one array: it keeps the previous call's contents (harmless: each
  * call overwrites what it reads), and two calls that overlap on the GPU (different streams) race — serialise them.
- * Results are identical to pkv_topk_bf16's. */
+ * Results are identical to pkv_topk_bf16's. Nothing is stated here about recording this call itself into a graph. */
 PKV_API size_t pkv_topk_static_scratch_words(void);
 PKV_API int pkv_topk_bf16_static(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream);
 
