@@ -681,13 +681,12 @@ __global__ void __launch_bounds__(256) store_rows_fp8_kernel(const uint16_t* __r
 }
 
 // The gather for one sequence (one block-table row), the shape of one reference attention call.
-__global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t* __restrict__ pool, OneTable tb, int max_pages,
-                                                                int num_rows_limit, int row_stride, int width,
+__global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t* __restrict__ pool, OneTable tb,
+                                                                int row_stride, int width,
                                                                 const int32_t* __restrict__ idx,
                                                                 const int32_t* __restrict__ q_visible, int T, int k,
                                                                 uint16_t* __restrict__ out) {
   __shared__ const uint4* s_src[kGatherRows];
-  (void)max_pages, (void)num_rows_limit;
   const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows;
   const long long total = (long long)T * tiles_per_q;
   for (long long w = blockIdx.x; w < total; w += gridDim.x) {
@@ -1033,7 +1032,7 @@ int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows_per_pag
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 5)));
-  gather_one_kernel<<<grid, kVecThreads, 0, stream>>>(pool, OneTable{table, rows_per_page}, 0, 0, row_stride, width, idx,
+  gather_one_kernel<<<grid, kVecThreads, 0, stream>>>(pool, OneTable{table, rows_per_page}, row_stride, width, idx,
                                                       q_visible, T, k, out);
   PKV_LAUNCH_CHECK("gather_one_kernel");
   return PKV_OK;
