@@ -194,8 +194,7 @@ class Workload:
         self.groups = [(l, min(self.lpl, LAYERS - l)) for l in range(0, LAYERS, self.lpl)]
         self.group_ptrs = [C.cast(C.byref(self.layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer))
                            for l, _ in self.groups]
-        fused = self.variant and (NSEQ + 1) // 2 * self.lpl <= 148   # the decode append rides in the gather launch
-        self.kernels_per_call = 2 if (self.variant and not fused) else 1
+        self.kernels_per_call = 1   # appends and the gather are tiles of one launch (both gather variants)
         # Layers that share a resident pool and run in ONE launch write the same appended row in no defined order.
         self.unordered_alias = self.lpl > self.resident or (self.lpl > 1 and self.resident < LAYERS)
         self.step_ref = C.byref(self.step)
@@ -437,7 +436,7 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and wl.lpl == 1) else None,
                          "traffic_source": "profiles/gather_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
                          "peak_kind": "of " + peak_kind,
-                         "kernel": "gather_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
+                         "kernel": "step_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
                          "algorithmic_bytes_per_launch": int(call_bytes)},
             "gpu_launches": launches, "clocks": clocks,
         }
@@ -530,13 +529,19 @@ def run_prefill(args):
     sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(LAYERS)]
 
+    chunk_ptr = [chunks[c].data_ptr() for c in range(nchunks)]
+    vis_ptr = [q_vis[c].data_ptr() for c in range(nchunks)]
+    idx_ptr = [idx[c].data_ptr() for c in range(nchunks)]
+    run, step_ref = lib.pkv_step_run, C.byref(step)
+
     def run_all():
         for c in range(nchunks):
-            step.chunks = chunks[c].data_ptr()
-            step.q_visible = q_vis[c].data_ptr()
+            step.chunks, step.q_visible = chunk_ptr[c], vis_ptr[c]
+            ip = idx_ptr[c]
             for l in range(LAYERS):
-                layers[l].idx = idx[c].data_ptr()
-                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, flags, sp))
+                layers[l].idx = ip
+                if run(step_ref, lptr[l], 1, flags, sp):
+                    capi.check(1)
 
     run_all()  # warm-up pass (also the pass that is verified)
     torch.cuda.synchronize()

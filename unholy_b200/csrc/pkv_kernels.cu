@@ -83,12 +83,13 @@ int env_int(const char* name, int dflt) {
   return v && *v ? std::atoi(v) : dflt;
 }
 struct Tuning {
-  int bulk_shape = env_int("PKV_BULK_SHAPE", 308);       // STAGES * 100 + ROWS of the bulk gather pipeline
+  int bulk_shape = env_int("PKV_BULK_SHAPE", 0);         // STAGES * 100 + ROWS of the bulk pipeline; 0: by launch size
   int bulk_ctas_per_sm = env_int("PKV_BULK_CTAS_PER_SM", 0);  // 0: as many as shared memory allows
   int pdl = env_int("PKV_PDL", 1);                       // programmatic dependent launch of the bulk kernel
   int vec_ctas_per_sm = env_int("PKV_VEC_CTAS_PER_SM", 5);
-  int prefetch = env_int("PKV_BULK_PREFETCH", 0);        // resolve index entries one tile ahead of the copies
-  int fuse_limit = env_int("PKV_FUSE_LIMIT", 148);       // append tiles (2 rows each) the bulk launch may carry itself
+  int fuse = env_int("PKV_BULK_FUSE", 1);                // the bulk launch carries the step's appends itself
+  int batch = env_int("PKV_BULK_BATCH", -1);             // tiles resolved together (0: a full warp's worth; -1: by launch size)
+  int resolve_late = env_int("PKV_BULK_RESOLVE_LATE", 0);
 };
 Tuning& tuning() {
   static Tuning t;
@@ -191,6 +192,10 @@ struct StepParams {
   int L;
   int flags;
   int append_tiles;  // per layer
+  int key_tiles;     // per layer (bulk kernel only)
+  int tpq_shift;     // log2(gather tiles per query) when that is a power of two, else -1 (bulk kernel only)
+  int rpp_shift;     // log2(rows_per_page) when that is a power of two, else -1
+  int resolve_late;  // resolve the next batch when the LAST tile of the current one is issued (else the first)
   int gather_tiles;  // per layer
   int tiles_per_q;
   pkv_layer layers[PKV_MAX_LAYERS];
@@ -215,7 +220,7 @@ __device__ __forceinline__ int find_chunk(const pkv_chunk* __restrict__ chunks, 
 
 // Physical row id of logical row `lr` of `slot`, or -1 (recorded) when the table entry is unusable.
 __device__ __forceinline__ long long physical_row(const pkv_step& s, int slot, int lr, int tag) {
-  const int pg = lr / s.rows_per_page;
+  const int pg = (s.rows_per_page & (s.rows_per_page - 1)) == 0 ? lr >> (31 - __clz(s.rows_per_page)) : lr / s.rows_per_page;
   if (lr < 0 || pg >= s.max_pages_per_seq) {
     report(2, tag);
     return -1;
@@ -325,9 +330,12 @@ __device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_firs
 __device__ __forceinline__ const uint4* gather_source(const StepParams& P, const pkv_layer& ly, int q, int e) {
   const pkv_step& s = P.s;
   if (e >= s.k) return nullptr;
+  // Three loads that depend on nothing are issued together; the chunk and the block-table entry follow.
   const int row = __ldg(&ly.idx[size_t(q) * s.k + e]);
-  if (row < 0 || row >= __ldg(&s.q_visible[q])) return nullptr;
-  const pkv_chunk ch = s.chunks[__ldg(&s.q_chunk[q])];
+  const int vis = __ldg(&s.q_visible[q]);
+  const int qc = __ldg(&s.q_chunk[q]);
+  const pkv_chunk ch = s.chunks[qc];
+  if (row < 0 || row >= vis) return nullptr;
   if ((P.flags & PKV_DO_ROWS) && ly.rows && row >= ch.s0 && row < ch.s0 + ch.n)
     return reinterpret_cast<const uint4*>(ly.rows + size_t(ch.t0 + (row - ch.s0)) * s.width);
   const long long rid = physical_row(s, ch.slot, row, q);
@@ -435,18 +443,82 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return false;
 }
 
-template <int STAGES, int ROWS, bool PREFETCH>
-__global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__ StepParams P) {
-  static_assert(ROWS <= 32 && STAGES >= 3, "one lane per row; two stages drain while the others fill");
+// Key quantisation of one staged tile: rows of 128 bf16 keys already in shared memory (key_bytes apart), 16 lanes
+// per row, two rows per pass of the warp. Same arithmetic and stores as append_tile.
+template <int ROWS>
+__device__ __forceinline__ void quantise_staged_keys(const StepParams& P, const pkv_layer& ly, const unsigned char* stage,
+                                                     const long long* rids, int nrows, bool fp4, bool fp8) {
+  const pkv_step& s = P.s;
+  const int lane = threadIdx.x, j = lane & 15;
+#pragma unroll 1
+  for (int r0 = 0; r0 < ROWS; r0 += 2) {
+    if (r0 >= nrows) break;
+    const int r = r0 + (lane >> 4);
+    const long long rid = r < nrows ? rids[r] : -1;
+    float v[8];
+    pkv::unpack8(*reinterpret_cast<const uint4*>(stage + size_t(r < ROWS ? r : 0) * (PKV_FP4_ROW_DIM * 2) + j * 16), v);
+    const float a8 = pkv::absmax8(v);
+    if (fp4) {
+      const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
+      const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
+      const int base = lane & 16;
+      const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
+                     s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
+      if (rid >= 0) {
+        const long long page = rid / s.rows_per_page;
+        const int slot = int(rid - page * s.rows_per_page);
+        uint8_t* pg = ly.key_pool_fp4 + size_t(page) * size_t(s.rows_per_page) * 68u;
+        *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
+        if (j == 0)
+          *reinterpret_cast<uint32_t*>(pg + size_t(s.rows_per_page) * 64u + size_t(slot) * 4u) =
+              s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+      }
+    }
+    if (fp8) {
+      const int group = s.fp8_block >> 3;
+      const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(a8, group));
+      const uint2 codes = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
+      if (rid >= 0) {
+        *reinterpret_cast<uint2*>(ly.key_fp8_codes + size_t(rid) * PKV_FP4_ROW_DIM + j * 8) = codes;
+        if (j % group == 0) ly.key_fp8_scales[size_t(rid) * (PKV_FP4_ROW_DIM / s.fp8_block) + j / group] = uint8_t(se);
+      }
+    }
+  }
+}
+
+// The whole step of up to PKV_MAX_LAYERS layers as ONE stream of tiles through one bulk-copy pipeline. Per layer:
+//   key tiles    ROWS batch rows of new keys: one bulk load of the contiguous source, quantised from shared memory;
+//   append tiles ROWS batch rows of new KV rows: one bulk load of the contiguous source, then one bulk store per run of
+//                rows that are contiguous in the pool (a run ends at a page boundary or where the chunk changes);
+//   gather tiles ROWS index entries of one query: one bulk load per row, one bulk store of the contiguous tile.
+// Tiles are dealt round-robin to single-warp CTAs; each keeps STAGES tiles rotating (loads of STAGES - 2 tiles in
+// flight while up to two tiles drain).
+template <int STAGES, int ROWS, int BATCH>
+__global__ void __launch_bounds__(32) step_bulk_kernel(const __grid_constant__ StepParams P) {
+  static_assert(ROWS <= 32 && ROWS % 2 == 0 && 32 % ROWS == 0 && STAGES >= 3, "one lane per row; two stages drain while the others fill");
+  static_assert(BATCH >= 1 && BATCH * ROWS <= 32 && (BATCH & (BATCH - 1)) == 0, "a batch is resolved by one warp, one lane per row");
+  constexpr int kBatch = BATCH;  // tiles whose addresses are resolved together, one lane per row
+  enum Kind { kKeys = 0, kAppend = 1, kGather = 2 };
+  struct Tile {  // what issue and drain need to know about a tile
+    int layer, kind, a, b;  // gather: a = query, b = first entry; keys / append: a = first batch row
+  };
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long bars[STAGES];
+  __shared__ long long s_rid[STAGES][ROWS];      // pool rows of a staged key / append tile
+  __shared__ Tile s_tile[STAGES];                // the staged tiles
+  __shared__ const uint4* s_src[2][32];          // resolved batches: gather source pointers (nullptr: masked) ...
+  __shared__ long long s_bat_rid[2][32];         // ... and pool rows of key / append rows
+  __shared__ Tile s_bat_tile[2][kBatch];
   const pkv_step& s = P.s;
   const int lane = threadIdx.x;
-  const uint32_t row_bytes = uint32_t(s.width) * 2u;
+  const uint32_t row_bytes = uint32_t(s.width) * 2u, key_bytes = PKV_FP4_ROW_DIM * 2u;
   const uint32_t stage_bytes = row_bytes * ROWS;
-  const int tiles_per_q = (s.k + ROWS - 1) / ROWS;
-  const long long per_layer = (long long)s.Q * tiles_per_q;
-  const long long total = per_layer * P.L;
+  // All tile arithmetic is 32-bit and incremental: a single warp runs the whole pipeline, so every long dependent
+  // instruction sequence (a 64-bit division is about a hundred) is paid in full on the critical path.
+  const unsigned tiles_per_q = unsigned(s.k + ROWS - 1) / ROWS;
+  const unsigned key_tiles = unsigned(P.key_tiles), app_tiles = unsigned(P.append_tiles);
+  const unsigned per_layer = key_tiles + app_tiles + unsigned(s.Q) * tiles_per_q;
+  const unsigned total = per_layer * unsigned(P.L);  // the host keeps this below 2^31
   if (lane == 0) {
 #pragma unroll
     for (int i = 0; i < STAGES; ++i) mbar_init(smem_addr(&bars[i]), 1);
@@ -455,132 +527,175 @@ __global__ void __launch_bounds__(32) gather_bulk_kernel(const __grid_constant__
   __syncwarp();
   // Programmatic dependent launch: this grid may have been scheduled while the previous kernel of the stream was still
   // draining. Nothing above touches global memory; everything below waits for that kernel's writes to be visible.
-  // The next kernel of the stream may be scheduled as soon as SM resources free up (it waits the same way).
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // Fused append: the step's new rows and keys are written by the CTAs at the END of the grid, which own one gather
-  // tile fewer than the others whenever the tile count does not divide evenly. In-chunk index entries read the row
-  // from its source (gather_source), so the gather does not depend on these writes.
-  if (P.append_tiles > 0) {
-    __shared__ long long s_rid[2];
-    const long long atotal = (long long)P.append_tiles * P.L;
-    for (long long a = gridDim.x - 1 - blockIdx.x; a < atotal; a += gridDim.x) {
-      const int layer = int(a / P.append_tiles), tile = int(a - (long long)layer * P.append_tiles);
-      append_tile<32>(P, P.layers[layer], tile * 2, s_rid);
-    }
-  }
-  const long long first = blockIdx.x, stride = gridDim.x;
-  const long long mine = first < total ? (total - first + stride - 1) / stride : 0;
+  const unsigned first = blockIdx.x, stride = gridDim.x;
+  const int mine = first < total ? int((total - first + stride - 1) / stride) : 0;
+  const bool fp4 = (P.flags & PKV_DO_KEYS_FP4) != 0, fp8 = (P.flags & PKV_DO_KEYS_FP8) != 0;
 
-  // Address resolution is split in two so that its dependent loads overlap the copies: fetch(j) issues the loads that
-  // do not depend on anything (the lane's index entry, the query's visibility and chunk) one tile before issue(j)
-  // uses them for the block-table lookup and starts the row copies into stage j % STAGES.
-  struct Staged {
-    int row, vis;
-    pkv_chunk ch;
-  };
-  auto locate = [&](long long j, int& layer, int& q, int& e0) {
-    const long long w = first + j * stride;
-    layer = int(w / per_layer);
-    const long long r = w - (long long)layer * per_layer;
-    q = int(r / tiles_per_q);
-    e0 = int(r - (long long)q * tiles_per_q) * ROWS;
-  };
-  auto fetch = [&](long long j) {
-    int layer, q, e0;
-    locate(j, layer, q, e0);
-    Staged g;
-    const int e = e0 + lane;
-    g.row = (lane < ROWS && e < s.k) ? __ldg(&P.layers[layer].idx[size_t(q) * s.k + e]) : -1;
-    g.vis = __ldg(&s.q_visible[q]);
-    g.ch = s.chunks[__ldg(&s.q_chunk[q])];
-    return g;
-  };
-  auto issue = [&](long long j, const Staged& g) {
-    int layer, q, e0;
-    locate(j, layer, q, e0);
-    const pkv_layer& ly = P.layers[layer];
-    const int st = int(j % STAGES);
-    unsigned char* stage = smem + size_t(st) * stage_bytes;
-    const uint32_t bar = smem_addr(&bars[st]);
+  // Address resolution runs a batch of kBatch tiles at a time, one lane per row of each tile, so the dependent loads
+  // (index entry -> chunk -> block-table entry) cost one latency per batch instead of one per tile and overlap the
+  // copies of earlier tiles. Two batches rotate: batch b + 1 is resolved when the first tile of batch b is issued.
+  // Each lane walks its own tile sequence (this CTA's tiles sub, sub + kBatch, ...) with a (layer, offset) cursor.
+  const int sub = lane / ROWS, r_in = lane % ROWS;
+  unsigned cur_layer = 0, cur_local = 0;  // position of this lane's next tile to resolve
+  {
+    const unsigned w = first + unsigned(sub) * stride;  // one division per kernel, not per tile
+    cur_layer = w / per_layer;
+    cur_local = w - cur_layer * per_layer;
+  }
+  const unsigned adv = unsigned(kBatch) * stride;
+  auto resolve_batch = [&](int b) {
+    const int j = b * kBatch + sub;
     const uint4* src = nullptr;
-    if (g.row >= 0 && g.row < g.vis) {
-      if ((P.flags & PKV_DO_ROWS) && ly.rows && g.row >= g.ch.s0 && g.row < g.ch.s0 + g.ch.n) {
-        src = reinterpret_cast<const uint4*>(ly.rows + size_t(g.ch.t0 + (g.row - g.ch.s0)) * s.width);
+    long long rid = -1;
+    if (sub < kBatch && j < mine) {
+      const pkv_layer& ly = P.layers[cur_layer];
+      Tile t;
+      t.layer = int(cur_layer);
+      if (cur_local >= key_tiles + app_tiles) {
+        const unsigned g = cur_local - key_tiles - app_tiles;
+        const unsigned q = P.tpq_shift >= 0 ? g >> P.tpq_shift : g / tiles_per_q;
+        const unsigned e0 = (g - q * tiles_per_q) * ROWS;
+        t.kind = kGather, t.a = int(q), t.b = int(e0);
+        src = gather_source(P, ly, int(q), int(e0) + r_in);
       } else {
-        const long long rid = physical_row(s, g.ch.slot, g.row, q);
-        if (rid >= 0) src = reinterpret_cast<const uint4*>(ly.row_pool + size_t(rid) * s.row_stride);
+        const bool keys = cur_local < key_tiles;
+        const int t_first = int(keys ? cur_local : cur_local - key_tiles) * ROWS, row = t_first + r_in;
+        t.kind = keys ? kKeys : kAppend, t.a = t_first, t.b = 0;
+        if (row < s.T) {
+          const int c = find_chunk(s.chunks, s.nchunks, row);
+          if (c >= 0) {
+            const pkv_chunk ch = s.chunks[c];
+            rid = physical_row(s, ch.slot, ch.s0 + (row - ch.t0), row);
+          }
+        }
+      }
+      if (r_in == 0) s_bat_tile[b & 1][sub] = t;
+      cur_local += adv;
+      while (cur_local >= per_layer) {
+        cur_local -= per_layer;
+        ++cur_layer;
       }
     }
-    const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
-    if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(valid)) * row_bytes);
-    // Masked rows (and rows past k, which are never stored) are zero-filled by the whole warp, one row at a time.
-    unsigned masked = ~valid & (ROWS == 32 ? 0xffffffffu : ((1u << ROWS) - 1u));
-    while (masked) {
-      const int r = __ffs(masked) - 1;
-      masked &= masked - 1;
-      uint4* z = reinterpret_cast<uint4*>(stage + size_t(r) * row_bytes);
-      for (uint32_t i = lane; i < row_bytes / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
-    }
+    s_src[b & 1][lane] = src;
+    s_bat_rid[b & 1][lane] = rid;
     __syncwarp();
-    if (src) bulk_load(smem_addr(stage + size_t(lane) * row_bytes), src, row_bytes, bar);
   };
 
-  const long long ahead = STAGES - 2;
-  Staged next_g;
-  next_g.row = -1;
-  next_g.vis = 0;
-  next_g.ch = pkv_chunk{0, 0, 0, 0};
-  if (PREFETCH && mine > 0) next_g = fetch(0);
-  for (long long j = 0; j < ahead && j < mine; ++j) {
-    const Staged g = PREFETCH ? next_g : fetch(j);
-    if (PREFETCH && j + 1 < mine) next_g = fetch(j + 1);
-    issue(j, g);
+  // Starts the loads of tile j into stage st (its batch is resolved).
+  auto issue = [&](int j, int st) {
+    const int slot = (j / kBatch) & 1, sub_j = j % kBatch, off = sub_j * ROWS;
+    const Tile t = s_bat_tile[slot][sub_j];
+    const pkv_layer& ly = P.layers[t.layer];
+    unsigned char* stage = smem + size_t(st) * stage_bytes;
+    const uint32_t bar = smem_addr(&bars[st]);
+    if (lane == 0) s_tile[st] = t;
+    if (t.kind == kGather) {
+      const uint4* src = lane < ROWS ? s_src[slot][off + lane] : nullptr;
+      const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
+      if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(valid)) * row_bytes);
+      // Masked rows (and rows past k, which are never stored) are zero-filled by the whole warp, one row at a time.
+      unsigned masked = ~valid & (ROWS == 32 ? 0xffffffffu : ((1u << ROWS) - 1u));
+      while (masked) {
+        const int r = __ffs(masked) - 1;
+        masked &= masked - 1;
+        uint4* z = reinterpret_cast<uint4*>(stage + size_t(r) * row_bytes);
+        for (uint32_t i = lane; i < row_bytes / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+      if (src) bulk_load(smem_addr(stage + size_t(lane) * row_bytes), src, row_bytes, bar);
+    } else {
+      // Batch rows [t.a, t.a + nrows): lane 0 loads the contiguous source; the rows' pool ids travel with the stage.
+      const int nrows = min(ROWS, s.T - t.a);
+      if (lane == 0) {
+        const uint32_t each = t.kind == kKeys ? key_bytes : row_bytes;
+        const unsigned char* src = t.kind == kKeys ? reinterpret_cast<const unsigned char*>(ly.keys) + size_t(t.a) * key_bytes
+                                                   : reinterpret_cast<const unsigned char*>(ly.rows) + size_t(t.a) * row_bytes;
+        mbar_expect_tx(bar, uint32_t(nrows) * each);
+        bulk_load(smem_addr(stage), src, uint32_t(nrows) * each, bar);
+      }
+      if (lane < ROWS) s_rid[st][lane] = s_bat_rid[slot][off + lane];
+      __syncwarp();
+    }
+    // The first tile of a batch is on its way: resolve the batch after it while its copies fly.
+    if (sub_j == (P.resolve_late ? kBatch - 1 : 0) && (j / kBatch + 1) * kBatch < mine) resolve_batch(j / kBatch + 1);
+  };
+
+  constexpr int ahead = STAGES - 2;
+  if (mine > 0) resolve_batch(0);
+  int st_issue = 0;
+  for (int j = 0; j < ahead && j < mine; ++j) {
+    issue(j, st_issue);
+    st_issue = st_issue + 1 == STAGES ? 0 : st_issue + 1;
   }
   bool alive = true;
-  long long j_fail = 0;
-  for (long long j = 0; j < mine; ++j) {
-    // Stage (j + ahead) % STAGES was stored by tile j - 2; its store must have finished reading shared memory.
+  int j_fail = 0, st = 0;
+  uint32_t parity = 0;
+  for (int j = 0; j < mine; ++j) {
+    // The stage tile j + ahead goes into was drained by tile j - 2; its stores must have finished reading shared memory
+    // (every lane waits on its own bulk groups: append tiles are stored by several lanes).
     if (j + ahead < mine) {
-      if (lane == 0) bulk_wait_read<1>();
+      bulk_wait_read<1>();
       __syncwarp();
-      const Staged g = PREFETCH ? next_g : fetch(j + ahead);
-      if (PREFETCH && j + ahead + 1 < mine) next_g = fetch(j + ahead + 1);
-      issue(j + ahead, g);
+      issue(j + ahead, st_issue);
+      st_issue = st_issue + 1 == STAGES ? 0 : st_issue + 1;
     }
-    const int st = int(j % STAGES);
-    const uint32_t parity = uint32_t(j / STAGES) & 1u;
     alive = mbar_wait_bounded(smem_addr(&bars[st]), parity, int(blockIdx.x));
     alive = __all_sync(0xffffffffu, alive);
     if (!alive) {
       j_fail = j;
       break;
     }
-    const long long w = first + j * stride;
-    const int layer = int(w / per_layer);
-    const long long r = w - (long long)layer * per_layer;
-    const int q = int(r / tiles_per_q), e0 = int(r - (long long)q * tiles_per_q) * ROWS;
-    const int nrows = min(ROWS, s.k - e0);
-    fence_async_smem();  // the zero rows were written through the generic proxy
+    const Tile t = s_tile[st];
+    const pkv_layer& ly = P.layers[t.layer];
+    unsigned char* stage = smem + size_t(st) * stage_bytes;
+    if (t.kind == kGather) {
+      const int nrows = min(ROWS, s.k - t.b);
+      fence_async_smem();  // the zero rows were written through the generic proxy
+      __syncwarp();
+      if (lane == 0)
+        bulk_store(ly.gathered + (size_t(t.a) * s.k + t.b) * s.width, smem_addr(stage), uint32_t(nrows) * row_bytes);
+    } else {
+      const int nrows = min(ROWS, s.T - t.a);
+      if (t.kind == kKeys) {
+        quantise_staged_keys<ROWS>(P, ly, stage, s_rid[st], nrows, fp4 && ly.key_pool_fp4, fp8 && ly.key_fp8_codes && ly.key_fp8_scales);
+      } else {
+        // Runs of rows that are contiguous in the pool leave with one bulk store each.
+        const long long rid = lane < nrows ? s_rid[st][lane] : -1;
+        const long long prev = __shfl_up_sync(0xffffffffu, rid, 1);
+        const bool start = rid >= 0 && (lane == 0 || prev < 0 || rid != prev + 1 || s.row_stride != s.width);
+        const unsigned breaks = __ballot_sync(0xffffffffu, start || rid < 0);
+        if (start) {
+          const unsigned higher = lane == 31 ? 0u : (breaks & ~((2u << lane) - 1u));
+          const int next = higher ? __ffs(higher) - 1 : 32;
+          bulk_store(ly.row_pool + size_t(rid) * s.row_stride, smem_addr(stage + size_t(lane) * row_bytes),
+                     uint32_t(next - lane) * row_bytes);
+        }
+      }
+    }
+    bulk_commit();
     __syncwarp();
-    if (lane == 0) {
-      bulk_store(P.layers[layer].gathered + (size_t(q) * s.k + e0) * s.width, smem_addr(smem + size_t(st) * stage_bytes),
-                 uint32_t(nrows) * row_bytes);
-      bulk_commit();
+    if (++st == STAGES) {
+      st = 0;
+      parity ^= 1u;
     }
   }
   if (!alive) {
     // Gave up on tile j_fail: give the loads of the tiles already started a second, bounded chance to land before the
     // CTA's shared memory is released.
-    for (long long jj = j_fail; jj < mine && jj <= j_fail + ahead; ++jj) {
-      const uint32_t bar = smem_addr(&bars[int(jj % STAGES)]), parity = uint32_t(jj / STAGES) & 1u;
+    int st2 = st;
+    uint32_t par2 = parity;
+    for (int jj = j_fail; jj < mine && jj <= j_fail + ahead; ++jj) {
+      const uint32_t bar = smem_addr(&bars[st2]);
       for (int spin = 0; spin < (1 << 18); ++spin) {
-        if (mbar_try_wait(bar, parity)) break;
+        if (mbar_try_wait(bar, par2)) break;
         __nanosleep(256);
       }
+      if (++st2 == STAGES) st2 = 0, par2 ^= 1u;
     }
   }
-  if (lane == 0) bulk_wait_all();
+  bulk_wait_all();
   __syncwarp();
 }
 
@@ -776,25 +891,38 @@ int check_quant_shape(int rows, int cols, int block, const char* name) {
   return PKV_OK;
 }
 
-template <int STAGES, int ROWS, bool PREFETCH>
-int launch_bulk_impl(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
+template <int STAGES, int ROWS, int BATCH>
+int launch_bulk_b(const StepParams& P0, int ctas_per_sm, cudaStream_t st) {
+  StepParams P = P0;
+  P.resolve_late = tuning().resolve_late;
+  const bool append = P.append_tiles != 0 || P.key_tiles != 0;   // set by the caller as flags; counted in ROWS here
+  const int row_tiles = (P.s.T + ROWS - 1) / ROWS;
+  P.append_tiles = P0.append_tiles ? row_tiles : 0;
+  P.key_tiles = P0.key_tiles ? row_tiles : 0;
+  (void)append;
   const size_t smem = size_t(STAGES) * ROWS * size_t(P.s.width) * 2u;
-  if (smem > 227u * 1024u - 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
-  static thread_local bool configured[64] = {};
+  if (smem > 224u * 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
+  // Dynamic shared memory above 48 KB has to be opted into, per device and per kernel instantiation.
+  static thread_local size_t opted[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(gather_bulk_kernel<STAGES, ROWS, PREFETCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+  if (smem > 48u * 1024u && dev >= 0 && dev < 64 && opted[dev] < smem) {
+    const cudaError_t e = cudaFuncSetAttribute(step_bulk_kernel<STAGES, ROWS, BATCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
-    configured[dev] = true;
+    opted[dev] = smem;
   }
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
-  int per_sm = ctas_per_sm > 0 ? ctas_per_sm : int((227u * 1024u) / (smem + 1024u));
+  int per_sm = ctas_per_sm > 0 ? ctas_per_sm : int((227u * 1024u) / (smem + 2048u + 8u * ROWS * STAGES));
   per_sm = std::max(1, std::min(per_sm, 32));
-  const long long tiles = std::max((long long)P.L * P.s.Q * ((P.s.k + ROWS - 1) / ROWS), (long long)P.L * P.append_tiles);
+  const int tpq = (P.s.k + ROWS - 1) / ROWS;
+  P.tpq_shift = -1;
+  for (int b = 0; b < 31; ++b)
+    if (tpq == (1 << b)) P.tpq_shift = b;
+  const long long tiles = (long long)P.L * ((long long)P.s.Q * tpq + P.append_tiles + P.key_tiles);
+  if (tiles == 0) return PKV_OK;
+  if (tiles >= (1ll << 31) - (1ll << 20)) return fail(PKV_ERR_LIMIT, "pkv_step_run: more than 2^31 tiles in one launch");
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * per_sm)));
-  const int pdl = tuning().pdl;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(grid));
@@ -805,30 +933,54 @@ int launch_bulk_impl(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, gather_bulk_kernel<STAGES, ROWS, PREFETCH>, P);
-  if (le != cudaSuccess) return fail_cuda("gather_bulk_kernel launch", le);
+  cfg.numAttrs = tuning().pdl ? 1 : 0;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, step_bulk_kernel<STAGES, ROWS, BATCH>, P);
+  if (le != cudaSuccess) return fail_cuda("step_bulk_kernel launch", le);
   return PKV_OK;
+}
+
+// Launches with many tiles per CTA (a decode step over long contexts) run best with 8-row tiles resolved one at a
+// time; launches with only a few tiles per CTA (a prefill chunk, a small shard) with 4-row tiles, twice the CTAs and
+// whole-warp batches (measured on B200: 5.9 vs 5.4 TB/s for the first kind, 4.4 vs 3.0 TB/s for the second).
+bool many_tiles_per_cta(const StepParams& P) {
+  const DeviceInfo& d = device_info();
+  const long long row_tiles = (P.s.T + 7) / 8;
+  const long long tiles8 = (long long)P.L * ((long long)P.s.Q * ((P.s.k + 7) / 8) + (P.append_tiles ? row_tiles : 0) + (P.key_tiles ? row_tiles : 0));
+  return tiles8 >= 6ll * 8 * (d.ok ? d.sms : 148);
 }
 
 template <int STAGES, int ROWS>
 int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
-  return tuning().prefetch ? launch_bulk_impl<STAGES, ROWS, true>(P, ctas_per_sm, st)
-                           : launch_bulk_impl<STAGES, ROWS, false>(P, ctas_per_sm, st);
+  constexpr int kFull = 32 / ROWS;
+  const int want = tuning().batch >= 0 ? tuning().batch : (many_tiles_per_cta(P) ? 1 : 0);
+  if (want == 1) return launch_bulk_b<STAGES, ROWS, 1>(P, ctas_per_sm, st);
+  if constexpr (kFull >= 2) {
+    if (want == 2) return launch_bulk_b<STAGES, ROWS, 2>(P, ctas_per_sm, st);
+  }
+  return launch_bulk_b<STAGES, ROWS, kFull>(P, ctas_per_sm, st);
 }
 
 int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t st) {
-  switch (shape) {
-    case 316: return launch_bulk<3, 16>(P, ctas_per_sm, st);
-    case 416: return launch_bulk<4, 16>(P, ctas_per_sm, st);
-    case 332: return launch_bulk<3, 32>(P, ctas_per_sm, st);
-    case 308: return launch_bulk<3, 8>(P, ctas_per_sm, st);
+  if (shape == 0) shape = many_tiles_per_cta(P) ? 308 : 304;
+  switch (shape) {  // STAGES * 100 + ROWS
+    case 302: return launch_bulk<3, 2>(P, ctas_per_sm, st);
+    case 402: return launch_bulk<4, 2>(P, ctas_per_sm, st);
+    case 602: return launch_bulk<6, 2>(P, ctas_per_sm, st);
     case 304: return launch_bulk<3, 4>(P, ctas_per_sm, st);
     case 404: return launch_bulk<4, 4>(P, ctas_per_sm, st);
     case 604: return launch_bulk<6, 4>(P, ctas_per_sm, st);
-    case 508: return launch_bulk<5, 8>(P, ctas_per_sm, st);
+    case 804: return launch_bulk<8, 4>(P, ctas_per_sm, st);
+    case 1204: return launch_bulk<12, 4>(P, ctas_per_sm, st);
+    case 308: return launch_bulk<3, 8>(P, ctas_per_sm, st);
     case 408: return launch_bulk<4, 8>(P, ctas_per_sm, st);
-    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape (316, 416, 332, 308, 408, 508, 304, 404, 604)");
+    case 508: return launch_bulk<5, 8>(P, ctas_per_sm, st);
+    case 608: return launch_bulk<6, 8>(P, ctas_per_sm, st);
+    case 808: return launch_bulk<8, 8>(P, ctas_per_sm, st);
+    case 316: return launch_bulk<3, 16>(P, ctas_per_sm, st);
+    case 416: return launch_bulk<4, 16>(P, ctas_per_sm, st);
+    case 616: return launch_bulk<6, 16>(P, ctas_per_sm, st);
+    case 332: return launch_bulk<3, 32>(P, ctas_per_sm, st);
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape");
   }
 }
 
@@ -846,8 +998,9 @@ int pkv_tune(int knob, int value) {
     case 1: t.bulk_ctas_per_sm = value; return PKV_OK;
     case 2: t.pdl = value; return PKV_OK;
     case 3: t.vec_ctas_per_sm = value > 0 ? value : 5; return PKV_OK;
-    case 4: t.prefetch = value; return PKV_OK;
-    case 5: t.fuse_limit = value; return PKV_OK;
+    case 4: t.fuse = value; return PKV_OK;
+    case 5: t.batch = value; return PKV_OK;
+    case 6: t.resolve_late = value; return PKV_OK;
     default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
   }
 }
@@ -993,14 +1146,18 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   P.flags = flags;
   std::memcpy(P.layers, layers, sizeof(pkv_layer) * size_t(L));
   const bool bulk = gather && (flags & PKV_VARIANT_BULK);
-  // With the bulk pipeline a small append (a decode step) rides inside the gather launch, two rows per 32-thread tile.
-  const bool fuse_append = (flags & PKV_VARIANT_BULK) && append && (long long)((s.T + 1) / 2) * L <= tuning().fuse_limit;
-  if (fuse_append) {
+  // With the bulk pipeline the step's appends are tiles of the same launch (rows of at least 256 bytes, so that a
+  // tile of 128-wide keys fits the stage a tile of rows uses).
+  const bool rows_on = append && (flags & PKV_DO_ROWS), keys_on = append && (flags & (PKV_DO_KEYS_FP4 | PKV_DO_KEYS_FP8));
+  if ((flags & PKV_VARIANT_BULK) && append && tuning().fuse && s.width >= PKV_FP4_ROW_DIM) {
     StepParams B = P;
-    B.append_tiles = (s.T + 1) / 2;
+    B.append_tiles = rows_on ? 1 : 0;   // flags here; launch_bulk counts the tiles for its ROWS
+    B.key_tiles = keys_on ? 1 : 0;
     if (!gather) B.s.Q = 0;
-    B.tiles_per_q = 0;
-    B.gather_tiles = 0;
+    for (int l = 0; l < L; ++l) {       // a layer without the arrays of a part cannot take part in it
+      if (rows_on && (!B.layers[l].rows || !B.layers[l].row_pool)) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks rows or row_pool");
+      if (keys_on && !B.layers[l].keys) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks keys");
+    }
     return dispatch_bulk(B, bulk_shape, bulk_ctas, stream);
   }
   P.append_tiles = append ? (s.T + kAppendRows - 1) / kAppendRows : 0;
@@ -1016,6 +1173,7 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   }
   if (bulk) {
     P.append_tiles = 0;
+    P.key_tiles = 0;
     return dispatch_bulk(P, bulk_shape, bulk_ctas, stream);
   }
   return PKV_OK;
