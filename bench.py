@@ -47,7 +47,7 @@ APPEND_BYTES = 2 * ROW_BYTES + (KEY_DIM * 2 + 68)      # 2304 + 324
 GATHER_BYTES = K_SEL * 2 * ROW_BYTES                   # 2048 rows read and written
 STEP_BYTES_PER_GPU = LAYERS * NSEQ * (APPEND_BYTES + GATHER_BYTES)
 # dram__bytes_read.sum + dram__bytes_write.sum of one per-layer launch (ncu capture summarised under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 248_560_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 249_350_000
 WORKLOAD_NAME = "decode43: 64 seq x 128k ctx per GPU, page 64, 43 layers, bf16 576 rows + MXFP4 128 keys, top-2048 gather"
 
 
@@ -434,7 +434,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and wl.lpl == 1) else None,
-                         "traffic_source": "profiles/gather_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
+                         "traffic_source": "profiles/step_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
                          "peak_kind": "of " + peak_kind,
                          "kernel": "step_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
                          "algorithmic_bytes_per_launch": int(call_bytes)},
