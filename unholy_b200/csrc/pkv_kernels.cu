@@ -895,11 +895,9 @@ template <int STAGES, int ROWS, int BATCH>
 int launch_bulk_b(const StepParams& P0, int ctas_per_sm, cudaStream_t st) {
   StepParams P = P0;
   P.resolve_late = tuning().resolve_late;
-  const bool append = P.append_tiles != 0 || P.key_tiles != 0;   // set by the caller as flags; counted in ROWS here
   const int row_tiles = (P.s.T + ROWS - 1) / ROWS;
   P.append_tiles = P0.append_tiles ? row_tiles : 0;
   P.key_tiles = P0.key_tiles ? row_tiles : 0;
-  (void)append;
   const size_t smem = size_t(STAGES) * ROWS * size_t(P.s.width) * 2u;
   if (smem > 224u * 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
   // Dynamic shared memory above 48 KB has to be opted into, per device and per kernel instantiation.

@@ -47,37 +47,70 @@ __host__ __device__ inline Layout layout(int T, int n, int k) {
   return l;
 }
 
-// Inclusive suffix sums of hist[0..255] in place (S[b] = sum of bins >= b), then the bin the reference's walk from the
-// top finds: the highest b >= 1 with S[b] >= need, else 0. Returns through shared variables. blockDim.x >= 256.
-__device__ void pick_bin(uint32_t* hist, uint32_t need, uint32_t* s_bin, uint32_t* s_need) {
-  const int tid = threadIdx.x;
-  for (int d = 1; d < 256; d <<= 1) {
-    uint32_t add = 0;
-    if (tid < 256 && tid + d < 256) add = hist[tid + d];
-    __syncthreads();
-    if (tid < 256) hist[tid] += add;
-    __syncthreads();
+constexpr int kPerThread = kSlice / kThreads;  // 16 consecutive keys per thread: two 16-byte loads
+
+// This thread's kPerThread consecutive keys of the slice, as order-preserving 16-bit keys; 0 (never valid) past the end.
+__device__ __forceinline__ void load_keys(const uint16_t* __restrict__ r, int base, int hi, uint32_t* key) {
+  const uint16_t* p = r + base;
+  if (base + kPerThread <= hi && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+    for (int v = 0; v < kPerThread / 8; ++v) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + v);
+      const uint32_t x[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        key[v * 8 + 2 * i] = key16(x[i] & 0xffffu);
+        key[v * 8 + 2 * i + 1] = key16(x[i] >> 16);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) key[i] = base + i < hi ? key16(p[i]) : 0u;
   }
-  if (tid == 0) {
-    *s_bin = 0;
-    *s_need = need - hist[1];
+}
+
+// Threshold bin of a 256-bin histogram h (plain counts in shared memory): the highest bin b >= 1 whose suffix sum
+// S[b] = sum of bins >= b reaches `need`, else bin 0 — what the reference's walk from the top finds
+// (src/kernels/indexer.hip:447-462). need < 0 means "min(k, number of valid keys)" (the first pass). Outputs through
+// shared memory: s_out[0] = bin, s_out[1] = how many are still needed inside that bin, s_out[2] = S[0] (all counted
+// keys). Called by every thread of the CTA; threads 0..255 hold one bin each; suffix sums by warp shuffles.
+__device__ void pick_bin(const uint32_t* h, int need_in, int k, uint32_t* s_wsum, uint32_t* s_out) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t mine = 0, v = 0;
+  if (tid < 256) {
+    mine = h[tid];
+    v = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_down_sync(0xffffffffu, v, o);
+      if (lane + o < 32) v += t;
+    }
+    if (lane == 0) s_wsum[warp] = v;
   }
   __syncthreads();
-  if (tid >= 1 && tid < 256) {
-    const uint32_t above = tid < 255 ? hist[tid + 1] : 0u;
-    if (hist[tid] >= need && above < need) {
-      *s_bin = uint32_t(tid);
-      *s_need = need - above;
-    }
+  if (tid < 256)
+    for (int w = warp + 1; w < 8; ++w) v += s_wsum[w];
+  if (tid == 0) {
+    s_out[2] = v;
+    const uint32_t need = need_in < 0 ? min(uint32_t(k), v) : uint32_t(need_in);
+    s_out[0] = 0;
+    s_out[1] = need - (v - mine);  // bin 0: everything above it counts
+    s_out[3] = need;
+  }
+  __syncthreads();
+  const uint32_t need = s_out[3];
+  if (tid >= 1 && tid < 256 && v >= need && v - mine < need) {
+    s_out[0] = uint32_t(tid);
+    s_out[1] = need - (v - mine);
   }
   __syncthreads();
 }
 
 // Sum over slices of one of the two histograms of a row into shared memory.
-__device__ void sum_hist(const uint32_t* row_hist, int slices, int which, uint32_t* out) {
+__device__ void sum_hist(const uint32_t* __restrict__ row_hist, int slices, int which, uint32_t* out) {
   for (int b = threadIdx.x; b < 256; b += blockDim.x) {
     uint32_t s = 0;
-    for (int sl = 0; sl < slices; ++sl) s += row_hist[(size_t(sl) * 2 + which) * 256 + b];
+    for (int sl = 0; sl < slices; ++sl) s += __ldg(&row_hist[(size_t(sl) * 2 + which) * 256 + b]);
     out[b] = s;
   }
   __syncthreads();
@@ -87,72 +120,84 @@ __device__ void sum_hist(const uint32_t* row_hist, int slices, int which, uint32
 // high byte is derived from the summed pass-1 histograms, then the low byte is histogrammed over the keys that share it.
 __global__ void __launch_bounds__(kThreads) hist_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
                                                         uint32_t* __restrict__ scratch, int slices, int which) {
-  __shared__ uint32_t hist[256], total[256];
-  __shared__ uint32_t s_bin, s_need;
+  __shared__ uint32_t hist[256], total[256], s_wsum[8], s_out[4];
   const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x;
   uint32_t* row_hist = scratch + size_t(row) * slices * 512;
+  const uint16_t* r = scores + size_t(row) * ld;
+  const int lo = sl * kSlice, hi = min(n, lo + kSlice);
+  uint32_t key[kPerThread];
+  load_keys(r, lo + tid * kPerThread, hi, key);  // issued before the threshold is known: the loads overlap the prologue
   uint32_t hi_bin = 0;
   if (which == 1) {
     sum_hist(row_hist, slices, 0, total);
-    uint32_t nvalid = 0;
-    // total[] still holds plain counts here: the number of valid keys is their sum (computed by every thread).
-    for (int b = 0; b < 256; ++b) nvalid += total[b];
-    const uint32_t want = min(uint32_t(k), nvalid);
-    __syncthreads();
-    pick_bin(total, want, &s_bin, &s_need);
-    hi_bin = s_bin;
+    pick_bin(total, -1, k, s_wsum, s_out);
+    hi_bin = s_out[0];
   }
   for (int b = tid; b < 256; b += kThreads) hist[b] = 0;
   __syncthreads();
-  const uint16_t* r = scores + size_t(row) * ld;
-  const int lo = sl * kSlice, hi = min(n, lo + kSlice);
-  for (int i = lo + tid; i < hi; i += kThreads) {
-    const uint32_t key = key16(r[i]);
-    if (key <= kNegInfKey) continue;
-    if (which == 0) atomicAdd(&hist[key >> 8], 1u);
-    else if ((key >> 8) == hi_bin) atomicAdd(&hist[key & 0xffu], 1u);
+  // Plain shared-memory atomics: measured faster here than electing one lane per bin (match.any or ballot rounds cost
+  // more than the same-address queueing they avoid).
+#pragma unroll
+  for (int i = 0; i < kPerThread; ++i) {
+    if (key[i] <= kNegInfKey) continue;
+    if (which == 0) atomicAdd(&hist[key[i] >> 8], 1u);
+    else if ((key[i] >> 8) == hi_bin) atomicAdd(&hist[key[i] & 0xffu], 1u);
   }
   __syncthreads();
   for (int b = tid; b < 256; b += kThreads) row_hist[(size_t(sl) * 2 + which) * 256 + b] = hist[b];
 }
 
 // Collect: every slice writes its keys above the threshold and its share of the threshold ties (lowest indices first
-// across the whole row) into the row's candidate array at offsets known from the per-slice histograms.
+// across the whole row) into the row's candidate array at offsets known from the per-slice histograms. Each thread owns
+// 16 consecutive keys, so index order is thread order and one block-wide scan places everything.
 __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
                                                            uint32_t* __restrict__ scratch, int slices, size_t cand_offset) {
-  __shared__ uint32_t total[256];
-  __shared__ uint32_t s_bin, s_need, s_above, s_warp[kThreads / 32], s_run;
+  __shared__ uint32_t total[256], s_wsum[kThreads / 32], s_out[4];
   __shared__ uint32_t s_slice_above[kMaxSlices], s_slice_ties[kMaxSlices];
-  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x;
+  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t* row_hist = scratch + size_t(row) * slices * 512;
   unsigned long long* cand = reinterpret_cast<unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
+  const uint16_t* r = scores + size_t(row) * ld;
+  const int lo = sl * kSlice, hi = min(n, lo + kSlice), base = lo + tid * kPerThread;
+  uint32_t key[kPerThread];
+  load_keys(r, base, hi, key);
   sum_hist(row_hist, slices, 0, total);
-  uint32_t nvalid = 0;
-  for (int b = 0; b < 256; ++b) nvalid += total[b];
-  const uint32_t want = min(uint32_t(k), nvalid);
+  pick_bin(total, -1, k, s_wsum, s_out);
+  const uint32_t hi_bin = s_out[0], need1 = s_out[1], want = s_out[3];
   __syncthreads();
   if (want == 0) return;
-  pick_bin(total, want, &s_bin, &s_need);
-  const uint32_t hi_bin = s_bin, need1 = s_need;
-  __syncthreads();
   sum_hist(row_hist, slices, 1, total);
-  pick_bin(total, need1, &s_bin, &s_need);
-  const uint32_t lo_bin = s_bin, need_ties = s_need;
+  pick_bin(total, int(need1), k, s_wsum, s_out);
+  const uint32_t lo_bin = s_out[0], need_ties = s_out[1];
   const uint32_t thr = (hi_bin << 8) | lo_bin;
-  // Offsets: keys above the threshold come first (any order: the sort follows), then the ties in index order. One warp
-  // per slice sums that slice's bins above the threshold.
-  for (int s2 = tid >> 5; s2 < slices; s2 += kThreads / 32) {
+  // Keys above the threshold come first (any order: the sort follows), then the ties in index order. One warp per
+  // slice sums that slice's bins above the threshold.
+  for (int s2 = warp; s2 < slices; s2 += kThreads / 32) {
     const uint32_t* h0 = row_hist + (size_t(s2) * 2) * 256;
     const uint32_t* h1 = h0 + 256;
     uint32_t a = 0;
-    for (uint32_t b = tid & 31; b < 256; b += 32) a += (b > hi_bin ? h0[b] : 0u) + (b > lo_bin ? h1[b] : 0u);
+    for (uint32_t b = lane; b < 256; b += 32) a += (b > hi_bin ? __ldg(&h0[b]) : 0u) + (b > lo_bin ? __ldg(&h1[b]) : 0u);
     for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    if ((tid & 31) == 0) {
+    if (lane == 0) {
       s_slice_above[s2] = a;
-      s_slice_ties[s2] = h1[lo_bin];
+      s_slice_ties[s2] = __ldg(&h1[lo_bin]);
     }
   }
+  // This thread's counts, packed (above << 16 | ties; a slice holds 8192 keys), and their block-wide exclusive scan.
+  uint32_t cnt = 0;
+#pragma unroll
+  for (int i = 0; i < kPerThread; ++i) cnt += key[i] > kNegInfKey ? (key[i] > thr ? 0x10000u : (key[i] == thr ? 1u : 0u)) : 0u;
+  uint32_t incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();  // s_wsum was last read inside pick_bin
+  if (lane == 31) s_wsum[warp] = incl;
   __syncthreads();
+  uint32_t before = incl - cnt;
+  for (int w = 0; w < warp; ++w) before += s_wsum[w];
   uint32_t above_before = 0, ties_before = 0, above_total = 0;
   for (int s2 = 0; s2 < slices; ++s2) {
     above_total += s_slice_above[s2];
@@ -161,47 +206,25 @@ __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __res
       ties_before += s_slice_ties[s2];
     }
   }
-  if (tid == 0) {
-    s_above = 0;
-    s_run = 0;
-  }
-  __syncthreads();
-  const uint16_t* r = scores + size_t(row) * ld;
-  const int lo = sl * kSlice, hi = min(n, lo + kSlice);
-  for (int base = lo; base < hi; base += kThreads) {
-    const int i = base + tid;
-    const uint32_t key = i < hi ? key16(r[i]) : 0u;
-    const bool valid = i < hi && key > kNegInfKey;
-    if (valid && key > thr) {
-      const uint32_t slot = above_before + atomicAdd(&s_above, 1u);
-      cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - uint32_t(i));
+  uint32_t a_pos = above_before + (before >> 16), t_rank = ties_before + (before & 0xffffu);
+#pragma unroll
+  for (int i = 0; i < kPerThread; ++i) {
+    if (key[i] <= kNegInfKey) continue;
+    const unsigned long long packed = (static_cast<unsigned long long>(key[i]) << 32) | (0xffffffffu - uint32_t(base + i));
+    if (key[i] > thr) {
+      cand[a_pos++] = packed;
+    } else if (key[i] == thr) {
+      if (t_rank < need_ties) cand[above_total + t_rank] = packed;
+      ++t_rank;
     }
-    // ordered positions of the ties of this chunk
-    const bool tie = valid && key == thr;
-    const unsigned ballot = __ballot_sync(0xffffffffu, tie);
-    const int lane = tid & 31, warp = tid >> 5;
-    if (lane == 0) s_warp[warp] = __popc(ballot);
-    __syncthreads();
-    uint32_t before = s_run;
-    for (int w = 0; w < warp; ++w) before += s_warp[w];
-    before += __popc(ballot & ((1u << lane) - 1u));
-    if (tie) {
-      const uint32_t rank = ties_before + before;
-      if (rank < need_ties) cand[above_total + rank] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - uint32_t(i));
-    }
-    __syncthreads();
-    if (tid == 0) {
-      uint32_t t = 0;
-      for (int w = 0; w < kThreads / 32; ++w) t += s_warp[w];
-      s_run += t;
-    }
-    __syncthreads();
   }
 }
 
-// Sort: one CTA per row; (key, ~index) descending = (score descending, index ascending); -1 padding.
-__global__ void __launch_bounds__(kThreads) sort_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
-                                                        size_t cand_offset, int32_t* __restrict__ idx) {
+// Sort: one CTA per row; (key, ~index) descending = (score descending, index ascending); -1 padding. Bitonic network,
+// one compare-exchange per thread per stage (thread p owns the p-th pair of the stage).
+constexpr int kSortThreads = 1024;
+__global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
+                                                            size_t cand_offset, int32_t* __restrict__ idx) {
   extern __shared__ unsigned long long s_keys[];
   __shared__ uint32_t s_want;
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -209,32 +232,32 @@ __global__ void __launch_bounds__(kThreads) sort_kernel(const uint32_t* __restri
   if (tid == 0) s_want = 0;
   __syncthreads();
   uint32_t local = 0;
-  for (int j = tid; j < slices * 256; j += kThreads) local += row_hist[(size_t(j >> 8) * 2) * 256 + (j & 255)];
-  atomicAdd(&s_want, local);
+  for (int j = tid; j < slices * 256; j += kSortThreads) local += __ldg(&row_hist[(size_t(j >> 8) * 2) * 256 + (j & 255)]);
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((tid & 31) == 0 && local) atomicAdd(&s_want, local);
   __syncthreads();
   const uint32_t want = min(uint32_t(k), s_want);
-  int size = 1;
+  int size = 2;
   while (size < k) size <<= 1;
   const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
-  for (int i = tid; i < size; i += kThreads) s_keys[i] = uint32_t(i) < want ? cand[i] : 0ull;
+  for (int i = tid; i < size; i += kSortThreads) s_keys[i] = uint32_t(i) < want ? cand[i] : 0ull;
   __syncthreads();
+  const int pairs = size >> 1;
   for (int len = 2; len <= size; len <<= 1)
     for (int stride = len >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < size; i += kThreads) {
-        const int j = i ^ stride;
-        if (j > i) {
-          const bool desc = (i & len) == 0;
-          const unsigned long long a = s_keys[i], b = s_keys[j];
-          if ((a < b) == desc) {
-            s_keys[i] = b;
-            s_keys[j] = a;
-          }
+      for (int p = tid; p < pairs; p += kSortThreads) {
+        const int i = ((p & ~(stride - 1)) << 1) | (p & (stride - 1)), j = i | stride;
+        const bool desc = (i & len) == 0;
+        const unsigned long long a = s_keys[i], b = s_keys[j];
+        if ((a < b) == desc) {
+          s_keys[i] = b;
+          s_keys[j] = a;
         }
       }
       __syncthreads();
     }
   int32_t* out = idx + size_t(row) * k;
-  for (int i = tid; i < k; i += kThreads)
+  for (int i = tid; i < k; i += kSortThreads)
     out[i] = uint32_t(i) < want ? int32_t(0xffffffffu - uint32_t(s_keys[i] & 0xffffffffull)) : -1;
 }
 
@@ -293,9 +316,9 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
   hist_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, 0);
   hist_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, 1);
   collect_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, l.cand_offset_words);
-  int size = 1;
+  int size = 2;
   while (size < k) size <<= 1;
-  sort_kernel<<<unsigned(T), kThreads, size_t(size) * 8, stream>>>(scratch, k, l.slices, l.cand_offset_words, idx);
+  sort_kernel<<<unsigned(T), kSortThreads, size_t(size) * 8, stream>>>(scratch, k, l.slices, l.cand_offset_words, idx);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     err = std::string("top-k launch: ") + cudaGetErrorString(e);
