@@ -290,12 +290,18 @@ class CpuWorkload:
 
 
 def cpu_baseline(threads: int, seconds_target: float = 10.0):
+    """(GB/s with `threads` threads, description, GB/s with one thread)."""
     wl = CpuWorkload(threads)
     times = []
     while sum(times) < seconds_target and len(times) < 86:
         times.append(wl.layer_step())
     gbs = wl.layer_bytes * len(times) / sum(times) / 1e9
-    return gbs, wl.describe(len(times))
+    wl.threads = 1
+    single = []
+    while sum(single) < seconds_target / 2 and len(single) < 8:
+        single.append(wl.layer_step())
+    wl.threads = threads
+    return gbs, wl.describe(len(times)), wl.layer_bytes * len(single) / sum(single) / 1e9
 
 
 def run_reference_arm(args):
@@ -448,8 +454,9 @@ def run_ours(args):
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle_lib as orc
             threads = max(1, orc.hardware_threads())
-            gbs, desc = cpu_baseline(threads)
-            line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc}
+            gbs, desc, gbs1 = cpu_baseline(threads)
+            line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": desc,
+                                    "value_1_thread": round(gbs1, 3)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

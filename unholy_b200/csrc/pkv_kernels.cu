@@ -238,6 +238,39 @@ constexpr int kAppendRows = kVecThreads / 16;  // batch rows per append tile: 16
 constexpr int kGatherRows = 32;             // index entries per gather tile
 constexpr int kGatherUnroll = 6;            // 32 rows x 72 vectors = 384 threads x 6
 
+// One 128-wide key row held by 16 consecutive lanes (8 values each, lane j of the row in `j`): MXFP4 and / or fp8
+// quantisation and the stores into the row's place (physical row `rid`; negative: nothing is stored). Every lane of the
+// warp must call it: the block maxima and the row's four MXFP4 scale bytes travel by shuffles.
+__device__ __forceinline__ void quantise_key_row(const pkv_step& s, const pkv_layer& ly, const float* v, long long rid, int j,
+                                                 bool fp4, bool fp8) {
+  const float a8 = pkv::absmax8(v);
+  if (fp4) {
+    const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
+    const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
+    const int base = (threadIdx.x & 31) & 16;  // the row's first lane
+    const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
+                   s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
+    if (rid >= 0) {
+      const long long page = rid / s.rows_per_page;
+      const int slot = int(rid - page * s.rows_per_page);
+      uint8_t* pg = ly.key_pool_fp4 + size_t(page) * size_t(s.rows_per_page) * 68u;
+      *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
+      if (j == 0)
+        *reinterpret_cast<uint32_t*>(pg + size_t(s.rows_per_page) * 64u + size_t(slot) * 4u) =
+            s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+    }
+  }
+  if (fp8) {
+    const int group = s.fp8_block >> 3;
+    const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(a8, group));
+    const uint2 codes = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
+    if (rid >= 0) {
+      *reinterpret_cast<uint2*>(ly.key_fp8_codes + size_t(rid) * PKV_FP4_ROW_DIM + j * 8) = codes;
+      if (j % group == 0) ly.key_fp8_scales[size_t(rid) * (PKV_FP4_ROW_DIM / s.fp8_block) + j / group] = uint8_t(se);
+    }
+  }
+}
+
 // One append tile: batch rows [t_first, t_first + kAppendRows) of one layer. Copies the bf16 rows into the pool and
 // quantises the keys (MXFP4 and/or fp8) to the same physical rows.
 template <int NT>
@@ -294,33 +327,7 @@ __device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_firs
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
-    const float a8 = pkv::absmax8(v);
-    if (fp4) {
-      const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
-      const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
-      // The four block scales of the row meet in the row's first lane.
-      const int base = (tid & 31) & 16;
-      const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
-                     s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
-      if (rid >= 0) {
-        const long long page = rid / s.rows_per_page;
-        const int slot = int(rid - page * s.rows_per_page);
-        uint8_t* pg = ly.key_pool_fp4 + size_t(page) * size_t(s.rows_per_page) * 68u;
-        *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
-        if (j == 0)
-          *reinterpret_cast<uint32_t*>(pg + size_t(s.rows_per_page) * 64u + size_t(slot) * 4u) =
-              s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
-      }
-    }
-    if (fp8) {
-      const int group = s.fp8_block >> 3;
-      const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(a8, group));
-      const uint2 codes = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
-      if (rid >= 0) {
-        *reinterpret_cast<uint2*>(ly.key_fp8_codes + size_t(rid) * PKV_FP4_ROW_DIM + j * 8) = codes;
-        if (j % group == 0) ly.key_fp8_scales[size_t(rid) * (PKV_FP4_ROW_DIM / s.fp8_block) + j / group] = uint8_t(se);
-      }
-    }
+    quantise_key_row(s, ly, v, rid, j, fp4, fp8);
   }
   __syncthreads();
 }
@@ -457,32 +464,7 @@ __device__ __forceinline__ void quantise_staged_keys(const StepParams& P, const 
     const long long rid = r < nrows ? rids[r] : -1;
     float v[8];
     pkv::unpack8(*reinterpret_cast<const uint4*>(stage + size_t(r < ROWS ? r : 0) * (PKV_FP4_ROW_DIM * 2) + j * 16), v);
-    const float a8 = pkv::absmax8(v);
-    if (fp4) {
-      const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
-      const uint32_t codes = pkv::fp4_pack8(v, pkv::e8m0_bits_to_f32(se));
-      const int base = lane & 16;
-      const uint32_t s0 = __shfl_sync(0xffffffffu, se, base), s1 = __shfl_sync(0xffffffffu, se, base + 4),
-                     s2 = __shfl_sync(0xffffffffu, se, base + 8), s3 = __shfl_sync(0xffffffffu, se, base + 12);
-      if (rid >= 0) {
-        const long long page = rid / s.rows_per_page;
-        const int slot = int(rid - page * s.rows_per_page);
-        uint8_t* pg = ly.key_pool_fp4 + size_t(page) * size_t(s.rows_per_page) * 68u;
-        *reinterpret_cast<uint32_t*>(pg + size_t(slot) * 64u + j * 4) = codes;
-        if (j == 0)
-          *reinterpret_cast<uint32_t*>(pg + size_t(s.rows_per_page) * 64u + size_t(slot) * 4u) =
-              s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
-      }
-    }
-    if (fp8) {
-      const int group = s.fp8_block >> 3;
-      const uint32_t se = pkv::fp8_scale_exp(pkv::group_max(a8, group));
-      const uint2 codes = pkv::fp8_pack8(v, pkv::e8m0_bits_to_f32(se));
-      if (rid >= 0) {
-        *reinterpret_cast<uint2*>(ly.key_fp8_codes + size_t(rid) * PKV_FP4_ROW_DIM + j * 8) = codes;
-        if (j % group == 0) ly.key_fp8_scales[size_t(rid) * (PKV_FP4_ROW_DIM / s.fp8_block) + j / group] = uint8_t(se);
-      }
-    }
+    quantise_key_row(s, ly, v, rid, j, fp4, fp8);
   }
 }
 
