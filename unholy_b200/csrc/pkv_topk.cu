@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -120,6 +121,8 @@ __device__ void sum_hist(const uint32_t* __restrict__ row_hist, int slices, int 
 // high byte is derived from the summed pass-1 histograms, then the low byte is histogrammed over the keys that share it.
 __global__ void __launch_bounds__(kThreads) hist_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
                                                         uint32_t* __restrict__ scratch, int slices, int which) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
   __shared__ uint32_t hist[256], total[256], s_wsum[8], s_out[4];
   const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x;
   uint32_t* row_hist = scratch + size_t(row) * slices * 512;
@@ -152,6 +155,8 @@ __global__ void __launch_bounds__(kThreads) hist_kernel(const uint16_t* __restri
 // 16 consecutive keys, so index order is thread order and one block-wide scan places everything.
 __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
                                                            uint32_t* __restrict__ scratch, int slices, size_t cand_offset) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
   __shared__ uint32_t total[256], s_wsum[kThreads / 32], s_out[4];
   __shared__ uint32_t s_slice_above[kMaxSlices], s_slice_ties[kMaxSlices];
   const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -225,6 +230,8 @@ __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __res
 constexpr int kSortThreads = 1024;
 __global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
                                                             size_t cand_offset, int32_t* __restrict__ idx) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
   extern __shared__ unsigned long long s_keys[];
   __shared__ uint32_t s_want;
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -259,6 +266,67 @@ __global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __re
   int32_t* out = idx + size_t(row) * k;
   for (int i = tid; i < k; i += kSortThreads)
     out[i] = uint32_t(i) < want ? int32_t(0xffffffffu - uint32_t(s_keys[i] & 0xffffffffull)) : -1;
+}
+
+// The same sort for 64 <= size <= 2048 with size / 2 threads, two elements per thread (2t, 2t + 1): strides 1..32 are
+// exchanges inside a thread or between lanes of a warp (shuffles, no barrier); only strides >= 64 go through shared
+// memory. 15 of the 66 stages of a 2048-element sort need a barrier instead of all of them.
+__device__ __forceinline__ unsigned long long shfl_xor64(unsigned long long v, int lane_mask) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, uint32_t(v), lane_mask);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), lane_mask);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+__global__ void __launch_bounds__(1024) sort_pairs_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
+                                                          size_t cand_offset, int32_t* __restrict__ idx, int size) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
+  extern __shared__ unsigned long long s_keys[];
+  __shared__ uint32_t s_want;
+  const int row = blockIdx.x, tid = threadIdx.x, nthreads = size >> 1;
+  const uint32_t* row_hist = scratch + size_t(row) * slices * 512;
+  if (tid == 0) s_want = 0;
+  __syncthreads();
+  uint32_t local = 0;
+  for (int j = tid; j < slices * 256; j += nthreads) local += __ldg(&row_hist[(size_t(j >> 8) * 2) * 256 + (j & 255)]);
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((tid & 31) == 0 && local) atomicAdd(&s_want, local);
+  __syncthreads();
+  const uint32_t want = min(uint32_t(k), s_want);
+  const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
+  const int i0 = 2 * tid, i1 = i0 + 1;
+  unsigned long long a = uint32_t(i0) < want ? cand[i0] : 0ull, b = uint32_t(i1) < want ? cand[i1] : 0ull;
+  // Position i keeps the larger of the pair when it is the lower position of a descending run (or the upper of an
+  // ascending one).
+  auto keep = [](unsigned long long mine, unsigned long long other, bool take_max) {
+    return take_max == (mine > other) ? mine : other;
+  };
+  for (int len = 2; len <= size; len <<= 1) {
+    for (int stride = len >> 1; stride > 0; stride >>= 1) {
+      const bool desc = (i0 & len) == 0;  // i0 and i1 lie in the same run of length len >= 2
+      if (stride == 1) {
+        const unsigned long long hi = a > b ? a : b, lo = a > b ? b : a;
+        a = desc ? hi : lo;
+        b = desc ? lo : hi;
+      } else if (stride <= 32) {
+        const bool lower = (i0 & stride) == 0;  // i1 shares the bit (stride >= 2)
+        const unsigned long long oa = shfl_xor64(a, stride >> 1), ob = shfl_xor64(b, stride >> 1);
+        a = keep(a, oa, lower == desc);
+        b = keep(b, ob, lower == desc);
+      } else {
+        s_keys[i0] = a;
+        s_keys[i1] = b;
+        __syncthreads();
+        const bool lower = (i0 & stride) == 0;
+        const unsigned long long oa = s_keys[i0 ^ stride], ob = s_keys[i1 ^ stride];
+        a = keep(a, oa, lower == desc);
+        b = keep(b, ob, lower == desc);
+        __syncthreads();
+      }
+    }
+  }
+  int32_t* out = idx + size_t(row) * k;
+  if (i0 < k) out[i0] = uint32_t(i0) < want ? int32_t(0xffffffffu - uint32_t(a & 0xffffffffull)) : -1;
+  if (i1 < k) out[i1] = uint32_t(i1) < want ? int32_t(0xffffffffu - uint32_t(b & 0xffffffffull)) : -1;
 }
 
 }  // namespace pkv_topk
@@ -313,12 +381,34 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
   using namespace pkv_topk;
   const Layout l = layout(T, n, k);
   const dim3 grid(unsigned(l.slices), unsigned(T));
-  hist_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, 0);
-  hist_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, 1);
-  collect_kernel<<<grid, kThreads, 0, stream>>>(scores, n, ld, k, scratch, l.slices, l.cand_offset_words);
   int size = 2;
   while (size < k) size <<= 1;
-  sort_kernel<<<unsigned(T), kSortThreads, size_t(size) * 8, stream>>>(scratch, k, l.slices, l.cand_offset_words, idx);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  auto config = [&](dim3 g, unsigned threads, size_t smem) {
+    cudaLaunchConfig_t c;
+    std::memset(&c, 0, sizeof(c));
+    c.gridDim = g;
+    c.blockDim = dim3(threads);
+    c.dynamicSmemBytes = smem;
+    c.stream = stream;
+    c.attrs = attr;
+    c.numAttrs = 1;
+    return c;
+  };
+  cudaLaunchConfig_t c = config(grid, kThreads, 0);
+  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l.slices, 0);
+  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l.slices, 1);
+  cudaLaunchKernelEx(&c, collect_kernel, scores, n, ld, k, scratch, l.slices, l.cand_offset_words);
+  const uint32_t* cscratch = scratch;
+  if (size >= 64 && size <= 2048) {
+    c = config(dim3(unsigned(T)), unsigned(size / 2), size_t(size) * 8);
+    cudaLaunchKernelEx(&c, sort_pairs_kernel, cscratch, k, l.slices, l.cand_offset_words, idx, size);
+  } else {
+    c = config(dim3(unsigned(T)), kSortThreads, size_t(size) * 8);
+    cudaLaunchKernelEx(&c, sort_kernel, cscratch, k, l.slices, l.cand_offset_words, idx);
+  }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     err = std::string("top-k launch: ") + cudaGetErrorString(e);
