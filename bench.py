@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="a reduced pool (for profiler captures and quick checks)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded"], default="decode43",
+    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk"], default="decode43",
                     help="decode43 is the benchmark line; the others measure the remaining operations of the path")
     return ap.parse_args()
 
@@ -972,6 +972,46 @@ def run_sharded(args):
     dist.destroy_process_group()
 
 
+def run_topk(args):
+    """The index-list producer in front of the gather: top-2048 of 131,072 bf16 scores for 64 rows (one layer's decode
+    batch), checked on the device against a full sort of (score descending, index ascending)."""
+    torch, capi, lib = _cuda_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(6)
+    T, n, k = NSEQ, (8192 if args.small else CONTEXT), K_SEL
+    scores = torch.randn(T, n, generator=g, device=dev).to(torch.bfloat16)
+    scores[0, n // 2:] = float("-inf")                      # a row whose later keys are invisible
+    words = lib.pkv_topk_scratch_words(T, n, k)
+    scratch = torch.empty(words, dtype=torch.int32, device=dev)
+    idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        capi.check(lib.pkv_topk_bf16(scores.data_ptr(), T, n, n, k, idx.data_ptr(), scratch.data_ptr(), words, sp))
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    reps = max(args.steps, 10)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / reps * 1e3
+    # reference order on the device: stable sort by score descending keeps ascending indices among equal scores
+    order = torch.sort(scores.float(), dim=1, descending=True, stable=True).indices[:, :k].to(torch.int32)
+    valid = torch.gather(scores.float(), 1, order.long()) > float("-inf")
+    want = torch.where(valid, order, torch.full_like(order, -1))
+    ok = bool(torch.equal(idx, want))
+    nbytes = T * n * 2 + T * k * 4
+    _emit("topk", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
+        "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16, caller scratch {words * 4} B)"},
+        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok}})
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -982,6 +1022,8 @@ def main():
         run_churn(args)
     elif args.workload == "sharded":
         run_sharded(args)
+    elif args.workload == "topk":
+        run_topk(args)
     else:
         run_ours(args)
 
