@@ -175,34 +175,44 @@ class Workload:
             del r
         self.out = torch.empty(LAYERS, NSEQ, K_SEL, W, dtype=torch.bfloat16, device=dev)
         self.out.fill_(float("nan"))
-        # Prepared calls: one pkv_step_run per group of `lpl` layers.
+        # Prepared calls: one pkv_step_run per group of `lpl` layers, bound to a set of input tensors. Set 0 is the
+        # tensors above; the end-to-end leg adds a second set so that one step's upload overlaps the previous step.
+        self.flags = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_GATHER | self.variant
+        self.groups = [(l, min(self.lpl, LAYERS - l)) for l in range(0, LAYERS, self.lpl)]
+        self.sets = [self._bind({k: getattr(self, k) for k in self.INPUTS})]
+        self.kernels_per_call = 1   # appends and the gather are tiles of one launch (both gather variants)
+        # Layers that share a resident pool and run in ONE launch write the same appended row in no defined order.
+        self.unordered_alias = self.lpl > self.resident or (self.lpl > 1 and self.resident < LAYERS)
+
+    INPUTS = ("rows", "keys", "idx", "tables", "chunks", "q_chunk", "q_visible")
+
+    def _bind(self, t):
+        """The step descriptor and per-layer pointer structs for one set of input tensors (pools and outputs shared)."""
+        capi = self.capi
         st = capi.PkvStep()
         st.width = st.row_stride = W
         st.rows_per_page, st.max_pages_per_seq, st.num_pages, st.fp8_block = RPP, self.pps, self.num_pages, 64
         st.nchunks = st.T = st.Q = NSEQ
         st.k = K_SEL
-        st.tables, st.chunks = self.tables.data_ptr(), self.chunks.data_ptr()
-        st.q_chunk, st.q_visible = self.q_chunk.data_ptr(), self.q_visible.data_ptr()
-        self.step = st
-        self.layers = (capi.PkvLayer * LAYERS)()
+        st.tables, st.chunks = t["tables"].data_ptr(), t["chunks"].data_ptr()
+        st.q_chunk, st.q_visible = t["q_chunk"].data_ptr(), t["q_visible"].data_ptr()
+        layers = (capi.PkvLayer * LAYERS)()
         for l in range(LAYERS):
-            y = self.layers[l]
-            y.rows, y.row_pool = self.rows[l].data_ptr(), self.pools[l % self.resident].data_ptr()
-            y.keys, y.key_pool_fp4 = self.keys[l].data_ptr(), self.fp4[l % self.resident].data_ptr()
-            y.idx, y.gathered = self.idx[l].data_ptr(), self.out[l].data_ptr()
-        self.flags = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_GATHER | self.variant
-        self.groups = [(l, min(self.lpl, LAYERS - l)) for l in range(0, LAYERS, self.lpl)]
-        self.group_ptrs = [C.cast(C.byref(self.layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer))
-                           for l, _ in self.groups]
-        self.kernels_per_call = 1   # appends and the gather are tiles of one launch (both gather variants)
-        # Layers that share a resident pool and run in ONE launch write the same appended row in no defined order.
-        self.unordered_alias = self.lpl > self.resident or (self.lpl > 1 and self.resident < LAYERS)
-        self.step_ref = C.byref(self.step)
+            y = layers[l]
+            y.rows, y.row_pool = t["rows"][l].data_ptr(), self.pools[l % self.resident].data_ptr()
+            y.keys, y.key_pool_fp4 = t["keys"][l].data_ptr(), self.fp4[l % self.resident].data_ptr()
+            y.idx, y.gathered = t["idx"][l].data_ptr(), self.out[l].data_ptr()
+        ptrs = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l, _ in self.groups]
+        return {"tensors": t, "step": st, "layers": layers, "ptrs": ptrs, "ref": C.byref(st)}
 
-    def run_step(self, stream_ptr):
-        run, check, flags, ref = self.lib.pkv_step_run, self.capi.check, self.flags, self.step_ref
-        for ptr, (_, n) in zip(self.group_ptrs, self.groups):
-            check(run(ref, ptr, n, flags, stream_ptr))
+    def add_input_set(self):
+        self.sets.append(self._bind({k: getattr(self, k).clone() for k in self.INPUTS}))
+        return len(self.sets) - 1
+
+    def run_step(self, stream_ptr, which=0):
+        run, check, flags, b = self.lib.pkv_step_run, self.capi.check, self.flags, self.sets[which]
+        for ptr, (_, n) in zip(b["ptrs"], self.groups):
+            check(run(b["ref"], ptr, n, flags, stream_ptr))
 
     @property
     def launches_per_step(self):
@@ -243,13 +253,13 @@ class CpuWorkload:
     tables shuffled over a full-size host pool when host memory allows, else the largest power-of-two context that
     fits). layer_step() runs the layer's appends and gathers once with fresh index lists and returns the seconds."""
 
-    def __init__(self, threads: int):
+    def __init__(self, threads: int, small: bool = False):
         import psutil
 
         from oracle import oracle_lib as orc
         self.orc, self.threads = orc, threads
         avail = psutil.virtual_memory().available
-        context = CONTEXT
+        context = 8192 if small else CONTEXT
         while NSEQ * (context // RPP) * (PAGE_BYTES + FP4_PAGE_BYTES) * 1.3 > avail * 0.5 and context > 4096:
             context //= 2
         self.context, self.pps = context, context // RPP
@@ -312,7 +322,7 @@ def run_reference_arm(args):
         return
     from oracle import oracle_lib as orc
     threads = max(1, orc.hardware_threads())
-    wl = CpuWorkload(threads)
+    wl = CpuWorkload(threads, args.small)
     sample_layers = 2
     times = []
     for i in range(args.warmup + args.steps):
@@ -385,19 +395,40 @@ def run_ours(args):
         h2d = sum(t.numel() * t.element_size() for t in host.values())
         d2h = sample.numel() * sample.element_size()
 
-        def e2e_step():
-            for k, t in host.items():
-                getattr(wl, k).copy_(t, non_blocking=True)
-            wl.run_step(sp)
-            sample.copy_(wl.out[LAYERS - 1, 0], non_blocking=True)
+        # Two input sets: while the kernels of step s read set s % 2, the copy stream uploads step s + 1 into the
+        # other set (an engine with two steps in flight does the same: src/engine/step.hpp:8-11).
+        wl.add_input_set()
+        copy_stream = torch.cuda.Stream()
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        free = [torch.cuda.Event(), torch.cuda.Event()]
+        for ev in free:
+            ev.record(stream)
 
-        for _ in range(3):
-            e2e_step()
+        def upload(i):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(free[i])
+                for k, t in host.items():
+                    wl.sets[i]["tensors"][k].copy_(t, non_blocking=True)
+                ready[i].record(copy_stream)
+
+        def compute(i):
+            stream.wait_event(ready[i])
+            wl.run_step(sp, i)
+            sample.copy_(wl.out[LAYERS - 1, 0], non_blocking=True)
+            free[i].record(stream)
+
+        def e2e_steps(count):
+            upload(0)
+            for step_i in range(count):
+                if step_i + 1 < count:
+                    upload((step_i + 1) % 2)
+                compute(step_i % 2)
+
+        e2e_steps(3)
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record(stream)
-        for _ in range(args.steps):
-            e2e_step()
+        e2e_steps(args.steps)
         f1.record(stream)
         barrier()
         e2e_ms = f0.elapsed_time(f1)
@@ -450,7 +481,8 @@ def run_ours(args):
             line["e2e"] = {"value": round(total_bytes / (e2e_ms_max * 1e-3) / 1e9, 1), "unit": "GB/s",
                            "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]),
                            "note": "host rows, keys, index lists, block tables and chunk lists copied in from pinned "
-                                   "memory every step; one sequence's gathered tile of the last layer copied back"}
+                                   "memory every step (on a copy stream, one step ahead of the kernels); one sequence's "
+                                   "gathered tile of the last layer copied back"}
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle_lib as orc
             threads = max(1, orc.hardware_threads())
