@@ -411,3 +411,69 @@ def test_config3_chunked_prefill(pkv, cuda, variant):
             assert np.array_equal(tl.host(d_scales[l], np.uint8, h_scales[l].shape), h_scales[l]), ("fp8 scales", s0, l)
             assert np.array_equal(tl.host(outs[l], np.uint16, wants[l].shape), wants[l]), ("gather", s0, l)
         s0 = end
+
+
+def test_full_size_decode_step_properties(pkv, cuda):
+    """Benchmark configuration 2 at its full per-layer size (64 sequences x 131,072 rows, 131,072 pages of 73,728 B:
+    a 9.7 GB row pool and a 0.57 GB MXFP4 key pool, block tables shuffled), one layer, checked through properties
+    that do not need a CPU copy of the pool: every gathered row equals the pool row its block-table entry names (all
+    64 x 2048 entries, torch indexing on the device as the checker), the appended rows landed in the last row of each
+    sequence's last page, the stored MXFP4 keys decode to fake_quant_fp4 of the inputs (the reference's own round-trip
+    property, tools/kernel_test/indexer.hip:82-95), and running the step again changes nothing."""
+    torch = cuda
+    free, _ = torch.cuda.mem_get_info()
+    if free < 16 << 30:
+        pytest.skip("needs 16 GB of free device memory")
+    nseq, ctx, k, W, rpp = 64, 131072, 2048, tl.W, tl.RPP
+    pps, pages = ctx // rpp, nseq * (ctx // rpp)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(2)
+    pool = torch.empty(pages * rpp * W, dtype=torch.bfloat16, device="cuda")
+    pool.normal_(generator=g)
+    fp4 = torch.zeros(pages * tl.FP4_PAGE_BYTES, dtype=torch.uint8, device="cuda")
+    tables = torch.randperm(pages, generator=g, device="cuda").to(torch.int32).view(nseq, pps).contiguous()
+    chunks = torch.tensor([[s, ctx - 1, 1, s] for s in range(nseq)], dtype=torch.int32, device="cuda")
+    q_chunk = torch.arange(nseq, dtype=torch.int32, device="cuda")
+    q_vis = torch.full((nseq,), ctx, dtype=torch.int32, device="cuda")
+    rows = torch.randn(nseq, W, generator=g, device="cuda").to(torch.bfloat16)
+    keys = (torch.randn(nseq, 128, generator=g, device="cuda") * 4).to(torch.bfloat16)
+    idx = torch.rand(nseq, ctx, generator=g, device="cuda").topk(k, dim=1).indices.sort(dim=1).values.to(torch.int32)
+    idx[:, -1] = ctx - 1                                   # every query also selects the row appended in this step
+    idx[0, :7] = -1                                        # and a few masked entries
+    out = torch.full((nseq, k, W), float("nan"), dtype=torch.bfloat16, device="cuda")
+    step = capi.PkvStep()
+    step.width = step.row_stride = W
+    step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = rpp, pps, pages, 64
+    step.nchunks = step.T = step.Q = nseq
+    step.k = k
+    step.tables, step.chunks, step.q_chunk, step.q_visible = (tables.data_ptr(), chunks.data_ptr(), q_chunk.data_ptr(),
+                                                               q_vis.data_ptr())
+    layers = tl.make_layers(1)
+    y = layers[0]
+    y.rows, y.row_pool, y.keys, y.key_pool_fp4 = rows.data_ptr(), pool.data_ptr(), keys.data_ptr(), fp4.data_ptr()
+    y.idx, y.gathered = idx.data_ptr(), out.data_ptr()
+    flags = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_GATHER | capi.PKV_VARIANT_BULK
+    results = []
+    for _ in range(2):
+        capi.check(pkv.pkv_step_run(C.byref(step), layers, 1, flags, tl.stream_ptr(cuda)))
+        torch.cuda.synchronize()
+        results.append(out.view(torch.int16).clone())
+    assert tl.device_status(pkv) == 0
+    assert torch.equal(results[0], results[1])                                  # idempotent
+    pool2 = pool.view(-1, W)
+    last = tables[:, pps - 1].long() * rpp + rpp - 1
+    assert torch.equal(pool2[last].view(torch.int16), rows.view(torch.int16))   # appended rows landed
+    pos = idx.long().clamp(min=0)
+    phys = torch.gather(tables.long(), 1, pos // rpp) * rpp + pos % rpp
+    want = pool2[phys.view(-1)].view(nseq, k, W).clone()
+    want[idx < 0] = 0
+    assert torch.equal(results[1], want.view(torch.int16))                      # every gathered row
+    # MXFP4 keys: decode the appended key row of each sequence and compare with fake_quant_fp4 of the input
+    back = torch.empty(nseq, 128, dtype=torch.bfloat16, device="cuda")
+    for s in range(nseq):
+        capi.check(pkv.pkv_load_rows_fp4(fp4.data_ptr(), tables[s].data_ptr(), rpp, ctx - 1, 1, back[s].data_ptr(),
+                                         tl.stream_ptr(cuda)))
+    fake = keys.clone()
+    capi.check(pkv.pkv_fake_quant_fp4(fake.data_ptr(), 128, nseq, 128, 32, tl.stream_ptr(cuda)))
+    torch.cuda.synchronize()
+    assert torch.equal(back.view(torch.int16), fake.view(torch.int16))
