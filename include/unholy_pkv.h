@@ -100,6 +100,14 @@ PKV_API int pkv_copy(void* dst, const void* src, size_t bytes, pkv_stream_t stre
 PKV_API int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows_per_page, int row_stride, int width,
                     const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out, pkv_stream_t stream);
 
+/* The same gather over fp8 rows with dequantisation to bf16 — replaces the gather loop of the reference's GLM attention
+ * (src/kernels/glm_fast.hip:29-31,190-227) for rows stored by pkv_store_rows_fp8 / glm_store_latent: entry -> physical
+ * row -> e4m3 codes [width] and e8m0 scales [width/block] -> out bf16 [T][k][width] = code * 2^scale (exact in bf16);
+ * masked entries (< 0 or >= q_visible[t]) give zero rows. */
+PKV_API int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32_t* table, int rows_per_page, int width,
+                        int block, const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out,
+                        pkv_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Batched step: all chunks of a step (src/engine/step.hpp:20-26 Chunk, src/model/forward_ref.hpp:50-60 BatchDesc),
  * for 1..PKV_MAX_LAYERS layers in ONE launch. Replaces the reference's one launch per (chunk, layer, pool)
@@ -169,6 +177,12 @@ PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, i
 PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
 PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                           size_t scratch_words, pkv_stream_t stream);
+
+/* glm_idx_expand — src/kernels/glm_fast.hpp:115-122, src/kernels/glm_fast.hip:737-748,915-920. Selected pools
+ * device int32 [n][k] (a top-k's output: valid pools first) and the queries' positions pos [n] -> the compact token
+ * list idx [n][k*pool + pool-1]: the tokens of the min((p+1)/pool, k) valid pools, then the (p+1) % pool tokens of the
+ * query's incomplete pool, then -1. The result is an index list in the format the gather takes. */
+PKV_API int pkv_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, pkv_stream_t stream);
 
 /* pkv_topk_bf16 for callers that cannot hand the library any device memory of their own and cannot let it allocate
  * either — an engine thread that is recording its step into a CUDA graph (cudaMalloc is illegal while a stream is

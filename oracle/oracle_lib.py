@@ -38,6 +38,8 @@ _SIGS = {
     "orc_move_pages": (None, [_vp, _vp, _sz, _vp, _vp, _i, _i]),
     "orc_copy": (None, [_vp, _vp, _sz]),
     "orc_topk_bf16": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
+    "orc_idx_expand": (None, [_vp, _vp, _vp, _i, _i, _i]),
+    "orc_gather_rows_fp8": (None, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "orc_hardware_threads": (_i, []),
 }
 _lib = None
@@ -145,6 +147,21 @@ def topk_bf16(scores, n, k, threads=1):
     idx = np.empty((T, k), np.int32)
     lib().orc_topk_bf16(_p(scores), T, n, ld, k, _p(idx), threads)
     return idx
+
+
+def idx_expand(pools, pos, pool):
+    n, k = pools.shape
+    idx = np.empty((n, k * pool + pool - 1), np.int32)
+    lib().orc_idx_expand(_p(pools), _p(pos), _p(idx), n, k, pool)
+    return idx
+
+
+def gather_rows_fp8(codes, scales, table, rows_per_page, block, idx, q_visible):
+    T, k = idx.shape
+    width = codes.shape[1]
+    out = np.empty((T, k, width), np.uint16)
+    lib().orc_gather_rows_fp8(_p(codes), _p(scales), _p(table), rows_per_page, width, block, _p(idx), _p(q_visible), T, k, _p(out))
+    return out
 
 
 def hardware_threads() -> int:

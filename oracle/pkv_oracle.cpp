@@ -351,6 +351,39 @@ void orc_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, in
   });
 }
 
+// src/kernels/glm_fast.hip:737-748 (idx_expand_compact_kernel) — selected pools -> compact token list.
+void orc_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool) {
+  const int w = k * pool + pool - 1;
+  for (int t = 0; t < n; ++t) {
+    const int p = pos[t], full = (p + 1) / pool, valid = full < k ? full : k, tail = (p + 1) % pool;
+    for (int j = 0; j < w; ++j) {
+      int v = -1;
+      if (j < valid * pool) v = pools[size_t(t) * k + j / pool] * pool + j % pool;
+      else if (j < valid * pool + tail) v = p + 1 - tail + (j - valid * pool);
+      idx[size_t(t) * w + j] = v;
+    }
+  }
+}
+
+// src/kernels/glm_fast.hip:190-227 (the gather loop of mla_attn_kernel): entry -> row id (glm_fast.hip:29-31), codes
+// dequantised on the fly as bf16(e4m3 * 2^scale) (:203-218), masked entries zero (:219-222).
+void orc_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32_t* table, int rows_per_page, int width,
+                         int block, const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out) {
+  const int nb = width / block;
+  for (int t = 0; t < T; ++t)
+    for (int e = 0; e < k; ++e) {
+      const int row = idx[size_t(t) * k + e];
+      uint16_t* dst = out + (size_t(t) * k + e) * size_t(width);
+      if (row < 0 || row >= q_visible[t]) {
+        std::memset(dst, 0, size_t(width) * 2);
+        continue;
+      }
+      const size_t rid = phys_row(table, rows_per_page, row);
+      for (int c = 0; c < width; ++c)
+        dst[c] = f32_to_bf16(e4m3_to_f32(codes[rid * size_t(width) + c]) * e8m0_to_f32(scales[rid * size_t(nb) + c / block]));
+    }
+}
+
 int orc_hardware_threads() { return int(std::thread::hardware_concurrency()); }
 
 }  // extern "C"

@@ -477,3 +477,38 @@ def test_full_size_decode_step_properties(pkv, cuda):
     capi.check(pkv.pkv_fake_quant_fp4(fake.data_ptr(), 128, nseq, 128, 32, tl.stream_ptr(cuda)))
     torch.cuda.synchronize()
     assert torch.equal(back.view(torch.int16), fake.view(torch.int16))
+
+
+@pytest.mark.parametrize("width,block,rpp,k", [(512, 64, 256, 2051), (128, 32, 64, 100), (256, 128, 64, 64)])
+def test_gather_rows_fp8_dequant(pkv, cuda, width, block, rpp, k):
+    """fp8 rows stored by pkv_store_rows_fp8, gathered and dequantised: equals the oracle's bf16(e4m3 * 2^scale) per
+    entry, zero rows for masked entries; also equals fake_quant_fp8 of the original rows (store then gather-dequant is
+    the reference's fake quantisation: src/kernels/glm_fast.hip:203-218 vs src/kernels/ref_elem.hip:18-41)."""
+    g = tl.rng(19)
+    pages, T = 5, 3
+    n = pages * rpp - 3
+    table = shuffled_table(g, pages)
+    rows = tl.outlier_rows(g, n, width)
+    codes = np.zeros((pages * rpp, width), np.uint8)
+    scales = np.zeros((pages * rpp, width // block), np.uint8)
+    orc.store_rows_fp8(rows, block, codes, scales, table, rpp, 0)
+    vis = np.array([n, n // 2, 1], np.int32)
+    idx = np.full((T, k), -1, np.int32)
+    for t in range(T):
+        m = min(k - 5, n)
+        idx[t, :m] = g.choice(n, size=m, replace=m > n)
+    want = orc.gather_rows_fp8(codes, scales, table, rpp, block, idx, vis)
+    fake = rows.copy()
+    orc.fake_quant_fp8(fake, width, block)
+    sel = idx[0] >= 0
+    assert np.array_equal(want[0][sel], fake[idx[0][sel]])
+    d_rows, d_t, d_idx, d_vis = tl.dev(cuda, rows), tl.dev(cuda, table), tl.dev(cuda, idx), tl.dev(cuda, vis)
+    d_c = cuda.zeros(codes.size, dtype=cuda.uint8, device="cuda")
+    d_s = cuda.zeros(scales.size, dtype=cuda.uint8, device="cuda")
+    d_out = cuda.full((want.size * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    st = tl.stream_ptr(cuda)
+    capi.check(pkv.pkv_store_rows_fp8(d_rows.data_ptr(), n, width, block, d_c.data_ptr(), d_s.data_ptr(), d_t.data_ptr(), rpp, 0, st))
+    capi.check(pkv.pkv_gather_rows_fp8(d_c.data_ptr(), d_s.data_ptr(), d_t.data_ptr(), rpp, width, block, d_idx.data_ptr(),
+                                       d_vis.data_ptr(), T, k, d_out.data_ptr(), st))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)

@@ -103,3 +103,41 @@ def test_topk_argument_errors(pkv):
     assert pkv.pkv_topk_bf16(16, 1, 10, 4, 4, 16, 16, 1 << 20, None) == capi.PKV_ERR_ARG
     assert pkv.pkv_topk_bf16(16, 1, 10, 10, 4, 16, None, 0, None) == capi.PKV_ERR_ARG
     assert b"scratch" in pkv.pkv_last_error()
+
+
+def expand_case(g, n, k, pool):
+    pos = g.integers(0, 4 * k * pool, size=n).astype(np.int32)
+    pos[0], pos[-1] = 0, k * pool * 3 + pool - 2
+    pools = np.full((n, k), -1, np.int32)
+    for t in range(n):
+        full = (int(pos[t]) + 1) // pool
+        m = min(full, k)
+        pools[t, :m] = g.choice(full, size=m, replace=False)
+    return pools, pos
+
+
+def test_oracle_idx_expand_matches_contract():
+    g = tl.rng(73)
+    for n, k, pool in ((9, 512, 4), (3, 5, 4), (4, 7, 1), (2, 3, 8)):
+        pools, pos = expand_case(g, n, k, pool)
+        got = orc.idx_expand(pools, pos, pool)
+        assert got.shape == (n, k * pool + pool - 1)
+        for t in range(n):
+            p = int(pos[t])
+            valid, tail = min((p + 1) // pool, k), (p + 1) % pool
+            want = [int(pools[t, j // pool]) * pool + j % pool for j in range(valid * pool)] + list(range(p + 1 - tail, p + 1))
+            assert list(got[t, :len(want)]) == want and (got[t, len(want):] == -1).all()
+            assert len(want) == valid * pool + tail          # glm_sel_count (src/kernels/glm_fast.hpp:118-121)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,k,pool", [(64, 512, 4), (3, 5, 4), (4, 7, 1), (1000, 16, 8)])
+def test_idx_expand_gpu(pkv, cuda, n, k, pool):
+    g = tl.rng(74)
+    pools, pos = expand_case(g, n, k, pool)
+    want = orc.idx_expand(pools, pos, pool)
+    d_pools, d_pos = tl.dev(cuda, pools), tl.dev(cuda, pos)
+    d_idx = cuda.full((want.size * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_idx_expand(d_pools.data_ptr(), d_pos.data_ptr(), d_idx.data_ptr(), n, k, pool, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_idx, np.int32, want.shape), want)

@@ -55,11 +55,13 @@ _SIGS = {
     "pkv_store_rows_fp8": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "pkv_copy": (_i, [_vp, _vp, _sz, _vp]),
     "pkv_gather_rows": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp]),
+    "pkv_gather_rows_fp8": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp]),
     "pkv_step_run": (_i, [C.POINTER(PkvStep), C.POINTER(PkvLayer), _i, _i, _vp]),
     "pkv_topk_scratch_words": (_sz, [_i, _i, _i]),
     "pkv_topk_bf16": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp, _sz, _vp]),
     "pkv_topk_static_scratch_words": (_sz, []),
     "pkv_topk_bf16_static": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp]),
+    "pkv_idx_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_copy_pages": (_i, [C.POINTER(PkvPoolDesc), _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_device_alloc": (_i, [C.POINTER(_vp), _sz]),
     "pkv_device_free": (_i, [_vp]),

@@ -75,6 +75,13 @@ inline void glm_store_latent(const bf16* lat, GlmPaged pg, int s0, int n, cudaSt
                                reinterpret_cast<pkv_stream_t>(st)), "glm_store_latent");
 }
 
+// The gather of the reference's GLM attention over fp8 latent rows (src/kernels/glm_fast.hip:190-227) as a call of its
+// own: idx [T][k] positions of the slot behind `pg`, dequantised to bf16 [T][k][512].
+inline void glm_gather_latent(GlmPaged pg, const int32_t* idx, const int32_t* visible, int T, int k, bf16* out, cudaStream_t st) {
+  pkv_throw(pkv_gather_rows_fp8(pg.lat, pg.lat_s, pg.table, kGlmPageRows, 512, 64, idx, visible, T, k, out,
+                                reinterpret_cast<pkv_stream_t>(st)), "glm_gather_latent");
+}
+
 // src/kernels/ref.hpp:90.
 inline void copy_kernel(void* dst, const void* src, size_t bytes, cudaStream_t st) {
   pkv_throw(pkv_copy(dst, src, bytes, reinterpret_cast<pkv_stream_t>(st)), "copy_kernel");
@@ -86,6 +93,20 @@ inline void gather_rows(PagedRows src, int width, const int32_t* idx, const int3
                         cudaStream_t st) {
   pkv_throw(pkv_gather_rows(src.pool, src.table, src.rows_per_page, src.row_stride, width, idx, visible, T, k, out,
                             reinterpret_cast<pkv_stream_t>(st)), "gather_rows");
+}
+
+// src/kernels/indexer.hpp:74-94 (top-k with scratch) and src/kernels/glm_fast.hpp:115-122.
+inline size_t topk_scratch_words(int rows, int n, int k) { return pkv_topk_scratch_words(rows, n, k); }
+inline void topk_bf16(const uint16_t* scores, int T, int n, int k, int32_t* idx, cudaStream_t st, uint32_t* scratch,
+                      size_t scratch_words) {
+  pkv_throw(pkv_topk_bf16(scores, T, n, n, k, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)), "topk_bf16");
+}
+inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
+  pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
+}
+inline int glm_sel_count(int p, int k, int pool) {
+  const int full = (p + 1) / pool;
+  return (full < k ? full : k) * pool + (p + 1) % pool;
 }
 
 }  // namespace unholy::kernels

@@ -804,6 +804,52 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
   }
 }
 
+// Gather with dequantisation for fp8 rows (the gather loop of src/kernels/glm_fast.hip:190-227): entry -> physical
+// row -> e4m3 codes [width] and one e8m0 scale per `block` values -> bf16 = code * 2^scale (exact). One thread per 16
+// codes: a 16-byte load, sixteen decodes, two 16-byte stores. Masked entries give zero rows.
+__global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                                         OneTable tb, int width, int block, const int32_t* __restrict__ idx,
+                                                         const int32_t* __restrict__ q_visible, int T, int k,
+                                                         uint16_t* __restrict__ out) {
+  __shared__ long long s_rid[kGatherRows];
+  const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows, upr = width >> 4, nb = width / block;
+  const long long total_tiles = (long long)T * tiles_per_q;
+  for (long long w = blockIdx.x; w < total_tiles; w += gridDim.x) {
+    const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
+    if (threadIdx.x < kGatherRows) {
+      const int e = e0 + int(threadIdx.x);
+      long long rid = -1;
+      if (e < k) {
+        const int row = __ldg(&idx[size_t(t) * k + e]);
+        if (row >= 0 && row < __ldg(&q_visible[t])) rid = (long long)one_row(tb, row);
+      }
+      s_rid[threadIdx.x] = rid;
+    }
+    __syncthreads();
+    const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
+    uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
+    for (int u = threadIdx.x; u < total; u += blockDim.x) {
+      const int r = u / upr, c = u - r * upr;
+      const long long rid = s_rid[r];
+      uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (rid >= 0) {
+        const uint4 q = ld_stream(reinterpret_cast<const uint4*>(codes + size_t(rid) * width) + c);
+        const float sc = pkv::e8m0_bits_to_f32(__ldg(&scales[size_t(rid) * nb + (c * 16) / block]));
+        const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t code = (qs[i >> 2] >> (8 * (i & 3))) & 0xffu;
+          const uint32_t b = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(code) * sc);
+          w16[i >> 1] |= b << (16 * (i & 1));
+        }
+      }
+      st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
+      st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void __launch_bounds__(256) copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n) {
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
@@ -1173,6 +1219,24 @@ int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows_per_pag
   gather_one_kernel<<<grid, kVecThreads, 0, stream>>>(pool, OneTable{table, rows_per_page}, row_stride, width, idx,
                                                       q_visible, T, k, out);
   PKV_LAUNCH_CHECK("gather_one_kernel");
+  return PKV_OK;
+}
+
+int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32_t* table, int rows_per_page, int width,
+                        int block, const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out,
+                        pkv_stream_t stream) {
+  if (T <= 0 || k <= 0) return PKV_OK;
+  if (!codes || !scales || !table || !idx || !q_visible || !out) return fail(PKV_ERR_ARG, "pkv_gather_rows_fp8: null pointer");
+  if (const int rc = check_quant_shape(T, width, block, "pkv_gather_rows_fp8")) return rc;
+  if (width <= 0 || width % 16 != 0 || block % 16 != 0 || rows_per_page <= 0)
+    return fail(PKV_ERR_ARG, "pkv_gather_rows_fp8: width must be a positive multiple of 16");
+  if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, "pkv_gather_rows_fp8: codes and out must be 16-byte aligned");
+  const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 8)));
+  gather_fp8_kernel<<<grid, 256, 0, stream>>>(codes, scales, OneTable{table, rows_per_page}, width, block, idx, q_visible, T, k, out);
+  PKV_LAUNCH_CHECK("gather_fp8_kernel");
   return PKV_OK;
 }
 

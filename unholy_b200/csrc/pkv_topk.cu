@@ -329,6 +329,21 @@ __global__ void __launch_bounds__(1024) sort_pairs_kernel(const uint32_t* __rest
   if (i1 < k) out[i1] = uint32_t(i1) < want ? int32_t(0xffffffffu - uint32_t(b & 0xffffffffull)) : -1;
 }
 
+// glm_idx_expand (src/kernels/glm_fast.hip:737-748): selected pools -> compact token list, one thread per entry.
+__global__ void __launch_bounds__(256) idx_expand_kernel(const int32_t* __restrict__ pools, const int32_t* __restrict__ pos,
+                                                         int32_t* __restrict__ idx, int n, int k, int pool) {
+  const int w = k * pool + pool - 1;
+  const long long total = (long long)n * w;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / w), j = int(i - (long long)t * w), p = __ldg(&pos[t]);
+    const int full = (p + 1) / pool, valid = full < k ? full : k, tail = (p + 1) % pool;
+    int v = -1;
+    if (j < valid * pool) v = __ldg(&pools[size_t(t) * k + j / pool]) * pool + j % pool;
+    else if (j < valid * pool + tail) v = p + 1 - tail + (j - valid * pool);
+    idx[i] = v;
+  }
+}
+
 }  // namespace pkv_topk
 
 extern thread_local std::string pkv_g_err;  // defined in pkv_kernels.cu: what pkv_last_error() returns
@@ -459,6 +474,28 @@ int pkv_topk_bf16_static(const uint16_t* scores, int T, int n, long long ld, int
   uint32_t* scratch = nullptr;
   if (const int rc = static_scratch(&scratch, pkv_g_err)) return rc;
   return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
+}
+
+int pkv_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, pkv_stream_t stream) {
+  if (n < 0 || k < 0 || pool <= 0) {
+    pkv_g_err = "pkv_idx_expand: bad shape";
+    return PKV_ERR_ARG;
+  }
+  const long long total = (long long)n * ((long long)k * pool + pool - 1);
+  if (total == 0) return PKV_OK;
+  if (!pools || !pos || !idx) {
+    pkv_g_err = "pkv_idx_expand: null pointer";
+    return PKV_ERR_ARG;
+  }
+  const long long blocks = (total + 255) / 256;
+  pkv_topk::idx_expand_kernel<<<unsigned(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pools, pos, idx, n, k, pool);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    pkv_g_err = std::string("idx_expand launch: ") + cudaGetErrorString(e);
+    return PKV_ERR_CUDA;
+  }
+  return PKV_OK;
 }
 
 }  // extern "C"
