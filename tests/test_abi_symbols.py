@@ -45,3 +45,35 @@ def test_product_package_does_not_touch_the_oracle():
     for p in (ROOT / "unholy_b200").rglob("*"):
         if p.suffix in (".py", ".cu", ".cuh", ".cpp", ".hpp", ".h"):
             assert "oracle" not in p.read_text(), f"{p} mentions the oracle"
+
+
+def test_step_run_validates_before_touching_the_device(pkv):
+    """Shape, pointer and alignment errors are reported by the host code, so they can be checked without a GPU."""
+    st = capi.PkvStep()
+    layers = (capi.PkvLayer * 1)()
+    st.width, st.row_stride, st.rows_per_page, st.max_pages_per_seq = 576, 576, 64, 8
+    st.nchunks, st.T, st.Q, st.k = 1, 1, 1, 8
+    flags = capi.PKV_DO_ROWS | capi.PKV_DO_GATHER
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG       # no tables / chunks
+    assert b"tables and chunks" in pkv.pkv_last_error()
+    st.tables = st.chunks = 4096
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG       # gather without q arrays
+    st.q_chunk = st.q_visible = 4096
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG       # layer lacks idx / gathered
+    st.width = 570
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG       # width not a multiple of 8
+    st.width = 576
+    layers[0].rows = layers[0].row_pool = layers[0].idx = layers[0].gathered = 4096
+    layers[0].row_pool = 4100                                                                  # off the 16-byte grid
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG
+    assert b"16-byte aligned" in pkv.pkv_last_error()
+    st.fp8_block = 48
+    layers[0].row_pool = 4096
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, flags | capi.PKV_DO_KEYS_FP8, None) == capi.PKV_ERR_ARG
+    assert pkv.pkv_step_run(C.byref(st), layers, 0, flags, None) == capi.PKV_OK            # nothing to do
+    assert pkv.pkv_copy_pages(None, 0, None, None, 0, 0, 0, None) == capi.PKV_OK
+    descs = (capi.PkvPoolDesc * 1)()
+    descs[0].src_base = descs[0].dst_base = 4096
+    descs[0].page_bytes = 100                                                                  # not a multiple of 16
+    assert pkv.pkv_copy_pages(descs, 1, 4096, 4096, 1, 0, 0, None) == capi.PKV_ERR_ARG
+    assert pkv.pkv_tune(99, 0) == capi.PKV_ERR_ARG

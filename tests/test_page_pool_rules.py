@@ -174,3 +174,17 @@ def test_migrate_between_pools(pkv):
     assert len(pages_of(pkv, a, big)) == 16
     for p in (a, b, tiny):
         pkv.pkv_pool_destroy(p)
+
+
+def test_cpp_class_api():
+    """The pool through its C++ class, as a C++ engine would use it (tests/cpp/page_pool_test.cpp), compiled with g++."""
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    exe = root / "tests" / "cpp" / "page_pool_test.bin"
+    cmd = ["g++", "-std=c++17", "-O1", "-I", str(root), str(root / "tests/cpp/page_pool_test.cpp"),
+           str(root / "unholy_b200/csrc/page_pool.cpp"), "-o", str(exe)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0 and "all ok" in run.stdout, run.stdout + run.stderr

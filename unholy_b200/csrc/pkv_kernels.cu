@@ -386,7 +386,7 @@ __device__ void gather_tile_vec(const StepParams& P, const pkv_layer& ly, int ti
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(kVecThreads) step_vec_kernel(const __grid_constant__ StepParams P) {
+__global__ void __launch_bounds__(kVecThreads, 3) step_vec_kernel(const __grid_constant__ StepParams P) {
   __shared__ long long s_rid[kAppendRows];
   __shared__ const uint4* s_src[kGatherRows];
   const int per_layer = P.append_tiles + P.gather_tiles;
@@ -1193,7 +1193,11 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   if (vec_work > 0) {
     const DeviceInfo& d = device_info();
     const int sms = d.ok ? d.sms : 148;
-    const int grid = int(std::max<long long>(1, std::min<long long>(vec_work, (long long)sms * grid_mult)));
+    // One wave: as many CTAs as are resident at once (asked of the runtime, capped by the tuning knob).
+    int resident = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, step_vec_kernel, kVecThreads, 0) != cudaSuccess || resident < 1) resident = 1;
+    resident = std::min(resident, std::max(1, grid_mult));
+    const int grid = int(std::max<long long>(1, std::min<long long>(vec_work, (long long)sms * resident)));
     step_vec_kernel<<<grid, kVecThreads, 0, stream>>>(P);
     PKV_LAUNCH_CHECK("step_vec_kernel");
   }
