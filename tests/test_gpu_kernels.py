@@ -512,3 +512,23 @@ def test_gather_rows_fp8_dequant(pkv, cuda, width, block, rpp, k):
                                        d_vis.data_ptr(), T, k, d_out.data_ptr(), st))
     cuda.cuda.synchronize()
     assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
+
+
+def test_copy_between_device_and_pinned_host(pkv, cuda):
+    """The snapshot save / restore primitive: the reference's state_copies moves slot state between device memory and
+    pinned host staging with copy_kernel, i.e. with ordinary loads and stores issued by SMs
+    (src/engine/resident.hip:545-557, src/kernels/ref.hpp:87-90). Same here: device -> pinned host -> device."""
+    torch = cuda
+    g = tl.rng(20)
+    n = (7 << 20) + 4096
+    src = g.integers(0, 256, size=n, dtype=np.uint8)
+    d_src = tl.dev(cuda, src)
+    h_snap = torch.empty(n, dtype=torch.uint8).pin_memory()
+    h_snap.fill_(0x5A)
+    d_back = torch.full((n,), 0xA5, dtype=torch.uint8, device="cuda")
+    st = tl.stream_ptr(cuda)
+    capi.check(pkv.pkv_copy(h_snap.data_ptr(), d_src.data_ptr(), n, st))       # save
+    capi.check(pkv.pkv_copy(d_back.data_ptr(), h_snap.data_ptr(), n, st))      # restore (stream-ordered after the save)
+    torch.cuda.synchronize()
+    assert np.array_equal(h_snap.numpy(), src)
+    assert np.array_equal(d_back.cpu().numpy(), src)
