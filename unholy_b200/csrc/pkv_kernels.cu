@@ -862,9 +862,11 @@ __global__ void __launch_bounds__(256) copy16_kernel(uint4* __restrict__ dst, co
     st_stream(dst + i + 3 * stride, d);
   }
   for (; i < n; i += stride) st_stream(dst + i, ld_stream(src + i));
+  __threadfence_system();  // as the reference's copy kernels: a flag written after this kernel orders the data for any observer
 }
 __global__ void __launch_bounds__(256) copy1_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, size_t n) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) dst[i] = src[i];
+  __threadfence_system();
 }
 
 // Page moves: work item = (pool, pair, 16 KB piece of the page).
