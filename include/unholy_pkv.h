@@ -173,7 +173,8 @@ PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, i
  * scores ordered (score descending, index ascending), ties at the threshold to the lowest indices, -1 padded; -inf is
  * never selected. k <= 4096. Rows are split over several CTAs; `scratch` is device memory of at least
  * pkv_topk_scratch_words(T, n, k) uint32 words, 8-byte aligned (the reference's topk_split_scratch_words). Its
- * contents need not be initialised and are garbage afterwards; two calls that overlap on the GPU must not share it. */
+ * contents need not be initialised (the call clears the few words that must start at zero with a memset on the
+ * stream) and are garbage afterwards; two calls that overlap on the GPU must not share it. */
 PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
 PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                           size_t scratch_words, pkv_stream_t stream);
@@ -191,10 +192,10 @@ PKV_API int pkv_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* id
  * only inputs and outputs; the scratch is a 4 MiB array compiled into the library (pkv_topk_static_scratch_words()
  * uint32 words = 1,048,576), which every GPU that loads the library keeps until the process exits. It calls no
  * cudaMalloc, cudaFree or other allocating routine. Shapes whose pkv_topk_scratch_words(T, n, k) exceeds the built-in
- * size are refused with PKV_ERR_LIMIT (64 rows x 131,072 keys x k = 2048 needs 786,432 words and fits). The first
+ * size are refused with PKV_ERR_LIMIT (64 rows x 131,072 keys x k = 2048 needs 788,992 words and fits). The first
  * call on each device looks the array's device address up (cudaGetSymbolAddress), so make that first call outside any
  * stream capture. Every call on a device shares the one array: it keeps the previous call's contents (harmless: each
- * call overwrites what it reads), and two calls that overlap on the GPU (different streams) race — serialise them.
+ * call clears or overwrites what it reads), and two calls that overlap on the GPU (different streams) race — serialise them.
  * Results are identical to pkv_topk_bf16's. Nothing is stated here about recording this call itself into a graph. */
 PKV_API size_t pkv_topk_static_scratch_words(void);
 PKV_API int pkv_topk_bf16_static(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream);

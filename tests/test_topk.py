@@ -97,7 +97,7 @@ def test_topk_feeds_the_gather(pkv, cuda):
 
 
 def test_topk_argument_errors(pkv):
-    assert pkv.pkv_topk_scratch_words(64, 131072, 2048) == 64 * 16 * 512 + 64 * 2048 * 2
+    assert pkv.pkv_topk_scratch_words(64, 131072, 2048) == 64 * 16 * 512 + 64 * 8 + 64 * 16 * 2 + 64 * 2048 * 2
     assert pkv.pkv_topk_bf16(None, 0, 10, 10, 4, None, None, 0, None) == capi.PKV_OK
     assert pkv.pkv_topk_bf16(16, 1, 10, 10, 5000, 16, 16, 1 << 20, None) == capi.PKV_ERR_LIMIT
     assert pkv.pkv_topk_bf16(16, 1, 10, 4, 4, 16, 16, 1 << 20, None) == capi.PKV_ERR_ARG

@@ -33,17 +33,22 @@ constexpr uint32_t kNegInfKey = 0x007Fu;  // key16 of the bf16 pattern 0xFF80
 
 __device__ __forceinline__ uint32_t key16(uint32_t b) { return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u); }
 
-// Scratch layout (uint32 words): hist[row][slice][2][256], then candidates as uint64 [row][k] (8-byte aligned).
+// Scratch layout (uint32 words): per-slice histograms hist[row][slice][2][256]; per-row results info[row][8]
+// (kWant.. below; the two arrival counters are the only words that must be zero when a call starts: the launcher
+// clears info); per-slice output offsets offs[row][slice][2]; candidates as uint64 [row][k] (8-byte aligned).
+enum Info { kWant = 0, kHiBin = 1, kNeed1 = 2, kLoBin = 3, kNeedTies = 4, kAboveTotal = 5, kArrived0 = 6, kArrived1 = 7 };
 struct Layout {
   int slices;
-  size_t hist_words, cand_offset_words, total_words;
+  size_t hist_words, info_offset, offs_offset, cand_offset_words, total_words;
 };
 __host__ __device__ inline Layout layout(int T, int n, int k) {
   Layout l;
   l.slices = (n + kSlice - 1) / kSlice;
   if (l.slices < 1) l.slices = 1;
   l.hist_words = size_t(T) * l.slices * 512;
-  l.cand_offset_words = (l.hist_words + 1) & ~size_t(1);
+  l.info_offset = l.hist_words;
+  l.offs_offset = l.info_offset + size_t(T) * 8;
+  l.cand_offset_words = (l.offs_offset + size_t(T) * l.slices * 2 + 1) & ~size_t(1);
   l.total_words = l.cand_offset_words + size_t(T) * k * 2;
   return l;
 }
@@ -111,31 +116,32 @@ __device__ void pick_bin(const uint32_t* h, int need_in, int k, uint32_t* s_wsum
 __device__ void sum_hist(const uint32_t* __restrict__ row_hist, int slices, int which, uint32_t* out) {
   for (int b = threadIdx.x; b < 256; b += blockDim.x) {
     uint32_t s = 0;
-    for (int sl = 0; sl < slices; ++sl) s += __ldg(&row_hist[(size_t(sl) * 2 + which) * 256 + b]);
+    for (int sl = 0; sl < slices; ++sl) s += __ldcg(&row_hist[(size_t(sl) * 2 + which) * 256 + b]);
     out[b] = s;
   }
   __syncthreads();
 }
 
-// Pass 1 (which = 0): histogram of the high key byte over the slice's valid keys. Pass 2 (which = 1): the threshold's
-// high byte is derived from the summed pass-1 histograms, then the low byte is histogrammed over the keys that share it.
+// Pass 1 (which = 0): histogram of the high key byte over the slice's valid keys. Pass 2 (which = 1): histogram of
+// the low byte over the keys whose high byte is the threshold's. In both, the CTA that finishes LAST for its row (an
+// arrival counter; writers fence before they count, the last one fences before it reads) folds the row's per-slice
+// histograms once for everybody: after pass 1 it leaves want / high threshold byte / remaining need in info[row];
+// after pass 2 the low byte, the number of threshold ties to take, and for every slice where its keys above the
+// threshold and its ties start in the output. No other CTA repeats that work.
 __global__ void __launch_bounds__(kThreads) hist_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
-                                                        uint32_t* __restrict__ scratch, int slices, int which) {
+                                                        uint32_t* __restrict__ scratch, Layout L, int which) {
   asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
-  __shared__ uint32_t hist[256], total[256], s_wsum[8], s_out[4];
-  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x;
+  __shared__ uint32_t hist[256], total[256], s_wsum[kThreads / 32], s_out[4], s_last;
+  __shared__ uint32_t s_slice_above[kMaxSlices], s_slice_ties[kMaxSlices];
+  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, slices = L.slices;
   uint32_t* row_hist = scratch + size_t(row) * slices * 512;
+  uint32_t* info = scratch + L.info_offset + size_t(row) * 8;
   const uint16_t* r = scores + size_t(row) * ld;
   const int lo = sl * kSlice, hi = min(n, lo + kSlice);
   uint32_t key[kPerThread];
-  load_keys(r, lo + tid * kPerThread, hi, key);  // issued before the threshold is known: the loads overlap the prologue
-  uint32_t hi_bin = 0;
-  if (which == 1) {
-    sum_hist(row_hist, slices, 0, total);
-    pick_bin(total, -1, k, s_wsum, s_out);
-    hi_bin = s_out[0];
-  }
+  load_keys(r, lo + tid * kPerThread, hi, key);
+  const uint32_t hi_bin = which == 1 ? __ldcg(&info[kHiBin]) : 0u;
   for (int b = tid; b < 256; b += kThreads) hist[b] = 0;
   __syncthreads();
   // Plain shared-memory atomics: measured faster here than electing one lane per bin (match.any or ballot rounds cost
@@ -148,46 +154,73 @@ __global__ void __launch_bounds__(kThreads) hist_kernel(const uint16_t* __restri
   }
   __syncthreads();
   for (int b = tid; b < 256; b += kThreads) row_hist[(size_t(sl) * 2 + which) * 256 + b] = hist[b];
-}
-
-// Collect: every slice writes its keys above the threshold and its share of the threshold ties (lowest indices first
-// across the whole row) into the row's candidate array at offsets known from the per-slice histograms. Each thread owns
-// 16 consecutive keys, so index order is thread order and one block-wide scan places everything.
-__global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
-                                                           uint32_t* __restrict__ scratch, int slices, size_t cand_offset) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
-  __shared__ uint32_t total[256], s_wsum[kThreads / 32], s_out[4];
-  __shared__ uint32_t s_slice_above[kMaxSlices], s_slice_ties[kMaxSlices];
-  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t* row_hist = scratch + size_t(row) * slices * 512;
-  unsigned long long* cand = reinterpret_cast<unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
-  const uint16_t* r = scores + size_t(row) * ld;
-  const int lo = sl * kSlice, hi = min(n, lo + kSlice), base = lo + tid * kPerThread;
-  uint32_t key[kPerThread];
-  load_keys(r, base, hi, key);
-  sum_hist(row_hist, slices, 0, total);
-  pick_bin(total, -1, k, s_wsum, s_out);
-  const uint32_t hi_bin = s_out[0], need1 = s_out[1], want = s_out[3];
+  __threadfence();
   __syncthreads();
-  if (want == 0) return;
-  sum_hist(row_hist, slices, 1, total);
+  if (tid == 0) s_last = atomicAdd(&info[which == 0 ? kArrived0 : kArrived1], 1u) == uint32_t(slices - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  sum_hist(row_hist, slices, which, total);
+  if (which == 0) {
+    pick_bin(total, -1, k, s_wsum, s_out);
+    if (tid == 0) {
+      info[kWant] = s_out[3];
+      info[kHiBin] = s_out[0];
+      info[kNeed1] = s_out[1];
+    }
+    return;
+  }
+  const uint32_t need1 = __ldcg(&info[kNeed1]);
   pick_bin(total, int(need1), k, s_wsum, s_out);
   const uint32_t lo_bin = s_out[0], need_ties = s_out[1];
-  const uint32_t thr = (hi_bin << 8) | lo_bin;
-  // Keys above the threshold come first (any order: the sort follows), then the ties in index order. One warp per
-  // slice sums that slice's bins above the threshold.
+  // One warp per slice: that slice's keys above the threshold and its ties.
   for (int s2 = warp; s2 < slices; s2 += kThreads / 32) {
     const uint32_t* h0 = row_hist + (size_t(s2) * 2) * 256;
     const uint32_t* h1 = h0 + 256;
     uint32_t a = 0;
-    for (uint32_t b = lane; b < 256; b += 32) a += (b > hi_bin ? __ldg(&h0[b]) : 0u) + (b > lo_bin ? __ldg(&h1[b]) : 0u);
+    for (uint32_t b = lane; b < 256; b += 32) a += (b > hi_bin ? __ldcg(&h0[b]) : 0u) + (b > lo_bin ? __ldcg(&h1[b]) : 0u);
     for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
     if (lane == 0) {
       s_slice_above[s2] = a;
-      s_slice_ties[s2] = __ldg(&h1[lo_bin]);
+      s_slice_ties[s2] = __ldcg(&h1[lo_bin]);
     }
   }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* offs = scratch + L.offs_offset + size_t(row) * slices * 2;
+    uint32_t above = 0, ties = 0;
+    for (int s2 = 0; s2 < slices; ++s2) {
+      offs[2 * s2] = above;
+      offs[2 * s2 + 1] = ties;
+      above += s_slice_above[s2];
+      ties += s_slice_ties[s2];
+    }
+    info[kLoBin] = lo_bin;
+    info[kNeedTies] = need_ties;
+    info[kAboveTotal] = above;
+  }
+}
+
+// Collect: every slice writes its keys above the threshold and its share of the threshold ties (lowest indices first
+// across the whole row) into the row's candidate array at the offsets pass 2 left in scratch. Each thread owns 16
+// consecutive keys, so index order is thread order and one block-wide scan places everything.
+__global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __restrict__ scores, int n, long long ld, int k,
+                                                           uint32_t* __restrict__ scratch, Layout L) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
+  __shared__ uint32_t s_wsum[kThreads / 32];
+  const int row = blockIdx.y, sl = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t* info = scratch + L.info_offset + size_t(row) * 8;
+  const uint32_t* offs = scratch + L.offs_offset + (size_t(row) * L.slices + sl) * 2;
+  unsigned long long* cand = reinterpret_cast<unsigned long long*>(scratch + L.cand_offset_words) + size_t(row) * k;
+  const uint16_t* r = scores + size_t(row) * ld;
+  const int lo = sl * kSlice, hi = min(n, lo + kSlice), base = lo + tid * kPerThread;
+  uint32_t key[kPerThread];
+  load_keys(r, base, hi, key);
+  const uint32_t want = __ldg(&info[kWant]);
+  if (want == 0) return;
+  const uint32_t thr = (__ldg(&info[kHiBin]) << 8) | __ldg(&info[kLoBin]), need_ties = __ldg(&info[kNeedTies]);
+  const uint32_t above_total = __ldg(&info[kAboveTotal]), above_before = __ldg(&offs[0]), ties_before = __ldg(&offs[1]);
   // This thread's counts, packed (above << 16 | ties; a slice holds 8192 keys), and their block-wide exclusive scan.
   uint32_t cnt = 0;
 #pragma unroll
@@ -198,19 +231,10 @@ __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __res
     const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += t;
   }
-  __syncthreads();  // s_wsum was last read inside pick_bin
   if (lane == 31) s_wsum[warp] = incl;
   __syncthreads();
   uint32_t before = incl - cnt;
   for (int w = 0; w < warp; ++w) before += s_wsum[w];
-  uint32_t above_before = 0, ties_before = 0, above_total = 0;
-  for (int s2 = 0; s2 < slices; ++s2) {
-    above_total += s_slice_above[s2];
-    if (s2 < sl) {
-      above_before += s_slice_above[s2];
-      ties_before += s_slice_ties[s2];
-    }
-  }
   uint32_t a_pos = above_before + (before >> 16), t_rank = ties_before + (before & 0xffffu);
 #pragma unroll
   for (int i = 0; i < kPerThread; ++i) {
@@ -228,22 +252,14 @@ __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __res
 // Sort: one CTA per row; (key, ~index) descending = (score descending, index ascending); -1 padding. Bitonic network,
 // one compare-exchange per thread per stage (thread p owns the p-th pair of the stage).
 constexpr int kSortThreads = 1024;
-__global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
-                                                            size_t cand_offset, int32_t* __restrict__ idx) {
+__global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __restrict__ scratch, int k, Layout L,
+                                                            int32_t* __restrict__ idx) {
   asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
   extern __shared__ unsigned long long s_keys[];
-  __shared__ uint32_t s_want;
   const int row = blockIdx.x, tid = threadIdx.x;
-  const uint32_t* row_hist = scratch + size_t(row) * slices * 512;
-  if (tid == 0) s_want = 0;
-  __syncthreads();
-  uint32_t local = 0;
-  for (int j = tid; j < slices * 256; j += kSortThreads) local += __ldg(&row_hist[(size_t(j >> 8) * 2) * 256 + (j & 255)]);
-  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-  if ((tid & 31) == 0 && local) atomicAdd(&s_want, local);
-  __syncthreads();
-  const uint32_t want = min(uint32_t(k), s_want);
+  const size_t cand_offset = L.cand_offset_words;
+  const uint32_t want = __ldg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
   int size = 2;
   while (size < k) size <<= 1;
   const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
@@ -276,22 +292,14 @@ __device__ __forceinline__ unsigned long long shfl_xor64(unsigned long long v, i
   const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), lane_mask);
   return (static_cast<unsigned long long>(hi) << 32) | lo;
 }
-__global__ void __launch_bounds__(1024) sort_pairs_kernel(const uint32_t* __restrict__ scratch, int k, int slices,
-                                                          size_t cand_offset, int32_t* __restrict__ idx, int size) {
+__global__ void __launch_bounds__(1024) sort_pairs_kernel(const uint32_t* __restrict__ scratch, int k, Layout L,
+                                                          int32_t* __restrict__ idx, int size) {
   asm volatile("griddepcontrol.wait;" ::: "memory");            // launched with programmatic stream serialisation:
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // only the launch latency overlaps the previous kernel
   extern __shared__ unsigned long long s_keys[];
-  __shared__ uint32_t s_want;
-  const int row = blockIdx.x, tid = threadIdx.x, nthreads = size >> 1;
-  const uint32_t* row_hist = scratch + size_t(row) * slices * 512;
-  if (tid == 0) s_want = 0;
-  __syncthreads();
-  uint32_t local = 0;
-  for (int j = tid; j < slices * 256; j += nthreads) local += __ldg(&row_hist[(size_t(j >> 8) * 2) * 256 + (j & 255)]);
-  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-  if ((tid & 31) == 0 && local) atomicAdd(&s_want, local);
-  __syncthreads();
-  const uint32_t want = min(uint32_t(k), s_want);
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const size_t cand_offset = L.cand_offset_words;
+  const uint32_t want = __ldg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
   const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
   const int i0 = 2 * tid, i1 = i0 + 1;
   unsigned long long a = uint32_t(i0) < want ? cand[i0] : 0ull, b = uint32_t(i1) < want ? cand[i1] : 0ull;
@@ -412,17 +420,20 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
     c.numAttrs = 1;
     return c;
   };
+  // The two arrival counters of every row (and the rest of the per-row results) start at zero: a memset node on the
+  // stream, not an allocation.
+  cudaMemsetAsync(scratch + l.info_offset, 0, size_t(T) * 8 * sizeof(uint32_t), stream);
   cudaLaunchConfig_t c = config(grid, kThreads, 0);
-  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l.slices, 0);
-  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l.slices, 1);
-  cudaLaunchKernelEx(&c, collect_kernel, scores, n, ld, k, scratch, l.slices, l.cand_offset_words);
+  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l, 0);
+  cudaLaunchKernelEx(&c, hist_kernel, scores, n, ld, k, scratch, l, 1);
+  cudaLaunchKernelEx(&c, collect_kernel, scores, n, ld, k, scratch, l);
   const uint32_t* cscratch = scratch;
   if (size >= 64 && size <= 2048) {
     c = config(dim3(unsigned(T)), unsigned(size / 2), size_t(size) * 8);
-    cudaLaunchKernelEx(&c, sort_pairs_kernel, cscratch, k, l.slices, l.cand_offset_words, idx, size);
+    cudaLaunchKernelEx(&c, sort_pairs_kernel, cscratch, k, l, idx, size);
   } else {
     c = config(dim3(unsigned(T)), kSortThreads, size_t(size) * 8);
-    cudaLaunchKernelEx(&c, sort_kernel, cscratch, k, l.slices, l.cand_offset_words, idx);
+    cudaLaunchKernelEx(&c, sort_kernel, cscratch, k, l, idx);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
