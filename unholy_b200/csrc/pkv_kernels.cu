@@ -9,9 +9,10 @@
 //     128-byte lines when the pool base is 128-byte aligned);
 //   * one launch covers all chunks of a step and up to PKV_MAX_LAYERS layers (the reference launches once per
 //     chunk, layer and pool), with a grid sized from the SM count;
-//   * the gather has two implementations: vector loads with every load of a tile in flight before the first store,
-//     and a bulk-copy pipeline (cp.async.bulk global->shared->global with mbarrier completion) in which one warp
-//     keeps several 16-row tiles in flight and the contiguous output tile leaves as a single bulk store;
+//   * a step has two implementations: a vector kernel (every load of a tile in flight before the first store), and a
+//     bulk-copy pipeline (cp.async.bulk global->shared->global with mbarrier completion) in which single-warp CTAs
+//     stream key tiles, append tiles and gather tiles through one ring of shared-memory stages; a gathered tile is
+//     contiguous in the output and leaves as a single bulk store, an append tile as one store per page-contiguous run;
 //   * quantisation keeps 8 values per thread and reduces the block maximum with warp shuffles;
 //   * block-table entries are bounds-checked; a bad entry is skipped and recorded in a status word, never dereferenced;
 //     the only device-side wait (an mbarrier) is bounded and records when it gives up.
@@ -402,10 +403,9 @@ __global__ void __launch_bounds__(kVecThreads, 3) step_vec_kernel(const __grid_c
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Bulk-copy gather pipeline. One warp per CTA. A tile is ROWS index entries of one query: each lane of the warp owns
-// entries and issues a cp.async.bulk (global -> shared) per row, all completing on the stage's mbarrier; the finished
-// tile is contiguous in the output and leaves with ONE cp.async.bulk (shared -> global). STAGES tiles rotate, so
-// (STAGES - 2) tiles of loads and up to 2 stores are in flight per warp at any time.
+// Bulk-copy pipeline: the primitives (mbarrier, cp.async.bulk in both directions, bulk-group waits, the proxy fence)
+// and the step kernel built on them. One warp per CTA; STAGES tiles rotate through shared memory, so (STAGES - 2) tiles
+// of loads and up to 2 tiles of stores are in flight per warp at any time.
 // ---------------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
