@@ -60,6 +60,7 @@ class Replay:
         self.cursor = 0
         self.tables_checked = 0
         self.max_cached = 0
+        self.evicted_for_one_request = 0
 
     def close(self):
         self.ref.refeng_destroy(self.eng)
@@ -160,6 +161,8 @@ class Replay:
                 assert free_pages == pkv.pkv_pool_available(pool)
                 assert cached == pkv.pkv_pool_cached_count(pool)
                 self.max_cached = max(self.max_cached, cached)
+                if running == 1:
+                    self.evicted_for_one_request = max(self.evicted_for_one_request, self.num_pages - free_pages)
             else:
                 raise AssertionError(f"unknown trace record {kind}")
         self.cursor = n
@@ -178,7 +181,7 @@ def test_prefix_churn_matches_reference_engine(pkv, refeng):
     then a filler request that forces LRU evictions of a quarter of the pool."""
     g = tl.rng(4)
     num_pages, pt = 2048, 64
-    r = Replay(pkv, refeng, num_pages, pt, slots=8, pps=320, budget=2048)
+    r = Replay(pkv, refeng, num_pages, pt, slots=8, pps=num_pages // 4 + 8, budget=2048)
     try:
         prefixes = [g.integers(2, 500, size=int(n)).astype(np.int32) for n in g.integers(170, 5462, size=24)]
         for p in prefixes:  # one at a time: each finishes, its full pages stay cached and evictable tail-first
@@ -192,6 +195,7 @@ def test_prefix_churn_matches_reference_engine(pkv, refeng):
         r.drain()
         r.submit(g.integers(2, 500, size=num_pages // 4 * pt).astype(np.int32), 1)  # evicts >= 25 % from the LRU front
         r.drain()
+        assert r.evicted_for_one_request >= num_pages // 4 - 2  # the filler really ran and held a quarter of the pool
         assert r.tables_checked > 100
         assert pkv.pkv_pool_available(r.pool) == num_pages  # no leak (tools/sched_test/main.cpp:1113-1116)
     finally:
@@ -214,5 +218,30 @@ def test_concurrent_admission_matches_reference_engine(pkv, refeng):
         r.drain()
         assert r.tables_checked > 20
         assert pkv.pkv_pool_available(r.pool) == 192
+    finally:
+        r.close()
+
+
+def test_prefix_churn_full_size_matches_reference_engine(pkv, refeng):
+    """Benchmark configuration 4, mode A, at its full size: a 24,576-page pool (1,572,864 tokens, page 64), 64 prefixes
+    of 2k..64k tokens written one after the other (their sum exceeds the pool, so later ones evict earlier ones
+    LRU-first), 8 requests that extend the 8 newest prefixes and decode 512 tokens, then a filler request of a quarter
+    of the pool. Every uploaded block table, slot, prefix-hit length and page count must equal the reference engine's."""
+    g = tl.rng(4)
+    num_pages, pt = 24576, 64
+    r = Replay(pkv, refeng, num_pages, pt, slots=16, pps=num_pages // 4 + 8, budget=2048)
+    try:
+        prefixes = [g.integers(2, 50000, size=int(n)).astype(np.int32) for n in g.integers(2048, 65537, size=64)]
+        for p in prefixes:
+            r.submit(p, 1)
+            r.drain()
+        for j in range(56, 64):
+            r.submit(np.concatenate([prefixes[j], g.integers(2, 50000, size=100).astype(np.int32)]), 512)
+        r.drain()
+        r.submit(g.integers(2, 50000, size=num_pages // 4 * pt).astype(np.int32), 1)
+        r.drain()
+        assert r.evicted_for_one_request >= num_pages // 4 - 2
+        assert r.tables_checked > 1000
+        assert pkv.pkv_pool_available(r.pool) == num_pages
     finally:
         r.close()
