@@ -179,6 +179,18 @@ PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
 PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                           size_t scratch_words, pkv_stream_t stream);
 
+/* topk_bf16_batch — src/kernels/indexer.hpp:76-94 (TopkRows / TopkBatch), src/kernels/indexer.hip:878-902: several
+ * score blocks in one call (the decode chunks of a step): group g's rows [rows][n] start at scores + off (elements),
+ * its index lists [rows][k] at idx + idx_off (elements); per row the same result as pkv_topk_bf16. The groups run one
+ * after the other on the stream and share `scratch` (at least pkv_topk_batch_scratch_words words). */
+typedef struct pkv_topk_group {
+  size_t off;
+  int32_t rows, n, k, idx_off;
+} pkv_topk_group;
+PKV_API size_t pkv_topk_batch_scratch_words(const pkv_topk_group* groups, int ngroups);
+PKV_API int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, int ngroups, int32_t* idx, uint32_t* scratch,
+                        size_t scratch_words, pkv_stream_t stream);
+
 /* glm_idx_expand — src/kernels/glm_fast.hpp:115-122, src/kernels/glm_fast.hip:737-748,915-920. Selected pools
  * device int32 [n][k] (a top-k's output: valid pools first) and the queries' positions pos [n] -> the compact token
  * list idx [n][k*pool + pool-1]: the tokens of the min((p+1)/pool, k) valid pools, then the (p+1) % pool tokens of the

@@ -141,3 +141,32 @@ def test_idx_expand_gpu(pkv, cuda, n, k, pool):
     capi.check(pkv.pkv_idx_expand(d_pools.data_ptr(), d_pos.data_ptr(), d_idx.data_ptr(), n, k, pool, tl.stream_ptr(cuda)))
     cuda.cuda.synchronize()
     assert np.array_equal(tl.host(d_idx, np.int32, want.shape), want)
+
+
+@pytest.mark.gpu
+def test_topk_batch_groups(pkv, cuda):
+    """Several score blocks with their own row counts, key counts and k in one call (the decode chunks of a step):
+    each group's lists equal the oracle's for that block."""
+    g = tl.rng(75)
+    shapes = [(3, 9000, 512), (1, 300, 512), (5, 20000, 2048), (2, 64, 16)]
+    blocks = [scores_case(g, T, n, n, kind) for (T, n, k), kind in zip(shapes, ("normal", "masked", "ties", "special"))]
+    flat = np.concatenate([b.reshape(-1) for b in blocks])
+    groups = (capi.PkvTopkGroup * len(shapes))()
+    off = idx_off = 0
+    for i, (T, n, k) in enumerate(shapes):
+        groups[i].off, groups[i].rows, groups[i].n, groups[i].k, groups[i].idx_off = off, T, n, k, idx_off
+        off += T * n
+        idx_off += T * k
+    words = pkv.pkv_topk_batch_scratch_words(groups, len(shapes))
+    assert words == max(pkv.pkv_topk_scratch_words(T, n, k) for T, n, k in shapes)
+    d_s = tl.dev(cuda, flat)
+    d_scratch = cuda.full((words * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+    d_idx = cuda.full((idx_off * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_topk_bf16_batch(d_s.data_ptr(), groups, len(shapes), d_idx.data_ptr(), d_scratch.data_ptr(), words,
+                                       tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    got = tl.host(d_idx, np.int32)
+    o = 0
+    for (T, n, k), b in zip(shapes, blocks):
+        assert np.array_equal(got[o:o + T * k].reshape(T, k), orc.topk_bf16(b, n, k)), (T, n, k)
+        o += T * k

@@ -36,6 +36,10 @@ class PkvStep(C.Structure):
                  "Q", "k")] + [(n, C.c_void_p) for n in ("tables", "chunks", "q_chunk", "q_visible")]
 
 
+class PkvTopkGroup(C.Structure):
+    _fields_ = [("off", C.c_size_t), ("rows", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("idx_off", C.c_int32)]
+
+
 class PkvPoolDesc(C.Structure):
     _fields_ = [("src_base", C.c_void_p), ("dst_base", C.c_void_p), ("page_bytes", C.c_uint64)]
 
@@ -61,6 +65,8 @@ _SIGS = {
     "pkv_topk_bf16": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp, _sz, _vp]),
     "pkv_topk_static_scratch_words": (_sz, []),
     "pkv_topk_bf16_static": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp]),
+    "pkv_topk_batch_scratch_words": (_sz, [C.POINTER(PkvTopkGroup), _i]),
+    "pkv_topk_bf16_batch": (_i, [_vp, C.POINTER(PkvTopkGroup), _i, _vp, _vp, _sz, _vp]),
     "pkv_idx_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_copy_pages": (_i, [C.POINTER(PkvPoolDesc), _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_device_alloc": (_i, [C.POINTER(_vp), _sz]),

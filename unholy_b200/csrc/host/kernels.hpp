@@ -101,6 +101,13 @@ inline void topk_bf16(const uint16_t* scores, int T, int n, int k, int32_t* idx,
                       size_t scratch_words) {
   pkv_throw(pkv_topk_bf16(scores, T, n, n, k, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)), "topk_bf16");
 }
+// src/kernels/indexer.hpp:76-94: TopkRows / TopkBatch keep their field names; scratch is required here.
+using TopkRows = pkv_topk_group;
+inline void topk_bf16_batch(const uint16_t* scores, const TopkRows* groups, int ngroups, int32_t* idx, cudaStream_t st,
+                            uint32_t* scratch, size_t scratch_words) {
+  pkv_throw(pkv_topk_bf16_batch(scores, groups, ngroups, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)),
+            "topk_bf16_batch");
+}
 inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
   pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
 }

@@ -16,6 +16,7 @@
 // (one CTA per row, bitonic on (key, ~index) packed in 64 bits). Scratch is caller-provided (pkv_topk_scratch_words).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <mutex>
@@ -469,6 +470,37 @@ int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int
     return PKV_ERR_ARG;
   }
   return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
+}
+
+size_t pkv_topk_batch_scratch_words(const pkv_topk_group* groups, int ngroups) {
+  size_t need = 0;
+  for (int g = 0; groups && g < ngroups; ++g)
+    need = std::max(need, pkv_topk_scratch_words(groups[g].rows, groups[g].n, groups[g].k));
+  return need;
+}
+
+int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, int ngroups, int32_t* idx, uint32_t* scratch,
+                        size_t scratch_words, pkv_stream_t stream) {
+  if (ngroups < 0 || (ngroups > 0 && !groups)) {
+    pkv_g_err = "pkv_topk_bf16_batch: bad group list";
+    return PKV_ERR_ARG;
+  }
+  if (ngroups > 0 && (!scratch || scratch_words < pkv_topk_batch_scratch_words(groups, ngroups) ||
+                      (reinterpret_cast<uintptr_t>(scratch) & 7u))) {
+    pkv_g_err = "pkv_topk_bf16_batch: scratch must be 8-byte aligned and hold pkv_topk_batch_scratch_words() words";
+    return PKV_ERR_ARG;
+  }
+  // The groups run one after the other on the stream, so they can share the scratch.
+  for (int g = 0; g < ngroups; ++g) {
+    const pkv_topk_group& q = groups[g];
+    if (q.rows <= 0) continue;
+    const uint16_t* sc = scores + q.off;
+    int32_t* out = idx + q.idx_off;
+    if (const int rc = pkv_topk_check(sc, q.rows, q.n, q.n, q.k, out, pkv_g_err)) return rc;
+    if (const int rc = pkv_topk_launch(sc, q.rows, q.n, q.n, q.k, out, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
+      return rc;
+  }
+  return PKV_OK;
 }
 
 size_t pkv_topk_static_scratch_words(void) { return kStaticScratchWords; }
