@@ -1057,10 +1057,35 @@ def run_topk(args):
     valid = torch.gather(scores.float(), 1, order.long()) > float("-inf")
     want = torch.where(valid, order, torch.full_like(order, -1))
     ok = bool(torch.equal(idx, want))
+    # the fp32 twin (topk_rows / glm_topk): 64 rows of context / 4 fp32 scores, k = 1024 (its limit), one CTA per row
+    n32, k32 = n // 4, 1024
+    s32 = torch.randn(T, n32, generator=g, device=dev)
+    s32[0, n32 // 2:] = float("-inf")
+    idx32 = torch.empty(T, k32, dtype=torch.int32, device=dev)
+
+    def call32():
+        capi.check(lib.pkv_topk_f32(s32.data_ptr(), T, n32, n32, k32, idx32.data_ptr(), sp))
+
+    for _ in range(3):
+        call32()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        call32()
+    e1.record()
+    torch.cuda.synchronize()
+    us32 = e0.elapsed_time(e1) / reps * 1e3
+    order = torch.sort(s32, dim=1, descending=True, stable=True).indices[:, :k32].to(torch.int32)
+    valid = torch.gather(s32, 1, order.long()) > float("-inf")
+    ok32 = bool(torch.equal(idx32, torch.where(valid, order, torch.full_like(order, -1))))
+    nbytes32 = T * n32 * 4 + T * k32 * 4
     nbytes = T * n * 2 + T * k * 4
     _emit("topk", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
         "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16, caller scratch {words * 4} B)"},
-        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok}})
+        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok},
+        "f32_twin": {"workload": f"top-{k32} of {n32} fp32 scores x {T} rows (pkv_topk_f32, no scratch)",
+                     "us_per_call": round(us32, 2), "GBps": round(nbytes32 / (us32 * 1e-6) / 1e9, 1),
+                     "bit_exact_check": {"ok": ok32}}})
 
 
 def main():

@@ -191,6 +191,15 @@ PKV_API size_t pkv_topk_batch_scratch_words(const pkv_topk_group* groups, int ng
 PKV_API int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, int ngroups, int32_t* idx, uint32_t* scratch,
                         size_t scratch_words, pkv_stream_t stream);
 
+/* topk_rows — src/kernels/ref.hpp:107, src/kernels/ref_attn.hip:143-254,390-393 — and glm_topk —
+ * src/kernels/glm_fast.hpp:86-93, src/kernels/glm_fast.hip:557-681,852-874 (the same selection in one or two stages;
+ * its cand scratch is not needed here). scores: device fp32 [T][ld] (ld >= n elements between rows; topk_rows has
+ * ld = n); idx: device int32 [T][k]. Per row the min(k, #scores above -inf) largest scores ordered by (score
+ * descending, index ascending), threshold ties to the lowest indices, -1 padded; -inf and negative NaN patterns are
+ * never selected. k <= 1024 as in the reference (PKV_ERR_ARG beyond). No scratch: one CTA per row selects in shared
+ * memory. T <= 0 or n <= 0 returns PKV_OK without a launch. */
+PKV_API int pkv_topk_f32(const float* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream);
+
 /* glm_idx_expand — src/kernels/glm_fast.hpp:115-122, src/kernels/glm_fast.hip:737-748,915-920. Selected pools
  * device int32 [n][k] (a top-k's output: valid pools first) and the queries' positions pos [n] -> the compact token
  * list idx [n][k*pool + pool-1]: the tokens of the min((p+1)/pool, k) valid pools, then the (p+1) % pool tokens of the

@@ -38,6 +38,7 @@ _SIGS = {
     "orc_move_pages": (None, [_vp, _vp, _sz, _vp, _vp, _i, _i]),
     "orc_copy": (None, [_vp, _vp, _sz]),
     "orc_topk_bf16": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
+    "orc_topk_f32": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_idx_expand": (None, [_vp, _vp, _vp, _i, _i, _i]),
     "orc_gather_rows_fp8": (None, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "orc_hardware_threads": (_i, []),
@@ -146,6 +147,14 @@ def topk_bf16(scores, n, k, threads=1):
     T, ld = scores.shape
     idx = np.empty((T, k), np.int32)
     lib().orc_topk_bf16(_p(scores), T, n, ld, k, _p(idx), threads)
+    return idx
+
+
+def topk_f32(scores, n, k, threads=1):
+    T, ld = scores.shape
+    assert scores.dtype == np.float32
+    idx = np.empty((T, k), np.int32)
+    lib().orc_topk_f32(_p(scores), T, n, ld, k, _p(idx), threads)
     return idx
 
 

@@ -351,6 +351,27 @@ void orc_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, in
   });
 }
 
+// src/kernels/ref_attn.hip:137-254 (sort_key, topk_rows_kernel) = src/kernels/glm_fast.hip:551-681 (topk_seg_kernel; the
+// two-stage form of glm_topk, :852-874, selects the same set): valid = key above the key of -inf; the min(k, #valid)
+// largest by (key descending, index ascending), -1 padded.
+void orc_topk_f32(const float* scores, int T, int n, long long ld, int k, int32_t* idx, int threads) {
+  parallel_for(T, threads, [&](int t) {
+    const float* row = scores + size_t(t) * size_t(ld);
+    std::vector<uint64_t> keys;
+    keys.reserve(size_t(n));
+    for (int i = 0; i < n; ++i) {
+      uint32_t u;
+      std::memcpy(&u, row + i, 4);
+      const uint32_t key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // ref_attn.hip:138-141
+      if (key > 0x007fffffu) keys.push_back((uint64_t(key) << 32) | (0xffffffffu - uint32_t(i)));
+    }
+    const size_t want = std::min(size_t(k), keys.size());
+    std::partial_sort(keys.begin(), keys.begin() + ptrdiff_t(want), keys.end(), std::greater<uint64_t>());
+    for (int j = 0; j < k; ++j)
+      idx[size_t(t) * k + j] = size_t(j) < want ? int32_t(0xffffffffu - uint32_t(keys[size_t(j)] & 0xffffffffu)) : -1;
+  });
+}
+
 // src/kernels/glm_fast.hip:737-748 (idx_expand_compact_kernel) — selected pools -> compact token list.
 void orc_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool) {
   const int w = k * pool + pool - 1;

@@ -3,6 +3,7 @@
 // fake_quant_fp4, store_rows + gather_rows equal to the rows, errors thrown as std::runtime_error. Prints and returns
 // non-zero on failure. Built and run by tests/test_gpu_cpp_wrappers.py.
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <numeric>
@@ -109,6 +110,42 @@ int main() {
       }
     std::printf("store_rows + gather_rows: %zu values differ\n", diff);
     fails += diff != 0;
+  }
+  // ---- topk_rows == glm_topk == a host sort by (score desc, index asc); k > 1024 throws as in the reference ----
+  {
+    const int T = 9, n = 6000, kk = 300;
+    std::vector<float> sc(size_t(T) * n);
+    for (auto& v : sc) v = float(int(rng() % 4001) - 2000) * 0.25f;   // many equal scores
+    for (int i = 4000; i < n; ++i) sc[size_t(2) * n + i] = -INFINITY;
+    Dev<float> d_sc(sc.size());
+    d_sc.up(sc);
+    Dev<int32_t> d_a(size_t(T) * kk), d_b(size_t(T) * kk);
+    k::topk_rows(d_sc.p, T, n, kk, d_a.p, nullptr);
+    k::glm_topk(d_sc.p, n, T, n, kk, d_b.p, nullptr, nullptr);
+    CK(cudaDeviceSynchronize());
+    const auto a = d_a.down(), b = d_b.down();
+    size_t diff = 0;
+    std::vector<int32_t> order(static_cast<size_t>(n));
+    for (int t = 0; t < T; ++t) {
+      std::iota(order.begin(), order.end(), 0);
+      const float* row = sc.data() + size_t(t) * n;
+      std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return row[x] > row[y]; });
+      for (int e = 0; e < kk; ++e) {
+        const int32_t want = row[order[size_t(e)]] == -INFINITY ? -1 : order[size_t(e)];
+        diff += a[size_t(t) * kk + e] != want;
+        diff += b[size_t(t) * kk + e] != want;
+      }
+    }
+    std::printf("topk_rows / glm_topk: %zu entries differ\n", diff);
+    fails += diff != 0;
+    bool threw = false;
+    try {
+      k::topk_rows(d_sc.p, T, n, 1025, d_a.p, nullptr);
+    } catch (const std::runtime_error& e) {
+      threw = std::strstr(e.what(), "k > 1024") != nullptr;
+    }
+    std::printf("topk_rows k > 1024 throws: %s\n", threw ? "yes" : "NO");
+    fails += !threw;
   }
   // ---- errors are exceptions ----
   {

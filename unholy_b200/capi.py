@@ -67,6 +67,7 @@ _SIGS = {
     "pkv_topk_bf16_static": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp]),
     "pkv_topk_batch_scratch_words": (_sz, [C.POINTER(PkvTopkGroup), _i]),
     "pkv_topk_bf16_batch": (_i, [_vp, C.POINTER(PkvTopkGroup), _i, _vp, _vp, _sz, _vp]),
+    "pkv_topk_f32": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp]),
     "pkv_idx_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_copy_pages": (_i, [C.POINTER(PkvPoolDesc), _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_device_alloc": (_i, [C.POINTER(_vp), _sz]),

@@ -108,6 +108,18 @@ inline void topk_bf16_batch(const uint16_t* scores, const TopkRows* groups, int 
   pkv_throw(pkv_topk_bf16_batch(scores, groups, ngroups, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)),
             "topk_bf16_batch");
 }
+// src/kernels/ref.hpp:107 (k > 1024 throws, as ref_attn.hip:391 does) and src/kernels/glm_fast.hpp:86-93: the same
+// selection; glm_topk keeps its cand argument (unused: one CTA per row selects in shared memory) and its size query.
+inline void topk_rows(const float* scores, int T, int n, int k, int32_t* idx, cudaStream_t st) {
+  pkv_throw(pkv_topk_f32(scores, T, n, n, k, idx, reinterpret_cast<pkv_stream_t>(st)), "topk_rows");
+}
+constexpr int kGlmTopkSeg = 4096;
+inline size_t glm_topk_cand_bytes(int rows, int cols, int k) {
+  return size_t(rows) * size_t((cols + kGlmTopkSeg - 1) / kGlmTopkSeg) * size_t(k) * 8;
+}
+inline void glm_topk(const float* scores, int ld, int n, int cols, int k, int32_t* idx, void* /*cand*/, cudaStream_t st) {
+  pkv_throw(pkv_topk_f32(scores, n, cols, ld, k, idx, reinterpret_cast<pkv_stream_t>(st)), "glm_topk");
+}
 inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
   pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
 }

@@ -1,0 +1,305 @@
+// Index-list producer on fp32 scores: top-k per row, the fp32 twin of pkv_topk_bf16.
+//
+// Contract of ewtodd/unholy's topk_rows (src/kernels/ref.hpp:107, src/kernels/ref_attn.hip:143-254) and glm_topk
+// (src/kernels/glm_fast.hpp:86-93, src/kernels/glm_fast.hip:557-681,852-874; one- or two-stage, same result): per row
+// the want = min(k, #valid) largest scores, a score being valid when its order-preserving 32-bit key is greater than
+// the key of -inf (-inf and negative NaN patterns are never selected; -0.0 sorts below +0.0); ties at the threshold
+// go to the lowest indices; the output is ordered by (score descending, index ascending) and padded with -1; k <= 1024.
+// That contract fixes every output element, so any algorithm that meets it is bit-exact with the reference.
+//
+// B200 design: one CTA of 512 threads per row, no scratch in global memory. The row is read from HBM ONCE: its keys
+// are kept in shared memory (rows of up to kCacheKeys keys; longer rows are re-read through L2) while the first
+// histogram is built. Radix select in three passes of 12 + 10 + 10 bits instead of four of 8: the first digit holds
+// sign, exponent and three mantissa bits, so scores of similar magnitude still spread over dozens of bins and the
+// shared-memory atomics do not pile up on one address; passes two and three only count the few keys inside the chosen
+// bin. The selected keys are placed without atomics: every warp counts the keys above the threshold and the ties in
+// its contiguous range of indices, the counts give each warp its bases, ballots give the rank inside a group of 32,
+// so the threshold ties come out in index order (no serial scan of the row by one warp). The final sort of up to 1024 (key, ~index) pairs keeps two elements per thread in registers:
+// strides up to 32 are register or shuffle exchanges, only strides >= 64 go through shared memory.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "../../include/unholy_pkv.h"
+
+extern thread_local std::string pkv_g_err;  // defined in pkv_kernels.cu: what pkv_last_error() returns
+
+namespace pkv_topkf {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxK = 1024;               // the reference's limit (ref_attn.hip:391, glm_fast.hip:854)
+constexpr int kCacheKeys = 49152;         // 192 KB of keys in shared memory
+constexpr int kBins = 4096;               // first pass: 12 bits
+constexpr uint32_t kNegInfKey = 0x007fffffu;  // sort_key(-inf) = ~0xff800000
+
+__device__ __forceinline__ uint32_t sort_key(uint32_t u) { return (u & 0x80000000u) ? ~u : (u | 0x80000000u); }
+
+struct Shared {
+  uint32_t hist[kBins];
+  unsigned long long sel[kMaxK];
+  uint32_t wsum[kWarps];
+  uint32_t wties[kWarps];
+  uint32_t bin, need;
+};
+
+// Sum over all bins (BINS / kThreads consecutive bins per thread); every thread returns the total.
+template <int BINS>
+__device__ uint32_t block_total(Shared& s) {
+  constexpr int PER = BINS / kThreads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t v = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) v += s.hist[tid * PER + j];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) s.wsum[warp] = v;
+  __syncthreads();
+  uint32_t t = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) t += s.wsum[w];
+  __syncthreads();
+  return t;
+}
+
+// The highest bin b with (count in bins > b) < need <= (count in bins >= b): s.bin = b, s.need = need - count above.
+// need is in 1..total, so exactly one thread writes.
+template <int BINS>
+__device__ void pick_bin(Shared& s, uint32_t need) {
+  constexpr int PER = BINS / kThreads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t h[PER], local = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    h[j] = s.hist[tid * PER + j];
+    local += h[j];
+  }
+  uint32_t sfx = local;  // inclusive suffix sum over threads
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_down_sync(0xffffffffu, sfx, o);
+    if (lane + o < 32) sfx += t;
+  }
+  if (lane == 0) s.wsum[warp] = sfx;
+  __syncthreads();
+  for (int w = warp + 1; w < kWarps; ++w) sfx += s.wsum[w];
+  uint32_t above = sfx - local;
+#pragma unroll
+  for (int j = PER - 1; j >= 0; --j) {
+    if (above < need && above + h[j] >= need) {
+      s.bin = uint32_t(tid * PER + j);
+      s.need = need - above;
+    }
+    above += h[j];
+  }
+  __syncthreads();
+}
+
+template <int BINS>
+__device__ __forceinline__ void clear_hist(Shared& s) {
+  for (int b = threadIdx.x; b < BINS; b += kThreads) s.hist[b] = 0;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads) topk_f32_kernel(const float* __restrict__ scores, int n, long long ld, int k,
+                                                            int32_t* __restrict__ idx, int cached) {
+  extern __shared__ __align__(16) uint32_t s_key[];  // [n + 3] when cached
+  __shared__ Shared s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t* row = reinterpret_cast<const uint32_t*>(scores) + size_t(blockIdx.x) * size_t(ld);
+  int32_t* out = idx + size_t(blockIdx.x) * size_t(k);
+  uint32_t* sk = s_key + ((reinterpret_cast<uintptr_t>(row) >> 2) & 3u);  // sk + i is 16-byte aligned where row + i is
+  const auto key_at = [&](int i) { return cached ? sk[i] : sort_key(__ldg(row + i)); };
+
+  // Pass 1: the only read of the row from HBM, 16 bytes per load from the first aligned element on; 12-bit digit.
+  // Keys that are not valid are not counted. sk is shifted so that the 16-byte groups are aligned in the cache too.
+  clear_hist<kBins>(s);
+  const int head = min(n, int((4u - uint32_t((reinterpret_cast<uintptr_t>(row) >> 2) & 3u)) & 3u));
+  const int nvec = (n - head) >> 2;
+  const auto count = [&](uint32_t key) {
+    if (key > kNegInfKey) atomicAdd(&s.hist[key >> 20], 1u);
+  };
+  if (tid < head) {
+    const uint32_t key = sort_key(__ldg(row + tid));
+    if (cached) sk[tid] = key;
+    count(key);
+  }
+  const uint4* rv = reinterpret_cast<const uint4*>(row + head);
+#pragma unroll 4
+  for (int v = tid; v < nvec; v += kThreads) {
+    uint4 q = __ldg(rv + v);
+    q.x = sort_key(q.x), q.y = sort_key(q.y), q.z = sort_key(q.z), q.w = sort_key(q.w);
+    if (cached) *reinterpret_cast<uint4*>(sk + head + 4 * v) = q;
+    count(q.x), count(q.y), count(q.z), count(q.w);
+  }
+  for (int i = head + 4 * nvec + tid; i < n; i += kThreads) {
+    const uint32_t key = sort_key(__ldg(row + i));
+    if (cached) sk[i] = key;
+    count(key);
+  }
+  __syncthreads();
+  const uint32_t nvalid = block_total<kBins>(s);
+  const uint32_t want = min(uint32_t(k), nvalid);
+  if (want == 0) {
+    for (int i = tid; i < k; i += kThreads) out[i] = -1;
+    return;
+  }
+  pick_bin<kBins>(s, want);
+  uint32_t prefix = s.bin << 20, need = s.need;
+  // Passes 2 and 3: 10 bits each, over the keys that share the prefix.
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int shift = pass == 0 ? 10 : 0;
+    const uint32_t mask_hi = pass == 0 ? 0xfff00000u : 0xfffffc00u;
+    __syncthreads();
+    clear_hist<1024>(s);
+#pragma unroll 4
+    for (int i = tid; i < n; i += kThreads) {
+      const uint32_t key = key_at(i);
+      if ((key & mask_hi) == prefix) atomicAdd(&s.hist[(key >> shift) & 0x3ffu], 1u);
+    }
+    __syncthreads();
+    pick_bin<1024>(s, need);
+    prefix |= s.bin << shift;
+    need = s.need;
+  }
+  // prefix = the threshold key (valid: it is the key of a counted score); need = threshold ties to take.
+  // Each warp owns a contiguous range of indices. First sweep: how many keys above the threshold and how many ties
+  // the range holds. Second sweep: every such key goes to its slot — the warps' counts give the bases, ballots the
+  // rank inside a group of 32 — so no atomic is needed and the ties come out in index order.
+  const int per_warp = ((n + kWarps - 1) / kWarps + 31) & ~31;
+  const int w0 = warp * per_warp, w1 = min(n, w0 + per_warp);
+  uint32_t above = 0, ties = 0;
+#pragma unroll 4
+  for (int i = w0 + lane; i < w1; i += 32) {
+    const uint32_t key = key_at(i);
+    above += key > prefix;
+    ties += key == prefix;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    above += __shfl_xor_sync(0xffffffffu, above, o);
+    ties += __shfl_xor_sync(0xffffffffu, ties, o);
+  }
+  if (lane == 0) {
+    s.wsum[warp] = above;
+    s.wties[warp] = ties;
+  }
+  __syncthreads();
+  uint32_t above_before = 0, ties_before = 0;
+  for (int w = 0; w < warp; ++w) {
+    above_before += s.wsum[w];
+    ties_before += s.wties[w];
+  }
+  const uint32_t base = want - need;  // = keys above the threshold in the whole row
+  const bool take_ties = ties > 0 && ties_before < need;
+  if (above > 0 || take_ties) {
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t a_rank = above_before, t_rank = ties_before;
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      const int i = i0 + lane;
+      const uint32_t key = i < w1 ? key_at(i) : 0u;  // 0 is below every threshold
+      const uint32_t ba = __ballot_sync(0xffffffffu, key > prefix);
+      const uint32_t bt = __ballot_sync(0xffffffffu, key == prefix);
+      const unsigned long long packed = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - uint32_t(i));
+      if (key > prefix) s.sel[a_rank + __popc(ba & lt)] = packed;
+      const uint32_t r = t_rank + __popc(bt & lt);
+      if (key == prefix && r < need) s.sel[base + r] = packed;
+      a_rank += __popc(ba);
+      t_rank += __popc(bt);
+    }
+  }
+  __syncthreads();
+  // Sort size = power of two >= max(k, 64) (<= 1024), two elements per thread, descending; padding 0 sorts last.
+  int size = 64;
+  while (size < k) size <<= 1;
+  const int i0 = 2 * tid, i1 = i0 + 1;
+  const bool active = i0 < size;  // whole warps: size / 2 is a multiple of 32
+  unsigned long long a = uint32_t(i0) < want ? s.sel[i0 & (kMaxK - 1)] : 0ull;
+  unsigned long long b = uint32_t(i1) < want ? s.sel[i1 & (kMaxK - 1)] : 0ull;
+  __syncthreads();
+  const auto keep = [](unsigned long long mine, unsigned long long other, bool take_max) {
+    return take_max == (mine > other) ? mine : other;
+  };
+  const auto shfl64 = [](unsigned long long v, int m) {
+    const uint32_t lo = __shfl_xor_sync(0xffffffffu, uint32_t(v), m);
+    const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), m);
+    return (static_cast<unsigned long long>(hi) << 32) | lo;
+  };
+  for (int len = 2; len <= size; len <<= 1) {
+    for (int stride = len >> 1; stride > 0; stride >>= 1) {
+      const bool desc = (i0 & len) == 0;
+      if (stride == 1) {
+        const unsigned long long hi = a > b ? a : b, lo = a > b ? b : a;
+        a = desc ? hi : lo;
+        b = desc ? lo : hi;
+      } else if (stride <= 32) {
+        if (active) {
+          const bool lower = (i0 & stride) == 0;
+          const unsigned long long oa = shfl64(a, stride >> 1), ob = shfl64(b, stride >> 1);
+          a = keep(a, oa, lower == desc);
+          b = keep(b, ob, lower == desc);
+        }
+      } else {
+        if (active) {
+          s.sel[i0] = a;
+          s.sel[i1] = b;
+        }
+        __syncthreads();
+        if (active) {
+          const bool lower = (i0 & stride) == 0;
+          const unsigned long long oa = s.sel[i0 ^ stride], ob = s.sel[i1 ^ stride];
+          a = keep(a, oa, lower == desc);
+          b = keep(b, ob, lower == desc);
+        }
+        __syncthreads();
+      }
+    }
+  }
+  if (i0 < k) out[i0] = uint32_t(i0) < want ? int32_t(0xffffffffu - uint32_t(a & 0xffffffffull)) : -1;
+  if (i1 < k) out[i1] = uint32_t(i1) < want ? int32_t(0xffffffffu - uint32_t(b & 0xffffffffull)) : -1;
+}
+
+}  // namespace pkv_topkf
+
+extern "C" {
+
+int pkv_topk_f32(const float* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream) {
+  using namespace pkv_topkf;
+  if (T <= 0 || n <= 0) return PKV_OK;  // nothing to do, as the reference (ref_attn.hip:390 launches T blocks)
+  if (k > kMaxK) {
+    pkv_g_err = "pkv_topk_f32: k > 1024";
+    return PKV_ERR_ARG;
+  }
+  if (!scores || !idx || k <= 0 || ld < n || n > (1 << 30)) {
+    pkv_g_err = "pkv_topk_f32: null pointer, k <= 0, ld < n or n > 2^30";
+    return PKV_ERR_ARG;
+  }
+  const int cached = n <= kCacheKeys;
+  const size_t smem = cached ? size_t(n + 3) * 4 : 0;
+  static thread_local int opted_dev = -1;
+  static thread_local size_t opted = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && smem > 48 * 1024 - sizeof(Shared) && (dev != opted_dev || smem > opted)) {
+    e = cudaFuncSetAttribute(topk_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int((kCacheKeys + 3) * 4));
+    if (e == cudaSuccess) {
+      opted_dev = dev;
+      opted = size_t(kCacheKeys + 3) * 4;
+    }
+  }
+  if (e != cudaSuccess) {
+    pkv_g_err = std::string("pkv_topk_f32: ") + cudaGetErrorString(e);
+    return PKV_ERR_CUDA;
+  }
+  topk_f32_kernel<<<T, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(scores, n, ld, k, idx, cached);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    pkv_g_err = std::string("pkv_topk_f32: ") + cudaGetErrorString(e);
+    return PKV_ERR_CUDA;
+  }
+  return PKV_OK;
+}
+
+}  // extern "C"
