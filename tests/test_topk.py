@@ -54,20 +54,30 @@ def test_oracle_topk_matches_contract(kind):
 @pytest.mark.gpu
 @pytest.mark.parametrize("kind", ["normal", "ties", "masked", "special"])
 @pytest.mark.parametrize("T,n,ld,k", [(37, 5000, 5000, 512), (64, 131072, 131072, 2048), (3, 8192, 8200, 2048),
-                                      (4, 8193, 8193, 100), (2, 300, 304, 2048), (1, 1, 8, 1), (5, 40000, 40000, 2051)])
+                                      (4, 8193, 8193, 100), (2, 300, 304, 2048), (1, 1, 8, 1), (5, 40000, 40000, 2051),
+                                      (6, 1000, 1003, 64), (2, 524288, 524288, 2048), (1, 524289, 524289, 300), (1, 800000, 800000, 300), (16, 40000, 40000, 1000),
+                                      (3, 7, 9, 2), (2, 65, 65, 129)])
 def test_topk_bf16_gpu(pkv, cuda, kind, T, n, ld, k):
+    """Both paths of pkv_topk_bf16 (knob 7: 0 = one launch of 8-CTA clusters where the shape allows it — k <= 2048,
+    n <= 786,432 —, 1 = the four launches through the scratch) against the oracle."""
     g = tl.rng(71)
     s = scores_case(g, T, n, ld, kind)
     want = orc.topk_bf16(s, n, k, threads=8)
     d_s = tl.dev(cuda, s)
     words = pkv.pkv_topk_scratch_words(T, n, k)
     d_scratch = cuda.full((words * 4,), 0x5A, dtype=cuda.uint8, device="cuda")   # poison: nothing relies on zeroes
-    d_idx = cuda.full((T * k * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
-    for _ in range(2):   # the second call reuses dirty scratch
-        capi.check(pkv.pkv_topk_bf16(d_s.data_ptr(), T, n, ld, k, d_idx.data_ptr(), d_scratch.data_ptr(), words,
-                                     tl.stream_ptr(cuda)))
-        cuda.cuda.synchronize()
-        assert np.array_equal(tl.host(d_idx, np.int32, (T, k)), want)
+    try:
+        for path in (0, 1):
+            capi.check(pkv.pkv_tune(7, path))
+            d_idx = cuda.full((T * k * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+            for _ in range(2):   # the second call reuses dirty scratch
+                capi.check(pkv.pkv_topk_bf16(d_s.data_ptr(), T, n, ld, k, d_idx.data_ptr(), d_scratch.data_ptr(), words,
+                                             tl.stream_ptr(cuda)))
+                cuda.cuda.synchronize()
+                assert np.array_equal(tl.host(d_idx, np.int32, (T, k)), want), path
+    finally:
+        capi.check(pkv.pkv_tune(7, 0))
+    assert tl.device_status(pkv) == 0
 
 
 @pytest.mark.gpu

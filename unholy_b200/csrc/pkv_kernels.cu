@@ -30,6 +30,12 @@
 
 // The calling thread's last error message (shared by every translation unit of the library).
 thread_local std::string pkv_g_err;
+// Which top-k path pkv_topk_bf16 takes: 0 = one cluster launch where the shape allows it, 1 = always the four launches
+// with scratch (pkv_tune knob 7; default from PKV_TOPK_PATH).
+int pkv_g_topk_path = [] {
+  const char* v = std::getenv("PKV_TOPK_PATH");
+  return v ? std::atoi(v) : 0;
+}();
 
 namespace {
 
@@ -1029,6 +1035,7 @@ int pkv_tune(int knob, int value) {
     case 4: t.fuse = value; return PKV_OK;
     case 5: t.batch = value; return PKV_OK;
     case 6: t.resolve_late = value; return PKV_OK;
+    case 7: pkv_g_topk_path = value; return PKV_OK;
     default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
   }
 }

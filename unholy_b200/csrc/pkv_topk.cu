@@ -444,6 +444,23 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
   return PKV_OK;
 }
 
+// pkv_topk_cluster.cu: the whole selection in one launch of 8-CTA clusters, for the shapes it takes.
+bool pkv_topk_cluster_eligible(int T, int n, int k);
+int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, cudaStream_t stream,
+                            bool* usable, std::string& err);
+extern int pkv_g_topk_path;
+
+// One cluster launch when the shape and the device allow it, else the four launches through `scratch`.
+int pkv_topk_dispatch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
+                      cudaStream_t stream, std::string& err) {
+  if (pkv_g_topk_path != 1 && pkv_topk_cluster_eligible(T, n, k)) {
+    bool usable = false;
+    if (const int rc = pkv_topk_cluster_launch(scores, T, n, ld, k, idx, stream, &usable, err)) return rc;
+    if (usable) return PKV_OK;
+  }
+  return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, stream, err);
+}
+
 int pkv_topk_check(const uint16_t* scores, int T, int n, long long ld, int k, const int32_t* idx, std::string& err) {
   if (T < 0 || n < 0 || k <= 0 || ld < n) {
     err = "pkv_topk_bf16: bad shape";
@@ -469,7 +486,7 @@ int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int
     pkv_g_err = "pkv_topk_bf16: scratch must be 8-byte aligned and hold pkv_topk_scratch_words(T, n, k) words";
     return PKV_ERR_ARG;
   }
-  return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
+  return pkv_topk_dispatch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
 }
 
 size_t pkv_topk_batch_scratch_words(const pkv_topk_group* groups, int ngroups) {
@@ -497,7 +514,7 @@ int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, in
     const uint16_t* sc = scores + q.off;
     int32_t* out = idx + q.idx_off;
     if (const int rc = pkv_topk_check(sc, q.rows, q.n, q.n, q.k, out, pkv_g_err)) return rc;
-    if (const int rc = pkv_topk_launch(sc, q.rows, q.n, q.n, q.k, out, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
+    if (const int rc = pkv_topk_dispatch(sc, q.rows, q.n, q.n, q.k, out, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
       return rc;
   }
   return PKV_OK;

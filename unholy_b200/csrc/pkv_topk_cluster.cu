@@ -1,0 +1,469 @@
+// Top-k of bf16 scores in ONE launch: a thread-block cluster of 1, 2, 4 or 8 CTAs per row, no scratch in global memory.
+//
+// Same contract as pkv_topk.cu (ewtodd/unholy's topk_bf16, src/kernels/indexer.hpp:74, src/kernels/indexer.hip:408-560):
+// per row the min(k, #valid) largest scores, valid = 16-bit order-preserving key above the key of -inf, threshold
+// ties to the lowest indices, output ordered by (score descending, index ascending), -1 padded.
+//
+// The four-launch path in pkv_topk.cu reads a row three times (the second and third time from L2) and passes
+// histograms, offsets and candidates through global scratch. Here the CTAs of a cluster split the row, every CTA reads
+// its slice from HBM once and keeps the keys in shared memory (up to 192 KB: one CTA of 1024 threads per SM), and the
+// CTAs exchange their histograms through distributed shared memory. The cluster size is chosen by the host so that
+// the launch is about one CTA per SM (64 rows of 131,072 keys: 2 CTAs per row on 128 SMs):
+//   1. load the slice, keys to shared memory, histogram of the top 12 key bits (sign, exponent, three mantissa bits:
+//      scores of similar magnitude still spread over dozens of bins, so the shared-memory atomics do not pile up);
+//      cluster barrier; every CTA sums the histograms and finds the bin of the k-th largest key;
+//   2. histogram of the low 4 bits over the keys of that bin; cluster barrier; the threshold key, the number of
+//      threshold ties to take, and for every CTA how many selected keys the CTAs before it hold;
+//   3. every CTA writes its selected keys, in index order, into the candidate list in CTA 0's shared memory (remote
+//      stores). A candidate is (key << 16 | 0xffff - ordinal) plus its index: the ordinal is the candidate's place
+//      in index order, so sorting the 32-bit words descending IS the (score descending, index ascending) order;
+//      cluster barrier; CTA 0 sorts the words (bitonic network unrolled at compile time, four words per thread in
+//      registers: strides up to 64 are register or shuffle exchanges) and writes the indices.
+// Every thread of every CTA passes the same three cluster barriers whatever the data (no early exit before the last
+// one), and no CTA touches another's shared memory after the last barrier.
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "../../include/unholy_pkv.h"
+
+namespace cg = cooperative_groups;
+
+#ifdef PKV_TOPK_TIMING  // development only: cycle stamps of row 0, CTA 0, thread 0
+__device__ long long g_topk_stamps[16];
+#define PKV_STAMP(i) do { if (blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 0) g_topk_stamps[i] = clock64(); } while (0)
+#else
+#define PKV_STAMP(i) do { } while (0)
+#endif
+
+namespace pkv_topkc {
+
+constexpr int kMaxCluster = 8;
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxK = 2048;
+constexpr int kMaxSlice = 98304;          // keys per CTA kept in shared memory (192 KB)
+constexpr int kBins1 = 4096;              // top 12 bits: four bins per thread
+constexpr int kBins2 = 16;                // low 4 bits
+constexpr uint32_t kNegInfKey = 0x007Fu;  // key of the bf16 pattern 0xFF80; valid keys are above it (their top 12 bits >= 8)
+
+// Two bf16 patterns in one word -> their order-preserving keys: ~b when the sign is set, b | 0x8000 otherwise.
+__device__ __forceinline__ uint32_t key_pair(uint32_t w) { return w ^ ((((w >> 15) & 0x00010001u) * 0xffffu) | 0x80008000u); }
+__device__ __forceinline__ uint32_t key_one(uint32_t b) { return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u); }
+
+struct __align__(16) Shared {
+  uint32_t hist1[kBins1];  // this CTA's first histogram; CTA 0 reuses it as the candidates' sort words after barrier 2
+  int32_t cand_idx[kMaxK];
+  uint32_t hist2[kBins2];
+  uint32_t h2[kMaxCluster][kBins2];
+  uint32_t wsum[kWarps], wsum2[kWarps];
+  uint32_t cta_above[kMaxCluster], cta_ties[kMaxCluster];
+  uint32_t above1;         // this CTA's keys in bins above the chosen one: read by the others after barrier 2
+  uint32_t bin, need, total;
+};
+
+template <class F>
+__device__ __forceinline__ void for_each_key(const uint4& q, F&& f) {
+  f(q.x & 0xffffu, 0), f(q.x >> 16, 1), f(q.y & 0xffffu, 2), f(q.y >> 16, 3);
+  f(q.z & 0xffffu, 4), f(q.z >> 16, 5), f(q.w & 0xffffu, 6), f(q.w >> 16, 7);
+}
+
+// Keys above the threshold in the low half, keys equal to it in the high half.
+__device__ __forceinline__ uint32_t count_selected(const uint4& q, uint32_t thr) {
+  uint32_t c = 0;
+  for_each_key(q, [&](uint32_t key, int) { c += (key > thr ? 1u : 0u) + (key == thr ? 0x10000u : 0u); });
+  return c;
+}
+
+__device__ __forceinline__ uint32_t keep(uint32_t mine, uint32_t other, bool take_max) {
+  return take_max ? max(mine, other) : min(mine, other);
+}
+
+// Bitonic sort, descending, of SIZE words: thread t < SIZE / 4 holds words 4t..4t+3. The network is unrolled at compile
+// time, so a stage is a handful of instructions: strides 1 and 2 inside the thread, 4..64 by shuffles, larger ones
+// through `buf` with a named barrier over the SIZE / 4 sorting threads.
+template <int LOG>
+__device__ __forceinline__ void sort_desc(uint32_t& e0, uint32_t& e1, uint32_t& e2, uint32_t& e3, uint32_t* buf, int tid) {
+  constexpr int kSortThreads = (1 << LOG) / 4;
+#pragma unroll
+  for (int L = 1; L <= LOG; ++L) {
+    const int len = 1 << L;
+    const bool desc = L == 1 ? true : ((4 * tid) & len) == 0;  // for len >= 4 the thread's four words share the direction
+#pragma unroll
+    for (int S = L - 1; S >= 0; --S) {
+      const int stride = 1 << S;
+      if (stride == 1) {
+        const bool d23 = L == 1 ? false : desc;
+        const uint32_t a = keep(e0, e1, desc), b = keep(e1, e0, !desc), c = keep(e2, e3, d23), d = keep(e3, e2, !d23);
+        e0 = a, e1 = b, e2 = c, e3 = d;
+      } else if (stride == 2) {
+        const uint32_t a = keep(e0, e2, desc), b = keep(e1, e3, desc), c = keep(e2, e0, !desc), d = keep(e3, e1, !desc);
+        e0 = a, e1 = b, e2 = c, e3 = d;
+      } else if (stride <= 64) {
+        const int m = stride >> 2;
+        const bool take_max = ((tid & m) == 0) == desc;
+        e0 = keep(e0, __shfl_xor_sync(0xffffffffu, e0, m), take_max);
+        e1 = keep(e1, __shfl_xor_sync(0xffffffffu, e1, m), take_max);
+        e2 = keep(e2, __shfl_xor_sync(0xffffffffu, e2, m), take_max);
+        e3 = keep(e3, __shfl_xor_sync(0xffffffffu, e3, m), take_max);
+      } else {
+        const int m = stride >> 2;
+        reinterpret_cast<uint4*>(buf)[tid] = make_uint4(e0, e1, e2, e3);
+        asm volatile("bar.sync 1, %0;" ::"n"(kSortThreads) : "memory");
+        const uint4 o = reinterpret_cast<const uint4*>(buf)[tid ^ m];
+        const bool take_max = ((tid & m) == 0) == desc;
+        e0 = keep(e0, o.x, take_max), e1 = keep(e1, o.y, take_max);
+        e2 = keep(e2, o.z, take_max), e3 = keep(e3, o.w, take_max);
+        asm volatile("bar.sync 1, %0;" ::"n"(kSortThreads) : "memory");
+      }
+    }
+  }
+}
+
+template <int LOG>
+__device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32_t want, int32_t* __restrict__ out) {
+  if (tid >= (1 << LOG) / 4) return;
+  const uint4 q = reinterpret_cast<const uint4*>(s.hist1)[tid];
+  uint32_t e0 = q.x, e1 = q.y, e2 = q.z, e3 = q.w;
+  sort_desc<LOG>(e0, e1, e2, e3, s.hist1, tid);
+  PKV_STAMP(9);
+  const uint32_t e[4] = {e0, e1, e2, e3};
+  int32_t v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = uint32_t(4 * tid + j) < want ? s.cand_idx[0xffffu - (e[j] & 0xffffu)] : -1;
+  if (4 * tid + 3 < k && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+    reinterpret_cast<int4*>(out)[tid] = make_int4(v[0], v[1], v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (4 * tid + j < k) out[4 * tid + j] = v[j];
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores, int n, long long ld,
+                                                                   int k, int32_t* __restrict__ idx, int slice) {
+  extern __shared__ __align__(16) uint16_t s_keys[];  // [slice + 16]
+  __shared__ Shared s;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  PKV_STAMP(0);
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = int(cluster.block_rank()), csize = int(cluster.num_blocks());
+  const int row = blockIdx.y;
+  const uint16_t* rp = scores + size_t(row) * size_t(ld);
+  const int lo = min(n, rank * slice), cnt = min(n, lo + slice) - lo;
+  // Position p of the cache holds element lo + p - mis, so 16-byte groups of the row are 16-byte groups of the cache.
+  const int mis = int((reinterpret_cast<uintptr_t>(rp) >> 1) & 7u);
+  const int padded = (mis + cnt + 7) & ~7;
+  const int groups = padded >> 3;
+  const uint4* s_groups = reinterpret_cast<const uint4*>(s_keys);
+
+  // ---- 1: load, cache, first histogram ----
+  for (int b = tid; b < kBins1; b += kThreads) s.hist1[b] = 0;
+  if (tid < kBins2) s.hist2[tid] = 0;
+  if (tid < mis) s_keys[tid] = 0;                                   // key 0 is never valid, never selected
+  if (tid < padded - (mis + cnt)) s_keys[mis + cnt + tid] = 0;
+  __syncthreads();
+  {
+    const auto count = [&](uint32_t key, int) {
+      if (key > kNegInfKey) atomicAdd(&s.hist1[key >> 4], 1u);
+    };
+    const int head = min(cnt, (8 - mis) & 7), nvec = (cnt - head) >> 3;
+    const uint16_t* src = rp + lo;
+    if (tid < head) {
+      const uint32_t key = key_one(__ldg(src + tid));
+      s_keys[mis + tid] = uint16_t(key);
+      count(key, 0);
+    }
+    const uint4* gv = reinterpret_cast<const uint4*>(src + head);
+    uint4* sv = reinterpret_cast<uint4*>(s_keys + mis + head);
+#pragma unroll 4
+    for (int v = tid; v < nvec; v += kThreads) {
+      uint4 q = __ldg(gv + v);
+      q.x = key_pair(q.x), q.y = key_pair(q.y), q.z = key_pair(q.z), q.w = key_pair(q.w);
+      sv[v] = q;
+      for_each_key(q, count);
+    }
+    for (int i = head + 8 * nvec + tid; i < cnt; i += kThreads) {
+      const uint32_t key = key_one(__ldg(src + i));
+      s_keys[mis + i] = uint16_t(key);
+      count(key, 0);
+    }
+  }
+  PKV_STAMP(1);
+  cluster.sync();  // barrier 1: every CTA's hist1 is complete
+  PKV_STAMP(2);
+
+  // Sum of the histograms for this thread's four bins, then the bin of the want-th largest key.
+  uint32_t r[4] = {0, 0, 0, 0};
+  for (int c = 0; c < csize; ++c) {
+    const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&s.hist1[4 * tid], c));
+    r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
+  }
+  const uint32_t local = r[0] + r[1] + r[2] + r[3];
+  uint32_t sfx = local;  // inclusive suffix sum over threads (higher bins first)
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_down_sync(0xffffffffu, sfx, o);
+    if (lane + o < 32) sfx += t;
+  }
+  if (lane == 0) s.wsum[warp] = sfx;
+  __syncthreads();
+  {
+    const uint32_t w = lane > warp ? s.wsum[lane] : 0u;  // the totals of the warps above this one
+    uint32_t t = w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    sfx += t;
+  }
+  if (tid == 0) s.total = sfx;
+  __syncthreads();
+  const uint32_t want = min(uint32_t(k), s.total);  // the same in every CTA of the cluster
+  if (want > 0) {
+    uint32_t above = sfx - local;
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      if (above < want && above + r[j] >= want) {
+        s.bin = uint32_t(4 * tid + j);
+        s.need = want - above;
+      }
+      above += r[j];
+    }
+  }
+  __syncthreads();
+  const uint32_t bin1 = want > 0 ? s.bin : 0xffffffffu, need1 = want > 0 ? s.need : 0u;
+  {
+    // This CTA's keys above the chosen bin (from its own histogram), published for the others.
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (uint32_t(4 * tid + j) > bin1) mine += s.hist1[4 * tid + j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) s.wsum2[warp] = mine;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t t = s.wsum2[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == 0) s.above1 = t;
+    }
+  }
+  PKV_STAMP(3);
+  // ---- 2: second histogram (low 4 bits) over this CTA's keys of the chosen bin ----
+  if (want > 0) {
+#pragma unroll 4
+    for (int g = tid; g < groups; g += kThreads) {
+      const uint4 q = s_groups[g];
+      for_each_key(q, [&](uint32_t key, int) {
+        if ((key >> 4) == bin1) atomicAdd(&s.hist2[key & 15u], 1u);
+      });
+    }
+  }
+  PKV_STAMP(4);
+  cluster.sync();  // barrier 2: hist2 and above1 of every CTA are complete; nobody reads hist1 any more
+  PKV_STAMP(5);
+
+  uint32_t thr = 0xffffffffu, need_ties = 0, base_above = 0, ties_before = 0, total_above = 0;
+  if (want > 0) {
+    if (tid < csize * kBins2) s.h2[tid >> 4][tid & 15] = *cluster.map_shared_rank(&s.hist2[tid & 15], tid >> 4);
+    if (tid >= 512 && tid < 512 + csize) s.cta_above[tid - 512] = *cluster.map_shared_rank(&s.above1, tid - 512);
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t h = 0;
+      if (lane < kBins2)
+        for (int c = 0; c < csize; ++c) h += s.h2[c][lane];
+      uint32_t sf = h;  // inclusive suffix over the bins (lanes 16..31 hold nothing)
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_down_sync(0xffffffffu, sf, o);
+        if (lane + o < 32) sf += t;
+      }
+      const uint32_t above = sf - h;
+      if (lane < kBins2 && above < need1 && sf >= need1) {
+        s.bin = uint32_t(lane);
+        s.need = need1 - above;
+      }
+    }
+    __syncthreads();
+    const uint32_t bin2 = s.bin;
+    need_ties = s.need;
+    thr = (bin1 << 4) | bin2;
+    if (warp < csize) {
+      uint32_t a = (lane < kBins2 && uint32_t(lane) > bin2) ? s.h2[warp][lane] : 0u;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0) {
+        s.cta_above[warp] += a;
+        s.cta_ties[warp] = s.h2[warp][bin2];
+      }
+    }
+    __syncthreads();
+    for (int c = 0; c < csize; ++c) {
+      if (c < rank) {
+        base_above += s.cta_above[c];
+        ties_before += s.cta_ties[c];
+      }
+      total_above += s.cta_above[c];
+    }
+  }
+  PKV_STAMP(6);
+  // ---- 3: place this CTA's selected keys, in index order, into CTA 0's candidate list ----
+  int log_size = 7;
+  while ((1 << log_size) < k) ++log_size;
+  if (rank == 0)
+    for (int i = int(want) + tid; i < (1 << log_size); i += kThreads) s.hist1[i] = 0;  // padding sorts last
+  if (want > 0) {
+    uint32_t* cand_key = cluster.map_shared_rank(s.hist1, 0);
+    int32_t* cand_idx = cluster.map_shared_rank(s.cand_idx, 0);
+    const int gw = (groups + kWarps - 1) / kWarps, g0 = warp * gw, g1 = min(groups, g0 + gw);
+    // first sweep: this warp's counts
+    uint32_t cntw = 0;
+#pragma unroll 4
+    for (int g = g0 + lane; g < g1; g += 32) cntw += count_selected(s_groups[g], thr);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cntw += __shfl_xor_sync(0xffffffffu, cntw, o);
+    if (lane == 0) s.wsum[warp] = cntw;
+    __syncthreads();
+    uint32_t before = lane < warp ? s.wsum[lane] : 0u;  // the counts of the warps before this one
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+    uint32_t a_pos = base_above + (before & 0xffffu);     // ordinal of this warp's next key above the threshold
+    uint32_t t_pos = ties_before + (before >> 16);        // rank of its next tie among the row's ties
+    // second sweep: 32 groups of 8 keys at a time; an exclusive scan over the lanes' counts gives every lane its place
+    if ((cntw & 0xffffu) != 0 || ((cntw >> 16) != 0 && t_pos < need_ties)) {
+      for (int g = g0; g < g1; g += 32) {
+        const int gl = g + lane;
+        uint4 q = make_uint4(0, 0, 0, 0);
+        if (gl < g1) q = s_groups[gl];
+        const uint32_t c = count_selected(q, thr);
+        if (__ballot_sync(0xffffffffu, c != 0) == 0) continue;  // nothing selected in these 256 keys
+        uint32_t inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += t;
+        }
+        const uint32_t tot = __shfl_sync(0xffffffffu, inc, 31), exc = inc - c;
+        uint32_t a = a_pos + (exc & 0xffffu), t = t_pos + (exc >> 16);
+        if (c != 0) {
+          const int i0 = lo + gl * 8 - mis;
+          for_each_key(q, [&](uint32_t key, int j) {
+            if (key > thr) {
+              cand_key[a] = (key << 16) | (0xffffu - a);
+              cand_idx[a] = i0 + j;
+              ++a;
+            } else if (key == thr) {
+              if (t < need_ties) {
+                const uint32_t o = total_above + t;
+                cand_key[o] = (key << 16) | (0xffffu - o);
+                cand_idx[o] = i0 + j;
+              }
+              ++t;
+            }
+          });
+        }
+        a_pos += tot & 0xffffu;
+        t_pos += tot >> 16;
+      }
+    }
+  }
+  PKV_STAMP(7);
+  cluster.sync();  // barrier 3: the candidate list in CTA 0 is complete; no remote access after this point
+  if (rank != 0) return;
+  PKV_STAMP(8);
+
+  // ---- sort in CTA 0: 2^log_size words (128..2048), four per thread, descending ----
+  int32_t* out = idx + size_t(row) * size_t(k);
+  switch (log_size) {
+    case 7: sort_and_write<7>(s, tid, k, want, out); break;
+    case 8: sort_and_write<8>(s, tid, k, want, out); break;
+    case 9: sort_and_write<9>(s, tid, k, want, out); break;
+    case 10: sort_and_write<10>(s, tid, k, want, out); break;
+    default: sort_and_write<11>(s, tid, k, want, out); break;
+  }
+  PKV_STAMP(10);
+}
+
+}  // namespace pkv_topkc
+
+extern "C" {  // library-internal (hidden visibility), declared in pkv_topk.cu
+
+// Whether the one-launch path takes this shape.
+bool pkv_topk_cluster_eligible(int T, int n, int k) {
+  using namespace pkv_topkc;
+  return T > 0 && T <= 65535 && n > 0 && k > 0 && k <= kMaxK && n <= kMaxCluster * kMaxSlice;
+}
+
+// CTAs per row: the fewest whose slices fit in shared memory, then doubled while the launch stays within about one
+// CTA per SM and a slice keeps at least 4096 keys.
+static int cluster_size_for(int T, int n, int sms) {
+  using namespace pkv_topkc;
+  int c = 1;
+  while (c < kMaxCluster && (n + c - 1) / c > kMaxSlice) c *= 2;
+  while (c < kMaxCluster && (long long)T * c * 2 <= sms + sms / 8 && n / (c * 2) >= 4096) c *= 2;
+  return c;
+}
+
+// Launches the cluster kernel; returns PKV_OK, or PKV_ERR_CUDA with `err` set. `usable` (per device, found on the first
+// call) is false when the device cannot co-schedule the largest cluster: the caller then takes the four-launch path.
+int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, cudaStream_t stream,
+                            bool* usable, std::string& err) {
+  using namespace pkv_topkc;
+  constexpr int kMaxDevices = 64;
+  static thread_local signed char state[kMaxDevices];  // 0 unknown, 1 usable, -1 not
+  static thread_local int sm_count[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *usable = false;
+    return PKV_OK;
+  }
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kMaxCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t c;
+  std::memset(&c, 0, sizeof(c));
+  c.blockDim = dim3(kThreads);
+  c.stream = stream;
+  c.attrs = attr;
+  if (state[dev] == 0) {
+    const size_t max_smem = size_t(kMaxSlice + 16) * 2;
+    e = cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(max_smem));
+    int clusters = 0, sms = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess) {
+      c.gridDim = dim3(kMaxCluster, 1);
+      c.dynamicSmemBytes = max_smem;
+      c.numAttrs = 1;
+      e = cudaOccupancyMaxActiveClusters(&clusters, topk_cluster_kernel, &c);
+    }
+    if (e != cudaSuccess) cudaGetLastError();  // not sticky: clear it
+    state[dev] = (e == cudaSuccess && clusters > 0 && sms > 0) ? 1 : -1;
+    sm_count[dev] = sms;
+  }
+  *usable = state[dev] == 1;
+  if (!*usable) return PKV_OK;
+  const int csize = cluster_size_for(T, n, sm_count[dev]);
+  const int slice = ((n + csize - 1) / csize + 7) & ~7;
+  attr[0].val.clusterDim.x = unsigned(csize);
+  c.gridDim = dim3(unsigned(csize), unsigned(T));
+  c.dynamicSmemBytes = size_t(slice + 16) * 2;
+  c.numAttrs = 2;
+  e = cudaLaunchKernelEx(&c, topk_cluster_kernel, scores, n, ld, k, idx, slice);
+  if (e != cudaSuccess) {
+    err = std::string("top-k cluster launch: ") + cudaGetErrorString(e);
+    return PKV_ERR_CUDA;
+  }
+  return PKV_OK;
+}
+
+}  // extern "C"
