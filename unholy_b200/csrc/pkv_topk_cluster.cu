@@ -45,8 +45,8 @@ constexpr int kMaxCluster = 8;
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxK = 2048;
-constexpr int kMaxSlice = 98304;          // keys per CTA kept in shared memory (192 KB)
-constexpr int kBins1 = 4096;              // top 12 bits: four bins per thread
+constexpr int kMaxSlice = 81920;          // keys per CTA kept in shared memory (160 KB, and 20 KB of group maxima)
+constexpr int kBins = 4096;               // top 12 bits: four bins per thread
 constexpr int kBins2 = 16;                // low 4 bits
 constexpr uint32_t kNegInfKey = 0x007Fu;  // key of the bf16 pattern 0xFF80; valid keys are above it (their top 12 bits >= 8)
 
@@ -55,7 +55,8 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) { return w ^ ((((w >> 1
 __device__ __forceinline__ uint32_t key_one(uint32_t b) { return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u); }
 
 struct __align__(16) Shared {
-  uint32_t hist1[kBins1];  // this CTA's first histogram; CTA 0 reuses it as the candidates' sort words after barrier 2
+  uint32_t hist0[kBins];   // histogram of the group maxima; CTA 0 reuses it as the candidates' sort words after barrier 2
+  uint32_t hist1[kBins];   // exact histogram of the keys still in the race
   int32_t cand_idx[kMaxK];
   uint32_t hist2[kBins2];
   uint32_t h2[kMaxCluster][kBins2];
@@ -69,6 +70,12 @@ template <class F>
 __device__ __forceinline__ void for_each_key(const uint4& q, F&& f) {
   f(q.x & 0xffffu, 0), f(q.x >> 16, 1), f(q.y & 0xffffu, 2), f(q.y >> 16, 3);
   f(q.z & 0xffffu, 4), f(q.z >> 16, 5), f(q.w & 0xffffu, 6), f(q.w >> 16, 7);
+}
+
+// The largest of the eight 16-bit keys of a group.
+__device__ __forceinline__ uint32_t group_max(const uint4& q) {
+  const uint32_t m = __vmaxu2(__vimax3_u16x2(q.x, q.y, q.z), q.w);
+  return max(m >> 16, m & 0xffffu);
 }
 
 // Keys above the threshold in the low half, keys equal to it in the high half.
@@ -126,9 +133,9 @@ __device__ __forceinline__ void sort_desc(uint32_t& e0, uint32_t& e1, uint32_t& 
 template <int LOG>
 __device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32_t want, int32_t* __restrict__ out) {
   if (tid >= (1 << LOG) / 4) return;
-  const uint4 q = reinterpret_cast<const uint4*>(s.hist1)[tid];
+  const uint4 q = reinterpret_cast<const uint4*>(s.hist0)[tid];
   uint32_t e0 = q.x, e1 = q.y, e2 = q.z, e3 = q.w;
-  sort_desc<LOG>(e0, e1, e2, e3, s.hist1, tid);
+  sort_desc<LOG>(e0, e1, e2, e3, s.hist0, tid);
   PKV_STAMP(9);
   const uint32_t e[4] = {e0, e1, e2, e3};
   int32_t v[4];
@@ -143,9 +150,76 @@ __device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32
   }
 }
 
+// Exclusive prefix sum over the CTA's threads (in thread order) and the total. Two barriers; uses s.wsum.
+__device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t v, uint32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) s.wsum[warp] = inc;
+  __syncthreads();
+  const uint32_t w = s.wsum[lane];
+  uint32_t before = lane < warp ? w : 0u, all = w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    all += __shfl_xor_sync(0xffffffffu, all, o);
+  }
+  __syncthreads();
+  total = all;
+  return before + inc - v;
+}
+
+// One suffix scan over the cluster's sum of a 4096-bin histogram (each thread owns four consecutive bins): returns the
+// total in s.total and, when need_fn(total) > 0, the highest bin with (count above it) < need <= (count from it up) in
+// s.bin and need - (count above it) in s.need. Ends with a barrier; the caller reads s.total / s.bin / s.need after it.
+template <class NeedFn>
+__device__ __forceinline__ void reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int csize,
+                                                NeedFn&& need_fn) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t r[4] = {0, 0, 0, 0};
+  for (int c = 0; c < csize; ++c) {
+    const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&hist[4 * tid], c));
+    r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
+  }
+  const uint32_t local = r[0] + r[1] + r[2] + r[3];
+  uint32_t sfx = local;  // inclusive suffix sum over threads (higher bins first)
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_down_sync(0xffffffffu, sfx, o);
+    if (lane + o < 32) sfx += t;
+  }
+  if (lane == 0) s.wsum[warp] = sfx;
+  __syncthreads();
+  {
+    uint32_t t = lane > warp ? s.wsum[lane] : 0u;  // the totals of the warps above this one
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    sfx += t;
+  }
+  if (tid == 0) s.total = sfx;
+  __syncthreads();
+  const uint32_t need = need_fn(s.total);
+  if (need > 0) {
+    uint32_t above = sfx - local;
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      if (above < need && above + r[j] >= need) {
+        s.bin = uint32_t(4 * tid + j);
+        s.need = need - above;
+      }
+      above += r[j];
+    }
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores, int n, long long ld,
                                                                    int k, int32_t* __restrict__ idx, int slice) {
-  extern __shared__ __align__(16) uint16_t s_keys[];  // [slice + 16]
+  extern __shared__ __align__(16) uint16_t s_keys[];  // keys [slice + 16], then group maxima [(slice + 16) / 8 + 8]
   __shared__ Shared s;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -159,82 +233,82 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   // Position p of the cache holds element lo + p - mis, so 16-byte groups of the row are 16-byte groups of the cache.
   const int mis = int((reinterpret_cast<uintptr_t>(rp) >> 1) & 7u);
   const int padded = (mis + cnt + 7) & ~7;
-  const int groups = padded >> 3;
+  const int groups = padded >> 3;            // groups of 8 keys
+  const int sgroups = (groups + 7) >> 3;     // groups of 8 group maxima = 64 keys
   const uint4* s_groups = reinterpret_cast<const uint4*>(s_keys);
+  uint16_t* s_gmax = s_keys + slice + 16;
+  const uint4* s_sg = reinterpret_cast<const uint4*>(s_gmax);
 
-  // ---- 1: load, cache, first histogram ----
-  for (int b = tid; b < kBins1; b += kThreads) s.hist1[b] = 0;
+  // ---- 1: load, cache, the largest key of every group of 8, histogram of those maxima (top 12 bits) ----
+  for (int b = tid; b < kBins; b += kThreads) s.hist0[b] = 0, s.hist1[b] = 0;
   if (tid < kBins2) s.hist2[tid] = 0;
   if (tid < mis) s_keys[tid] = 0;                                   // key 0 is never valid, never selected
   if (tid < padded - (mis + cnt)) s_keys[mis + cnt + tid] = 0;
+  if (tid < sgroups * 8 - groups) s_gmax[groups + tid] = 0;
   __syncthreads();
+  const int head = min(cnt, (8 - mis) & 7), nvec = (cnt - head) >> 3, gbase = (mis + head) >> 3;
   {
-    const auto count = [&](uint32_t key, int) {
-      if (key > kNegInfKey) atomicAdd(&s.hist1[key >> 4], 1u);
-    };
-    const int head = min(cnt, (8 - mis) & 7), nvec = (cnt - head) >> 3;
     const uint16_t* src = rp + lo;
-    if (tid < head) {
-      const uint32_t key = key_one(__ldg(src + tid));
-      s_keys[mis + tid] = uint16_t(key);
-      count(key, 0);
-    }
+    if (tid < head) s_keys[mis + tid] = uint16_t(key_one(__ldg(src + tid)));
     const uint4* gv = reinterpret_cast<const uint4*>(src + head);
     uint4* sv = reinterpret_cast<uint4*>(s_keys + mis + head);
-#pragma unroll 4
+#pragma unroll 8
     for (int v = tid; v < nvec; v += kThreads) {
       uint4 q = __ldg(gv + v);
       q.x = key_pair(q.x), q.y = key_pair(q.y), q.z = key_pair(q.z), q.w = key_pair(q.w);
       sv[v] = q;
-      for_each_key(q, count);
+      const uint32_t gm = group_max(q);
+      s_gmax[gbase + v] = uint16_t(gm);
+      if (gm > kNegInfKey) atomicAdd(&s.hist0[gm >> 4], 1u);
     }
-    for (int i = head + 8 * nvec + tid; i < cnt; i += kThreads) {
-      const uint32_t key = key_one(__ldg(src + i));
-      s_keys[mis + i] = uint16_t(key);
-      count(key, 0);
+    for (int i = head + 8 * nvec + tid; i < cnt; i += kThreads) s_keys[mis + i] = uint16_t(key_one(__ldg(src + i)));
+  }
+  __syncthreads();
+  if (tid < 2) {  // the first and the last group when the 16-byte loads did not cover them
+    const int g = tid == 0 ? 0 : groups - 1;
+    const bool todo = tid == 0 ? (groups > 0 && !(gbase == 0 && nvec > 0)) : (groups > 1 && gbase + nvec != groups);
+    if (todo) {
+      const uint32_t gm = group_max(s_groups[g]);
+      s_gmax[g] = uint16_t(gm);
+      if (gm > kNegInfKey) atomicAdd(&s.hist0[gm >> 4], 1u);
     }
   }
   PKV_STAMP(1);
-  cluster.sync();  // barrier 1: every CTA's hist1 is complete
+  cluster.sync();  // barrier 1: every CTA's hist0 is complete
   PKV_STAMP(2);
 
-  // Sum of the histograms for this thread's four bins, then the bin of the want-th largest key.
-  uint32_t r[4] = {0, 0, 0, 0};
-  for (int c = 0; c < csize; ++c) {
-    const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&s.hist1[4 * tid], c));
-    r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
-  }
-  const uint32_t local = r[0] + r[1] + r[2] + r[3];
-  uint32_t sfx = local;  // inclusive suffix sum over threads (higher bins first)
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t t = __shfl_down_sync(0xffffffffu, sfx, o);
-    if (lane + o < 32) sfx += t;
-  }
-  if (lane == 0) s.wsum[warp] = sfx;
-  __syncthreads();
+  // At least min(k, #valid groups) keys are >= the lower edge of the bin that holds the k-th largest group maximum;
+  // with fewer than k valid groups every valid key stays in the race.
+  reduce_and_pick(cluster, s, s.hist0, csize, [&](uint32_t valid_groups) { return valid_groups >= uint32_t(k) ? uint32_t(k) : 0u; });
+  const uint32_t floor_key = s.total >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
+  // ---- 2: the groups that still hold a key in the race, as a list in index order (it takes the place of the group
+  // maxima: every thread reads the maxima of its two supergroups before anyone writes), then the exact histogram
+  // (top 12 bits) of their keys >= floor_key. Lanes work on listed groups only, so no lane idles on the other 7/8. ----
+  uint16_t* s_list = s_gmax;
+  uint32_t listed = 0;
   {
-    const uint32_t w = lane > warp ? s.wsum[lane] : 0u;  // the totals of the warps above this one
-    uint32_t t = w;
+    uint32_t mask[2] = {0, 0};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    sfx += t;
-  }
-  if (tid == 0) s.total = sfx;
-  __syncthreads();
-  const uint32_t want = min(uint32_t(k), s.total);  // the same in every CTA of the cluster
-  if (want > 0) {
-    uint32_t above = sfx - local;
-#pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      if (above < want && above + r[j] >= want) {
-        s.bin = uint32_t(4 * tid + j);
-        s.need = want - above;
-      }
-      above += r[j];
+    for (int u = 0; u < 2; ++u) {
+      const int sg = 2 * tid + u;
+      if (sg < sgroups) for_each_key(s_sg[sg], [&](uint32_t gm, int j) { mask[u] |= (gm >= floor_key ? 1u : 0u) << j; });
     }
+    uint32_t pos = block_exclusive_scan(s, uint32_t(__popc(mask[0]) + __popc(mask[1])), listed);
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      for (uint32_t m = mask[u]; m != 0; m &= m - 1) s_list[pos++] = uint16_t((2 * tid + u) * 8 + (__ffs(int(m)) - 1));
   }
   __syncthreads();
+  for (uint32_t e = tid; e < listed; e += kThreads)
+    for_each_key(s_groups[s_list[e]], [&](uint32_t key, int) {
+      if (key >= floor_key) atomicAdd(&s.hist1[key >> 4], 1u);
+    });
+  PKV_STAMP(3);
+  cluster.sync();  // barrier 2: every CTA's hist1 is complete; nobody reads hist0 any more
+  PKV_STAMP(4);
+
+  reduce_and_pick(cluster, s, s.hist1, csize, [&](uint32_t in_race) { return min(uint32_t(k), in_race); });
+  const uint32_t want = min(uint32_t(k), s.total);  // the same in every CTA of the cluster
   const uint32_t bin1 = want > 0 ? s.bin : 0xffffffffu, need1 = want > 0 ? s.need : 0u;
   {
     // This CTA's keys above the chosen bin (from its own histogram), published for the others.
@@ -253,20 +327,15 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       if (lane == 0) s.above1 = t;
     }
   }
-  PKV_STAMP(3);
-  // ---- 2: second histogram (low 4 bits) over this CTA's keys of the chosen bin ----
-  if (want > 0) {
-#pragma unroll 4
-    for (int g = tid; g < groups; g += kThreads) {
-      const uint4 q = s_groups[g];
-      for_each_key(q, [&](uint32_t key, int) {
+  // ---- 3: histogram of the low 4 bits over this CTA's keys of the chosen bin ----
+  if (want > 0)
+    for (uint32_t e = tid; e < listed; e += kThreads)
+      for_each_key(s_groups[s_list[e]], [&](uint32_t key, int) {
         if ((key >> 4) == bin1) atomicAdd(&s.hist2[key & 15u], 1u);
       });
-    }
-  }
-  PKV_STAMP(4);
-  cluster.sync();  // barrier 2: hist2 and above1 of every CTA are complete; nobody reads hist1 any more
   PKV_STAMP(5);
+  cluster.sync();  // barrier 3: hist2 and above1 of every CTA are complete
+  PKV_STAMP(6);
 
   uint32_t thr = 0xffffffffu, need_ties = 0, base_above = 0, ties_before = 0, total_above = 0;
   if (want > 0) {
@@ -311,69 +380,52 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       total_above += s.cta_above[c];
     }
   }
-  PKV_STAMP(6);
-  // ---- 3: place this CTA's selected keys, in index order, into CTA 0's candidate list ----
+  // ---- 4: place this CTA's selected keys, in index order, into CTA 0's candidate list ----
   int log_size = 7;
   while ((1 << log_size) < k) ++log_size;
   if (rank == 0)
-    for (int i = int(want) + tid; i < (1 << log_size); i += kThreads) s.hist1[i] = 0;  // padding sorts last
+    for (int i = int(want) + tid; i < (1 << log_size); i += kThreads) s.hist0[i] = 0;  // padding sorts last
   if (want > 0) {
-    uint32_t* cand_key = cluster.map_shared_rank(s.hist1, 0);
+    uint32_t* cand_key = cluster.map_shared_rank(s.hist0, 0);
     int32_t* cand_idx = cluster.map_shared_rank(s.cand_idx, 0);
-    const int gw = (groups + kWarps - 1) / kWarps, g0 = warp * gw, g1 = min(groups, g0 + gw);
-    // first sweep: this warp's counts
-    uint32_t cntw = 0;
-#pragma unroll 4
-    for (int g = g0 + lane; g < g1; g += 32) cntw += count_selected(s_groups[g], thr);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) cntw += __shfl_xor_sync(0xffffffffu, cntw, o);
-    if (lane == 0) s.wsum[warp] = cntw;
-    __syncthreads();
-    uint32_t before = lane < warp ? s.wsum[lane] : 0u;  // the counts of the warps before this one
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
-    uint32_t a_pos = base_above + (before & 0xffffu);     // ordinal of this warp's next key above the threshold
-    uint32_t t_pos = ties_before + (before >> 16);        // rank of its next tie among the row's ties
-    // second sweep: 32 groups of 8 keys at a time; an exclusive scan over the lanes' counts gives every lane its place
-    if ((cntw & 0xffffu) != 0 || ((cntw >> 16) != 0 && t_pos < need_ties)) {
-      for (int g = g0; g < g1; g += 32) {
-        const int gl = g + lane;
-        uint4 q = make_uint4(0, 0, 0, 0);
-        if (gl < g1) q = s_groups[gl];
-        const uint32_t c = count_selected(q, thr);
-        if (__ballot_sync(0xffffffffu, c != 0) == 0) continue;  // nothing selected in these 256 keys
-        uint32_t inc = c;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-          if (lane >= o) inc += t;
-        }
-        const uint32_t tot = __shfl_sync(0xffffffffu, inc, 31), exc = inc - c;
-        uint32_t a = a_pos + (exc & 0xffffu), t = t_pos + (exc >> 16);
-        if (c != 0) {
-          const int i0 = lo + gl * 8 - mis;
-          for_each_key(q, [&](uint32_t key, int j) {
-            if (key > thr) {
-              cand_key[a] = (key << 16) | (0xffffu - a);
-              cand_idx[a] = i0 + j;
-              ++a;
-            } else if (key == thr) {
-              if (t < need_ties) {
-                const uint32_t o = total_above + t;
-                cand_key[o] = (key << 16) | (0xffffu - o);
-                cand_idx[o] = i0 + j;
-              }
-              ++t;
-            }
-          });
-        }
-        a_pos += tot & 0xffffu;
-        t_pos += tot >> 16;
+    // The listed groups are in index order: an exclusive scan over the threads' counts (keys above the threshold in
+    // the low half of a word, ties in the high half) gives every thread the places of its group's keys.
+    uint32_t a_pos = base_above, t_pos = ties_before;
+    for (uint32_t e0 = 0; e0 < listed; e0 += kThreads) {
+      const uint32_t e = e0 + tid;
+      uint4 q = make_uint4(0, 0, 0, 0);
+      int g = 0;
+      if (e < listed) {
+        g = s_list[e];
+        q = s_groups[g];
       }
+      const uint32_t c = count_selected(q, thr);
+      uint32_t tot;
+      const uint32_t exc = block_exclusive_scan(s, c, tot);
+      uint32_t a = a_pos + (exc & 0xffffu), t = t_pos + (exc >> 16);
+      if (c != 0) {
+        const int i0 = lo + g * 8 - mis;
+        for_each_key(q, [&](uint32_t key, int j) {
+          if (key > thr) {
+            cand_key[a] = (key << 16) | (0xffffu - a);
+            cand_idx[a] = i0 + j;
+            ++a;
+          } else if (key == thr) {
+            if (t < need_ties) {
+              const uint32_t o = total_above + t;
+              cand_key[o] = (key << 16) | (0xffffu - o);
+              cand_idx[o] = i0 + j;
+            }
+            ++t;
+          }
+        });
+      }
+      a_pos += tot & 0xffffu;
+      t_pos += tot >> 16;
     }
   }
   PKV_STAMP(7);
-  cluster.sync();  // barrier 3: the candidate list in CTA 0 is complete; no remote access after this point
+  cluster.sync();  // barrier 4: the candidate list in CTA 0 is complete; no remote access after this point
   if (rank != 0) return;
   PKV_STAMP(8);
 
@@ -389,6 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   PKV_STAMP(10);
 }
 
+
 }  // namespace pkv_topkc
 
 extern "C" {  // library-internal (hidden visibility), declared in pkv_topk.cu
@@ -398,6 +451,9 @@ bool pkv_topk_cluster_eligible(int T, int n, int k) {
   using namespace pkv_topkc;
   return T > 0 && T <= 65535 && n > 0 && k > 0 && k <= kMaxK && n <= kMaxCluster * kMaxSlice;
 }
+
+// Keys [slice + 16] and group maxima [(slice + 16) / 8 + 8], 16 bits each.
+static size_t smem_bytes(int slice) { return size_t(slice + 16) * 2 + size_t((slice + 16) / 8 + 8) * 2; }
 
 // CTAs per row: the fewest whose slices fit in shared memory, then doubled while the launch stays within about one
 // CTA per SM and a slice keeps at least 4096 keys.
@@ -436,7 +492,7 @@ int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, 
   c.stream = stream;
   c.attrs = attr;
   if (state[dev] == 0) {
-    const size_t max_smem = size_t(kMaxSlice + 16) * 2;
+    const size_t max_smem = smem_bytes(kMaxSlice);
     e = cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(max_smem));
     int clusters = 0, sms = 0;
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -456,7 +512,7 @@ int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, 
   const int slice = ((n + csize - 1) / csize + 7) & ~7;
   attr[0].val.clusterDim.x = unsigned(csize);
   c.gridDim = dim3(unsigned(csize), unsigned(T));
-  c.dynamicSmemBytes = size_t(slice + 16) * 2;
+  c.dynamicSmemBytes = smem_bytes(slice);
   c.numAttrs = 2;
   e = cudaLaunchKernelEx(&c, topk_cluster_kernel, scores, n, ld, k, idx, slice);
   if (e != cudaSuccess) {
