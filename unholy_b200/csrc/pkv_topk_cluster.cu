@@ -33,7 +33,7 @@
 namespace cg = cooperative_groups;
 
 #ifdef PKV_TOPK_TIMING  // development only: cycle stamps of row 0, CTA 0, thread 0
-__device__ long long g_topk_stamps[16];
+__device__ long long g_topk_stamps[32];
 #define PKV_STAMP(i) do { if (blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 0) g_topk_stamps[i] = clock64(); } while (0)
 #else
 #define PKV_STAMP(i) do { } while (0)
@@ -59,11 +59,10 @@ struct __align__(16) Shared {
   uint32_t hist1[kBins];   // exact histogram of the keys still in the race
   int32_t cand_idx[kMaxK];
   uint32_t hist2[kBins2];
-  uint32_t h2[kMaxCluster][kBins2];
+  unsigned long long wsum64[kWarps];
   uint32_t wsum[kWarps], wsum2[kWarps];
-  uint32_t cta_above[kMaxCluster], cta_ties[kMaxCluster];
   uint32_t above1;         // this CTA's keys in bins above the chosen one: read by the others after barrier 2
-  uint32_t bin, need, total;
+  uint32_t bin, need;
 };
 
 template <class F>
@@ -173,15 +172,34 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t v, 
   return before + inc - v;
 }
 
-// One suffix scan over the cluster's sum of a 4096-bin histogram (each thread owns four consecutive bins): returns the
-// total in s.total and, when need_fn(total) > 0, the highest bin with (count above it) < need <= (count from it up) in
-// s.bin and need - (count above it) in s.need. Ends with a barrier; the caller reads s.total / s.bin / s.need after it.
+// The same for 64-bit values (two counters side by side), without the total.
+__device__ __forceinline__ unsigned long long block_exclusive_scan(Shared& s, unsigned long long v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) s.wsum64[warp] = inc;
+  __syncthreads();
+  unsigned long long before = lane < warp ? s.wsum64[lane] : 0ull;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  __syncthreads();
+  return before + inc - v;
+}
+
+// One suffix scan over the sum of the 4096-bin histograms of CTAs c0 .. c0 + nc - 1 of the cluster (each thread owns
+// four consecutive bins). Returns the total; when need_fn(total) > 0, s.bin is the highest bin with
+// (count above it) < need <= (count from it up) and s.need = need - (count above it). Two barriers; the caller reads
+// s.bin / s.need after the call.
 template <class NeedFn>
-__device__ __forceinline__ void reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int csize,
-                                                NeedFn&& need_fn) {
+__device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int c0, int nc,
+                                                    NeedFn&& need_fn) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint32_t r[4] = {0, 0, 0, 0};
-  for (int c = 0; c < csize; ++c) {
+  for (int c = c0; c < c0 + nc; ++c) {
     const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&hist[4 * tid], c));
     r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
   }
@@ -194,15 +212,15 @@ __device__ __forceinline__ void reduce_and_pick(cg::cluster_group& cluster, Shar
   }
   if (lane == 0) s.wsum[warp] = sfx;
   __syncthreads();
-  {
-    uint32_t t = lane > warp ? s.wsum[lane] : 0u;  // the totals of the warps above this one
+  const uint32_t w = s.wsum[lane];
+  uint32_t higher = lane > warp ? w : 0u, total = w;  // the totals of the warps above this one, and of all warps
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    sfx += t;
+  for (int o = 16; o > 0; o >>= 1) {
+    higher += __shfl_xor_sync(0xffffffffu, higher, o);
+    total += __shfl_xor_sync(0xffffffffu, total, o);
   }
-  if (tid == 0) s.total = sfx;
-  __syncthreads();
-  const uint32_t need = need_fn(s.total);
+  sfx += higher;
+  const uint32_t need = need_fn(total);
   if (need > 0) {
     uint32_t above = sfx - local;
 #pragma unroll
@@ -215,6 +233,7 @@ __device__ __forceinline__ void reduce_and_pick(cg::cluster_group& cluster, Shar
     }
   }
   __syncthreads();
+  return total;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores, int n, long long ld,
@@ -273,14 +292,17 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       if (gm > kNegInfKey) atomicAdd(&s.hist0[gm >> 4], 1u);
     }
   }
+  __syncthreads();
   PKV_STAMP(1);
-  cluster.sync();  // barrier 1: every CTA's hist0 is complete
-  PKV_STAMP(2);
 
-  // At least min(k, #valid groups) keys are >= the lower edge of the bin that holds the k-th largest group maximum;
-  // with fewer than k valid groups every valid key stays in the race.
-  reduce_and_pick(cluster, s, s.hist0, csize, [&](uint32_t valid_groups) { return valid_groups >= uint32_t(k) ? uint32_t(k) : 0u; });
-  const uint32_t floor_key = s.total >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
+  // This CTA's floor: with at least k valid groups here, at least k of this CTA's keys are >= the lower edge of the
+  // bin that holds its k-th largest group maximum, so the row's k-th largest key is too, and no key below the floor can
+  // be selected; with fewer valid groups every valid key of this CTA stays in the race. (Floors differ between the
+  // CTAs; the bins of hist1 from the row's threshold bin upwards are complete in every CTA, and only those decide.)
+  const uint32_t valid_groups =
+      reduce_and_pick(cluster, s, s.hist0, rank, 1, [&](uint32_t v) { return v >= uint32_t(k) ? uint32_t(k) : 0u; });
+  const uint32_t floor_key = valid_groups >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
+  PKV_STAMP(2);
   // ---- 2: the groups that still hold a key in the race, as a list in index order (it takes the place of the group
   // maxima: every thread reads the maxima of its two supergroups before anyone writes), then the exact histogram
   // (top 12 bits) of their keys >= floor_key. Lanes work on listed groups only, so no lane idles on the other 7/8. ----
@@ -293,22 +315,26 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       const int sg = 2 * tid + u;
       if (sg < sgroups) for_each_key(s_sg[sg], [&](uint32_t gm, int j) { mask[u] |= (gm >= floor_key ? 1u : 0u) << j; });
     }
+    PKV_STAMP(11);
     uint32_t pos = block_exclusive_scan(s, uint32_t(__popc(mask[0]) + __popc(mask[1])), listed);
+    PKV_STAMP(12);
 #pragma unroll
     for (int u = 0; u < 2; ++u)
       for (uint32_t m = mask[u]; m != 0; m &= m - 1) s_list[pos++] = uint16_t((2 * tid + u) * 8 + (__ffs(int(m)) - 1));
   }
   __syncthreads();
+  PKV_STAMP(13);
   for (uint32_t e = tid; e < listed; e += kThreads)
     for_each_key(s_groups[s_list[e]], [&](uint32_t key, int) {
       if (key >= floor_key) atomicAdd(&s.hist1[key >> 4], 1u);
     });
   PKV_STAMP(3);
-  cluster.sync();  // barrier 2: every CTA's hist1 is complete; nobody reads hist0 any more
+  cluster.sync();  // barrier 1: every CTA's hist1 is complete
   PKV_STAMP(4);
 
-  reduce_and_pick(cluster, s, s.hist1, csize, [&](uint32_t in_race) { return min(uint32_t(k), in_race); });
-  const uint32_t want = min(uint32_t(k), s.total);  // the same in every CTA of the cluster
+  const uint32_t in_race = reduce_and_pick(cluster, s, s.hist1, 0, csize, [&](uint32_t v) { return min(uint32_t(k), v); });
+  const uint32_t want = min(uint32_t(k), in_race);  // the same in every CTA of the cluster
+  PKV_STAMP(14);
   const uint32_t bin1 = want > 0 ? s.bin : 0xffffffffu, need1 = want > 0 ? s.need : 0u;
   {
     // This CTA's keys above the chosen bin (from its own histogram), published for the others.
@@ -327,6 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       if (lane == 0) s.above1 = t;
     }
   }
+  PKV_STAMP(15);
   // ---- 3: histogram of the low 4 bits over this CTA's keys of the chosen bin ----
   if (want > 0)
     for (uint32_t e = tid; e < listed; e += kThreads)
@@ -334,52 +361,45 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
         if ((key >> 4) == bin1) atomicAdd(&s.hist2[key & 15u], 1u);
       });
   PKV_STAMP(5);
-  cluster.sync();  // barrier 3: hist2 and above1 of every CTA are complete
+  cluster.sync();  // barrier 2: hist2 and above1 of every CTA are complete
   PKV_STAMP(6);
 
   uint32_t thr = 0xffffffffu, need_ties = 0, base_above = 0, ties_before = 0, total_above = 0;
   if (want > 0) {
-    if (tid < csize * kBins2) s.h2[tid >> 4][tid & 15] = *cluster.map_shared_rank(&s.hist2[tid & 15], tid >> 4);
-    if (tid >= 512 && tid < 512 + csize) s.cta_above[tid - 512] = *cluster.map_shared_rank(&s.above1, tid - 512);
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t h = 0;
-      if (lane < kBins2)
-        for (int c = 0; c < csize; ++c) h += s.h2[c][lane];
-      uint32_t sf = h;  // inclusive suffix over the bins (lanes 16..31 hold nothing)
+    // Every warp works this out on its own from the CTAs' hist2 (lane b < 16 holds bin b): no barrier.
+    uint32_t hc[kMaxCluster], h = 0;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_down_sync(0xffffffffu, sf, o);
-        if (lane + o < 32) sf += t;
-      }
-      const uint32_t above = sf - h;
-      if (lane < kBins2 && above < need1 && sf >= need1) {
-        s.bin = uint32_t(lane);
-        s.need = need1 - above;
-      }
+    for (int c = 0; c < kMaxCluster; ++c) {
+      hc[c] = (c < csize && lane < kBins2) ? *cluster.map_shared_rank(&s.hist2[lane & (kBins2 - 1)], c) : 0u;
+      h += hc[c];
     }
-    __syncthreads();
-    const uint32_t bin2 = s.bin;
-    need_ties = s.need;
-    thr = (bin1 << 4) | bin2;
-    if (warp < csize) {
-      uint32_t a = (lane < kBins2 && uint32_t(lane) > bin2) ? s.h2[warp][lane] : 0u;
+    uint32_t sf = h;  // inclusive suffix over the bins (lanes 16..31 hold nothing)
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (lane == 0) {
-        s.cta_above[warp] += a;
-        s.cta_ties[warp] = s.h2[warp][bin2];
-      }
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_down_sync(0xffffffffu, sf, o);
+      if (lane + o < 32) sf += t;
     }
-    __syncthreads();
-    for (int c = 0; c < csize; ++c) {
-      if (c < rank) {
-        base_above += s.cta_above[c];
-        ties_before += s.cta_ties[c];
+    const uint32_t above = sf - h;
+    const int bin2 = __ffs(int(__ballot_sync(0xffffffffu, lane < kBins2 && above < need1 && sf >= need1))) - 1;
+    need_ties = need1 - __shfl_sync(0xffffffffu, above, bin2);
+    thr = (bin1 << 4) | uint32_t(bin2);
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) {
+      if (c < csize) {
+        uint32_t a = lane > bin2 ? hc[c] : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        a += *cluster.map_shared_rank(&s.above1, c);
+        const uint32_t t = __shfl_sync(0xffffffffu, hc[c], bin2);
+        if (c < rank) {
+          base_above += a;
+          ties_before += t;
+        }
+        total_above += a;
       }
-      total_above += s.cta_above[c];
     }
   }
+  PKV_STAMP(16);
   // ---- 4: place this CTA's selected keys, in index order, into CTA 0's candidate list ----
   int log_size = 7;
   while ((1 << log_size) < k) ++log_size;
@@ -388,22 +408,25 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   if (want > 0) {
     uint32_t* cand_key = cluster.map_shared_rank(s.hist0, 0);
     int32_t* cand_idx = cluster.map_shared_rank(s.cand_idx, 0);
-    // The listed groups are in index order: an exclusive scan over the threads' counts (keys above the threshold in
-    // the low half of a word, ties in the high half) gives every thread the places of its group's keys.
-    uint32_t a_pos = base_above, t_pos = ties_before;
-    for (uint32_t e0 = 0; e0 < listed; e0 += kThreads) {
-      const uint32_t e = e0 + tid;
-      uint4 q = make_uint4(0, 0, 0, 0);
-      int g = 0;
-      if (e < listed) {
-        g = s_list[e];
-        q = s_groups[g];
-      }
-      const uint32_t c = count_selected(q, thr);
-      uint32_t tot;
-      const uint32_t exc = block_exclusive_scan(s, c, tot);
-      uint32_t a = a_pos + (exc & 0xffffu), t = t_pos + (exc >> 16);
-      if (c != 0) {
+    // The listed groups are in index order and every thread takes a contiguous run of them: one exclusive scan over
+    // the threads' counts (keys above the threshold in the low word, ties in the high word) gives every thread the
+    // places of its keys.
+    const uint32_t per = (listed + kThreads - 1) / kThreads;
+    const uint32_t e0 = min(listed, uint32_t(tid) * per), e1 = min(listed, e0 + per);
+    unsigned long long c = 0;
+    for (uint32_t e = e0; e < e1; ++e) {
+      const uint32_t cs = count_selected(s_groups[s_list[e]], thr);
+      c += (cs & 0xffffu) | (static_cast<unsigned long long>(cs >> 16) << 32);
+    }
+    PKV_STAMP(17);
+    const unsigned long long exc = block_exclusive_scan(s, c);
+    PKV_STAMP(18);
+    uint32_t a = base_above + uint32_t(exc), t = ties_before + uint32_t(exc >> 32);
+    if (c != 0)
+      for (uint32_t e = e0; e < e1; ++e) {
+        const int g = s_list[e];
+        const uint4 q = s_groups[g];
+        if (count_selected(q, thr) == 0) continue;
         const int i0 = lo + g * 8 - mis;
         for_each_key(q, [&](uint32_t key, int j) {
           if (key > thr) {
@@ -420,12 +443,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
           }
         });
       }
-      a_pos += tot & 0xffffu;
-      t_pos += tot >> 16;
-    }
   }
   PKV_STAMP(7);
-  cluster.sync();  // barrier 4: the candidate list in CTA 0 is complete; no remote access after this point
+  cluster.sync();  // barrier 3: the candidate list in CTA 0 is complete; no remote access after this point
   if (rank != 0) return;
   PKV_STAMP(8);
 
