@@ -1048,7 +1048,7 @@ def run_topk(args):
     reps = max(args.steps, 10)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     us_by_path, ok = {}, True
-    for path in (1, 0):   # knob 7: 1 = four launches through the scratch, 0 = one launch of 8-CTA clusters (the default)
+    for path in (1, 0):   # knob 7: 1 = four launches through the scratch, 0 = one launch of thread-block clusters (the default)
         capi.check(lib.pkv_tune(7, path))
         idx.fill_(-7)
         for _ in range(3):
@@ -1086,7 +1086,7 @@ def run_topk(args):
     nbytes32 = T * n32 * 4 + T * k32 * 4
     nbytes = T * n * 2 + T * k * 4
     _emit("topk", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
-        "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16: one launch of 8-CTA clusters; the four-launch path uses {words * 4} B of caller scratch)"},
+        "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16: one launch of thread-block clusters, 2 CTAs per row here; the four-launch path uses {words * 4} B of caller scratch)"},
         "us_per_call": round(us, 2), "us_per_call_four_launches": round(us_by_path[1], 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok},
         "f32_twin": {"workload": f"top-{k32} of {n32} fp32 scores x {T} rows (pkv_topk_f32, no scratch)",
                      "us_per_call": round(us32, 2), "GBps": round(nbytes32 / (us32 * 1e-6) / 1e9, 1),

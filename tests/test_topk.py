@@ -58,7 +58,7 @@ def test_oracle_topk_matches_contract(kind):
                                       (6, 1000, 1003, 64), (2, 524288, 524288, 2048), (1, 524289, 524289, 300), (1, 800000, 800000, 300), (16, 40000, 40000, 1000),
                                       (3, 7, 9, 2), (2, 65, 65, 129), (2, 655360, 655360, 2048)])
 def test_topk_bf16_gpu(pkv, cuda, kind, T, n, ld, k):
-    """Both paths of pkv_topk_bf16 (knob 7: 0 = one launch of 8-CTA clusters where the shape allows it — k <= 2048,
+    """Both paths of pkv_topk_bf16 (knob 7: 0 = one launch of thread-block clusters where the shape allows it — k <= 2048,
     n <= 655,360 —, 1 = the four launches through the scratch) against the oracle."""
     g = tl.rng(71)
     s = scores_case(g, T, n, ld, kind)

@@ -6,21 +6,28 @@
 //
 // The four-launch path in pkv_topk.cu reads a row three times (the second and third time from L2) and passes
 // histograms, offsets and candidates through global scratch. Here the CTAs of a cluster split the row, every CTA reads
-// its slice from HBM once and keeps the keys in shared memory (up to 192 KB: one CTA of 1024 threads per SM), and the
+// its slice from HBM once and keeps the keys in shared memory (up to 160 KB: one CTA of 1024 threads per SM), and the
 // CTAs exchange their histograms through distributed shared memory. The cluster size is chosen by the host so that
 // the launch is about one CTA per SM (64 rows of 131,072 keys: 2 CTAs per row on 128 SMs):
-//   1. load the slice, keys to shared memory, histogram of the top 12 key bits (sign, exponent, three mantissa bits:
-//      scores of similar magnitude still spread over dozens of bins, so the shared-memory atomics do not pile up);
-//      cluster barrier; every CTA sums the histograms and finds the bin of the k-th largest key;
-//   2. histogram of the low 4 bits over the keys of that bin; cluster barrier; the threshold key, the number of
-//      threshold ties to take, and for every CTA how many selected keys the CTAs before it hold;
-//   3. every CTA writes its selected keys, in index order, into the candidate list in CTA 0's shared memory (remote
+//   1. load the slice (16-byte loads), keys to shared memory together with the largest key of every group of 8
+//      (DPX three-way 16-bit maxima), histogram of those group maxima by their top 12 bits. With at least k groups
+//      whose maximum is >= x, at least k keys are >= x: the bin of the k-th largest group maximum gives this CTA a
+//      floor below which no key can be selected. Cluster barrier A; the row's floor `base` is the largest of the CTAs'.
+//   2. the groups with a key >= base are compacted, in index order, into a list (about a quarter of the groups for
+//      k = 2048 of 131,072): every later pass walks the list with all lanes busy;
+//   3. exact counts, one bin per key value, of the keys in the window [base, base + 4096) — equal scores are the only
+//      same-address atomics —, keys above the window counted apart; cluster barrier B; the sum over the CTAs gives the
+//      threshold key and the number of threshold ties to take. (If the keys above the window alone reach k, a coarse
+//      histogram names the 16 keys around the threshold and a second round of the same pass looks at those: two rounds
+//      at most, two more barriers.) Every CTA publishes how many selected keys it holds; cluster barrier C;
+//   4. every CTA writes its selected keys, in index order, into the candidate list in CTA 0's shared memory (remote
 //      stores). A candidate is (key << 16 | 0xffff - ordinal) plus its index: the ordinal is the candidate's place
 //      in index order, so sorting the 32-bit words descending IS the (score descending, index ascending) order;
-//      cluster barrier; CTA 0 sorts the words (bitonic network unrolled at compile time, four words per thread in
+//      cluster barrier D; CTA 0 sorts the words (bitonic network unrolled at compile time, four words per thread in
 //      registers: strides up to 64 are register or shuffle exchanges) and writes the indices.
-// Every thread of every CTA passes the same three cluster barriers whatever the data (no early exit before the last
-// one), and no CTA touches another's shared memory after the last barrier.
+// Every thread of every CTA passes the same cluster barriers whatever its own data (the branch that adds a round is
+// taken from cluster-wide sums, identical in every CTA; no early exit before the last barrier), and no CTA touches
+// another's shared memory after the last barrier.
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
@@ -32,13 +39,6 @@
 
 namespace cg = cooperative_groups;
 
-#ifdef PKV_TOPK_TIMING  // development only: cycle stamps of row 0, CTA 0, thread 0
-__device__ long long g_topk_stamps[32];
-#define PKV_STAMP(i) do { if (blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 0) g_topk_stamps[i] = clock64(); } while (0)
-#else
-#define PKV_STAMP(i) do { } while (0)
-#endif
-
 namespace pkv_topkc {
 
 constexpr int kMaxCluster = 8;
@@ -47,7 +47,6 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxK = 2048;
 constexpr int kMaxSlice = 81920;          // keys per CTA kept in shared memory (160 KB, and 20 KB of group maxima)
 constexpr int kBins = 4096;               // top 12 bits: four bins per thread
-constexpr int kBins2 = 16;                // low 4 bits
 constexpr uint32_t kNegInfKey = 0x007Fu;  // key of the bf16 pattern 0xFF80; valid keys are above it (their top 12 bits >= 8)
 
 // Two bf16 patterns in one word -> their order-preserving keys: ~b when the sign is set, b | 0x8000 otherwise.
@@ -55,13 +54,15 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) { return w ^ ((((w >> 1
 __device__ __forceinline__ uint32_t key_one(uint32_t b) { return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u); }
 
 struct __align__(16) Shared {
-  uint32_t hist0[kBins];   // histogram of the group maxima; CTA 0 reuses it as the candidates' sort words after barrier 2
-  uint32_t hist1[kBins];   // exact histogram of the keys still in the race
+  uint32_t hist0[kBins];   // group maxima by their top 12 bits; then the keys above the window, 16 to a bin; after
+                           // barrier C, in CTA 0, the candidates' sort words
+  uint32_t fine[kBins];    // exact counts of the keys base + v of the window
   int32_t cand_idx[kMaxK];
-  uint32_t hist2[kBins2];
   unsigned long long wsum64[kWarps];
   uint32_t wsum[kWarps], wsum2[kWarps];
-  uint32_t above1;         // this CTA's keys in bins above the chosen one: read by the others after barrier 2
+  uint32_t floor_pub;      // this CTA's floor: read by the others after barrier A
+  uint32_t over;           // this CTA's keys above the window
+  uint32_t pub_above, pub_ties;  // this CTA's selected keys above the threshold, and its ties: read after barrier C
   uint32_t bin, need;
 };
 
@@ -75,6 +76,19 @@ __device__ __forceinline__ void for_each_key(const uint4& q, F&& f) {
 __device__ __forceinline__ uint32_t group_max(const uint4& q) {
   const uint32_t m = __vmaxu2(__vimax3_u16x2(q.x, q.y, q.z), q.w);
   return max(m >> 16, m & 0xffffu);
+}
+
+// Key j (0..7) of a group.
+__device__ __forceinline__ uint32_t key_at(const uint4& q, int j) {
+  const uint32_t w = (j & 4) ? ((j & 2) ? q.w : q.z) : ((j & 2) ? q.y : q.x);
+  return (j & 1) ? (w >> 16) : (w & 0xffffu);
+}
+
+// Bit j set when key j of the group is >= floor_key.
+__device__ __forceinline__ uint32_t mask_at_least(const uint4& q, uint32_t floor_key) {
+  uint32_t m = 0;
+  for_each_key(q, [&](uint32_t key, int j) { m |= (key >= floor_key ? 1u : 0u) << j; });
+  return m;
 }
 
 // Keys above the threshold in the low half, keys equal to it in the high half.
@@ -135,7 +149,6 @@ __device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32
   const uint4 q = reinterpret_cast<const uint4*>(s.hist0)[tid];
   uint32_t e0 = q.x, e1 = q.y, e2 = q.z, e3 = q.w;
   sort_desc<LOG>(e0, e1, e2, e3, s.hist0, tid);
-  PKV_STAMP(9);
   const uint32_t e[4] = {e0, e1, e2, e3};
   int32_t v[4];
 #pragma unroll
@@ -190,18 +203,23 @@ __device__ __forceinline__ unsigned long long block_exclusive_scan(Shared& s, un
   return before + inc - v;
 }
 
-// One suffix scan over the sum of the 4096-bin histograms of CTAs c0 .. c0 + nc - 1 of the cluster (each thread owns
-// four consecutive bins). Returns the total; when need_fn(total) > 0, s.bin is the highest bin with
-// (count above it) < need <= (count from it up) and s.need = need - (count above it). Two barriers; the caller reads
-// s.bin / s.need after the call.
+// One suffix scan over a 4096-bin histogram (each thread owns four consecutive bins): of this CTA alone (nc == 0,
+// plain shared-memory reads) or summed over CTAs 0 .. nc - 1 of the cluster (distributed shared memory). Returns the
+// total; when need_fn(total) > 0, s.bin is the highest bin with (count above it) < need <= (count from it up) and
+// s.need = need - (count above it). Two barriers; the caller reads s.bin / s.need after the call.
 template <class NeedFn>
-__device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int c0, int nc,
+__device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int nc,
                                                     NeedFn&& need_fn) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint32_t r[4] = {0, 0, 0, 0};
-  for (int c = c0; c < c0 + nc; ++c) {
-    const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&hist[4 * tid], c));
-    r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
+  if (nc == 0) {
+    const uint4 h = *reinterpret_cast<const uint4*>(&hist[4 * tid]);
+    r[0] = h.x, r[1] = h.y, r[2] = h.z, r[3] = h.w;
+  } else {
+    for (int c = 0; c < nc; ++c) {
+      const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&hist[4 * tid], c));
+      r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
+    }
   }
   const uint32_t local = r[0] + r[1] + r[2] + r[3];
   uint32_t sfx = local;  // inclusive suffix sum over threads (higher bins first)
@@ -242,7 +260,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   __shared__ Shared s;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  PKV_STAMP(0);
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rank = int(cluster.block_rank()), csize = int(cluster.num_blocks());
@@ -259,8 +276,8 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   const uint4* s_sg = reinterpret_cast<const uint4*>(s_gmax);
 
   // ---- 1: load, cache, the largest key of every group of 8, histogram of those maxima (top 12 bits) ----
-  for (int b = tid; b < kBins; b += kThreads) s.hist0[b] = 0, s.hist1[b] = 0;
-  if (tid < kBins2) s.hist2[tid] = 0;
+  for (int b = tid; b < kBins; b += kThreads) s.hist0[b] = 0, s.fine[b] = 0;
+  if (tid == 0) s.over = 0;
   if (tid < mis) s_keys[tid] = 0;                                   // key 0 is never valid, never selected
   if (tid < padded - (mis + cnt)) s_keys[mis + cnt + tid] = 0;
   if (tid < sgroups * 8 - groups) s_gmax[groups + tid] = 0;
@@ -293,19 +310,25 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
     }
   }
   __syncthreads();
-  PKV_STAMP(1);
 
   // This CTA's floor: with at least k valid groups here, at least k of this CTA's keys are >= the lower edge of the
-  // bin that holds its k-th largest group maximum, so the row's k-th largest key is too, and no key below the floor can
-  // be selected; with fewer valid groups every valid key of this CTA stays in the race. (Floors differ between the
-  // CTAs; the bins of hist1 from the row's threshold bin upwards are complete in every CTA, and only those decide.)
-  const uint32_t valid_groups =
-      reduce_and_pick(cluster, s, s.hist0, rank, 1, [&](uint32_t v) { return v >= uint32_t(k) ? uint32_t(k) : 0u; });
-  const uint32_t floor_key = valid_groups >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
-  PKV_STAMP(2);
-  // ---- 2: the groups that still hold a key in the race, as a list in index order (it takes the place of the group
-  // maxima: every thread reads the maxima of its two supergroups before anyone writes), then the exact histogram
-  // (top 12 bits) of their keys >= floor_key. Lanes work on listed groups only, so no lane idles on the other 7/8. ----
+  // bin that holds its k-th largest group maximum, so the row's k-th largest key is too; with fewer valid groups this
+  // CTA says nothing (floor = the smallest valid key). The row's floor is the largest of the CTAs' floors: no key
+  // below it can be selected.
+  {
+    const uint32_t valid_groups =
+        reduce_and_pick(cluster, s, s.hist0, 0, [&](uint32_t v) { return v >= uint32_t(k) ? uint32_t(k) : 0u; });
+    if (tid == 0) s.floor_pub = valid_groups >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
+    // hist0 now becomes the coarse histogram (16 keys per bin) of the keys above the exact window, see below
+    *reinterpret_cast<uint4*>(&s.hist0[4 * tid]) = make_uint4(0, 0, 0, 0);
+  }
+  cluster.sync();  // barrier A: the floors
+  uint32_t base = 0;
+  for (int c = 0; c < csize; ++c) base = max(base, *cluster.map_shared_rank(&s.floor_pub, c));
+
+  // ---- 2: the groups that hold a key >= base, as a list in index order (it takes the place of the group maxima:
+  // every thread reads the maxima of its two supergroups before anyone writes). Later passes go over the list only,
+  // so all lanes work. ----
   uint16_t* s_list = s_gmax;
   uint32_t listed = 0;
   {
@@ -313,35 +336,84 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int sg = 2 * tid + u;
-      if (sg < sgroups) for_each_key(s_sg[sg], [&](uint32_t gm, int j) { mask[u] |= (gm >= floor_key ? 1u : 0u) << j; });
+      if (sg < sgroups) for_each_key(s_sg[sg], [&](uint32_t gm, int j) { mask[u] |= (gm >= base ? 1u : 0u) << j; });
     }
-    PKV_STAMP(11);
     uint32_t pos = block_exclusive_scan(s, uint32_t(__popc(mask[0]) + __popc(mask[1])), listed);
-    PKV_STAMP(12);
 #pragma unroll
     for (int u = 0; u < 2; ++u)
       for (uint32_t m = mask[u]; m != 0; m &= m - 1) s_list[pos++] = uint16_t((2 * tid + u) * 8 + (__ffs(int(m)) - 1));
   }
   __syncthreads();
-  PKV_STAMP(13);
-  for (uint32_t e = tid; e < listed; e += kThreads)
-    for_each_key(s_groups[s_list[e]], [&](uint32_t key, int) {
-      if (key >= floor_key) atomicAdd(&s.hist1[key >> 4], 1u);
-    });
-  PKV_STAMP(3);
-  cluster.sync();  // barrier 1: every CTA's hist1 is complete
-  PKV_STAMP(4);
 
-  const uint32_t in_race = reduce_and_pick(cluster, s, s.hist1, 0, csize, [&](uint32_t v) { return min(uint32_t(k), v); });
-  const uint32_t want = min(uint32_t(k), in_race);  // the same in every CTA of the cluster
-  PKV_STAMP(14);
-  const uint32_t bin1 = want > 0 ? s.bin : 0xffffffffu, need1 = want > 0 ? s.need : 0u;
+  // ---- 3: exact counts of the keys in the window [base, base + window): one bin per key value, so equal scores are
+  // the only same-address atomics. Keys above the window are counted in `over` and, 16 to a bin, in the coarse
+  // histogram. The threshold lies in the window unless `over` alone reaches want; then the coarse histogram names
+  // the 16 keys around the threshold and a second round looks at those (two rounds at most). ----
+  uint32_t want = 0, thr = 0xffffffffu, need_ties = 0;
+  int vstar = -1;  // the threshold's bin in the window; -1: every key of the window is selected
+  uint32_t window = kBins;
+  for (int round = 0; round < 2; ++round) {
+    // A shared-memory atomic costs about the same with one active lane as with 32, so every lane first marks its
+    // keys that are in the race and the warp then pops one marked key per lane and step: two or three atomic
+    // instructions per 32 groups instead of eight.
+    uint32_t my_over = 0;
+    for (uint32_t eb = 0; eb < listed; eb += kThreads) {
+      const uint32_t e = eb + tid;
+      uint4 q = make_uint4(0, 0, 0, 0);
+      if (e < listed) q = s_groups[s_list[e]];
+      uint32_t m = mask_at_least(q, base);
+      while (__any_sync(0xffffffffu, m != 0)) {
+        if (m != 0) {
+          const uint32_t key = key_at(q, __ffs(int(m)) - 1);
+          m &= m - 1;
+          const uint32_t v = key - base;
+          if (v < window) {
+            atomicAdd(&s.fine[v], 1u);
+          } else {
+            ++my_over;
+            if (round == 0) atomicAdd(&s.hist0[key >> 4], 1u);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) my_over += __shfl_xor_sync(0xffffffffu, my_over, o);
+    if (lane == 0 && my_over != 0) atomicAdd(&s.over, my_over);
+    cluster.sync();  // barrier B: fine, over (and the coarse histogram) of every CTA are complete
+    uint32_t over_all = 0;
+    for (int c = 0; c < csize; ++c) over_all += *cluster.map_shared_rank(&s.over, c);
+    const uint32_t in_window = reduce_and_pick(cluster, s, s.fine, csize, [&](uint32_t v) {
+      const uint32_t w = round == 0 ? min(uint32_t(k), v + over_all) : want;
+      return w > over_all ? w - over_all : 0u;
+    });
+    if (round == 0) want = min(uint32_t(k), in_window + over_all);  // the same in every CTA of the cluster
+    if (want == 0) break;
+    if (want > over_all) {
+      if (round == 0 && in_window + over_all <= uint32_t(k)) {
+        thr = base - 1u;  // fewer keys in the race than k: all of them are selected, none is a tie
+      } else {
+        vstar = int(s.bin);
+        thr = base + s.bin;
+        need_ties = s.need;
+      }
+      break;
+    }
+    // The threshold is above the window (round 0 only: the second window holds it by construction).
+    reduce_and_pick(cluster, s, s.hist0, csize, [&](uint32_t) { return want; });
+    const uint32_t coarse_bin = s.bin;
+    cluster.sync();  // everyone has read this CTA's fine, over and coarse histogram
+    base = coarse_bin << 4;
+    window = 16;
+    *reinterpret_cast<uint4*>(&s.fine[4 * tid]) = make_uint4(0, 0, 0, 0);
+    if (tid == 0) s.over = 0;
+    __syncthreads();
+  }
   {
-    // This CTA's keys above the chosen bin (from its own histogram), published for the others.
+    // This CTA's selected keys above the threshold and its ties, published for the others.
     uint32_t mine = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
-      if (uint32_t(4 * tid + j) > bin1) mine += s.hist1[4 * tid + j];
+      if (4 * tid + j > vstar && uint32_t(4 * tid + j) < window) mine += s.fine[4 * tid + j];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
     if (lane == 0) s.wsum2[warp] = mine;
@@ -350,56 +422,20 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       uint32_t t = s.wsum2[lane];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-      if (lane == 0) s.above1 = t;
-    }
-  }
-  PKV_STAMP(15);
-  // ---- 3: histogram of the low 4 bits over this CTA's keys of the chosen bin ----
-  if (want > 0)
-    for (uint32_t e = tid; e < listed; e += kThreads)
-      for_each_key(s_groups[s_list[e]], [&](uint32_t key, int) {
-        if ((key >> 4) == bin1) atomicAdd(&s.hist2[key & 15u], 1u);
-      });
-  PKV_STAMP(5);
-  cluster.sync();  // barrier 2: hist2 and above1 of every CTA are complete
-  PKV_STAMP(6);
-
-  uint32_t thr = 0xffffffffu, need_ties = 0, base_above = 0, ties_before = 0, total_above = 0;
-  if (want > 0) {
-    // Every warp works this out on its own from the CTAs' hist2 (lane b < 16 holds bin b): no barrier.
-    uint32_t hc[kMaxCluster], h = 0;
-#pragma unroll
-    for (int c = 0; c < kMaxCluster; ++c) {
-      hc[c] = (c < csize && lane < kBins2) ? *cluster.map_shared_rank(&s.hist2[lane & (kBins2 - 1)], c) : 0u;
-      h += hc[c];
-    }
-    uint32_t sf = h;  // inclusive suffix over the bins (lanes 16..31 hold nothing)
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_down_sync(0xffffffffu, sf, o);
-      if (lane + o < 32) sf += t;
-    }
-    const uint32_t above = sf - h;
-    const int bin2 = __ffs(int(__ballot_sync(0xffffffffu, lane < kBins2 && above < need1 && sf >= need1))) - 1;
-    need_ties = need1 - __shfl_sync(0xffffffffu, above, bin2);
-    thr = (bin1 << 4) | uint32_t(bin2);
-#pragma unroll
-    for (int c = 0; c < kMaxCluster; ++c) {
-      if (c < csize) {
-        uint32_t a = lane > bin2 ? hc[c] : 0u;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        a += *cluster.map_shared_rank(&s.above1, c);
-        const uint32_t t = __shfl_sync(0xffffffffu, hc[c], bin2);
-        if (c < rank) {
-          base_above += a;
-          ties_before += t;
-        }
-        total_above += a;
+      if (lane == 0) {
+        s.pub_above = want > 0 ? t + s.over : 0u;
+        s.pub_ties = (want > 0 && vstar >= 0) ? s.fine[vstar] : 0u;
       }
     }
   }
-  PKV_STAMP(16);
+  cluster.sync();  // barrier C: every CTA's counts
+  uint32_t base_above = 0, ties_before = 0;
+  for (int c = 0; c < rank; ++c) {
+    base_above += *cluster.map_shared_rank(&s.pub_above, c);
+    ties_before += *cluster.map_shared_rank(&s.pub_ties, c);
+  }
+  const uint32_t total_above = want - need_ties;
+
   // ---- 4: place this CTA's selected keys, in index order, into CTA 0's candidate list ----
   int log_size = 7;
   while ((1 << log_size) < k) ++log_size;
@@ -418,36 +454,43 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       const uint32_t cs = count_selected(s_groups[s_list[e]], thr);
       c += (cs & 0xffffu) | (static_cast<unsigned long long>(cs >> 16) << 32);
     }
-    PKV_STAMP(17);
     const unsigned long long exc = block_exclusive_scan(s, c);
-    PKV_STAMP(18);
     uint32_t a = base_above + uint32_t(exc), t = ties_before + uint32_t(exc >> 32);
-    if (c != 0)
-      for (uint32_t e = e0; e < e1; ++e) {
-        const int g = s_list[e];
-        const uint4 q = s_groups[g];
-        if (count_selected(q, thr) == 0) continue;
+    // The same popping for the stores: a lane's selected keys leave in slot order, so index order is kept.
+    if (__any_sync(0xffffffffu, c != 0))
+      for (uint32_t i = 0; i < per; ++i) {
+        const uint32_t e = e0 + i;
+        uint4 q = make_uint4(0, 0, 0, 0);
+        int g = 0;
+        if (e < e1) {
+          g = s_list[e];
+          q = s_groups[g];
+        }
+        uint32_t m = mask_at_least(q, thr);
         const int i0 = lo + g * 8 - mis;
-        for_each_key(q, [&](uint32_t key, int j) {
-          if (key > thr) {
-            cand_key[a] = (key << 16) | (0xffffu - a);
-            cand_idx[a] = i0 + j;
-            ++a;
-          } else if (key == thr) {
-            if (t < need_ties) {
-              const uint32_t o = total_above + t;
-              cand_key[o] = (key << 16) | (0xffffu - o);
-              cand_idx[o] = i0 + j;
+        while (__any_sync(0xffffffffu, m != 0)) {
+          if (m != 0) {
+            const int j = __ffs(int(m)) - 1;
+            m &= m - 1;
+            const uint32_t key = key_at(q, j);
+            if (key > thr) {
+              cand_key[a] = (key << 16) | (0xffffu - a);
+              cand_idx[a] = i0 + j;
+              ++a;
+            } else {
+              if (t < need_ties) {
+                const uint32_t o = total_above + t;
+                cand_key[o] = (key << 16) | (0xffffu - o);
+                cand_idx[o] = i0 + j;
+              }
+              ++t;
             }
-            ++t;
           }
-        });
+        }
       }
   }
-  PKV_STAMP(7);
-  cluster.sync();  // barrier 3: the candidate list in CTA 0 is complete; no remote access after this point
+  cluster.sync();  // barrier D: the candidate list in CTA 0 is complete; no remote access after this point
   if (rank != 0) return;
-  PKV_STAMP(8);
 
   // ---- sort in CTA 0: 2^log_size words (128..2048), four per thread, descending ----
   int32_t* out = idx + size_t(row) * size_t(k);
@@ -458,7 +501,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
     case 10: sort_and_write<10>(s, tid, k, want, out); break;
     default: sort_and_write<11>(s, tid, k, want, out); break;
   }
-  PKV_STAMP(10);
 }
 
 

@@ -14,8 +14,9 @@
 // shared-memory atomics do not pile up on one address; passes two and three only count the few keys inside the chosen
 // bin. The selected keys are placed without atomics: every warp counts the keys above the threshold and the ties in
 // its contiguous range of indices, the counts give each warp its bases, ballots give the rank inside a group of 32,
-// so the threshold ties come out in index order (no serial scan of the row by one warp). The final sort of up to 1024 (key, ~index) pairs keeps two elements per thread in registers:
-// strides up to 32 are register or shuffle exchanges, only strides >= 64 go through shared memory.
+// so the threshold ties come out in index order (no serial scan of the row by one warp). The final sort of up to 1024
+// (key, ~index) pairs keeps two elements per thread in registers and its network is unrolled at compile time: strides
+// up to 32 are register or shuffle exchanges, only strides >= 64 go through shared memory.
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -100,6 +101,55 @@ template <int BINS>
 __device__ __forceinline__ void clear_hist(Shared& s) {
   for (int b = threadIdx.x; b < BINS; b += kThreads) s.hist[b] = 0;
   __syncthreads();
+}
+
+__device__ __forceinline__ unsigned long long keep(unsigned long long mine, unsigned long long other, bool take_max) {
+  return take_max == (mine > other) ? mine : other;
+}
+__device__ __forceinline__ unsigned long long shfl_xor64(unsigned long long v, int m) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, uint32_t(v), m);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), m);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+
+// Bitonic sort, descending, of 2^LOG (key, ~index) words held two per thread (words 2t, 2t + 1) by the first 2^LOG / 2
+// threads; the network is unrolled at compile time: stride 1 inside the thread, 2..32 by shuffles, larger ones through
+// s.sel with a named barrier over the sorting threads. Then the indices, -1 padded.
+template <int LOG>
+__device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32_t want, int32_t* __restrict__ out) {
+  constexpr int kSortThreads = (1 << LOG) / 2;
+  if (tid >= kSortThreads) return;
+  const int i0 = 2 * tid, i1 = i0 + 1;
+  unsigned long long a = uint32_t(i0) < want ? s.sel[i0] : 0ull, b = uint32_t(i1) < want ? s.sel[i1] : 0ull;
+  if (LOG > 6) asm volatile("bar.sync 1, %0;" ::"n"(kSortThreads) : "memory");  // s.sel is the exchange buffer below
+#pragma unroll
+  for (int L = 1; L <= LOG; ++L) {
+    const bool desc = (i0 & (1 << L)) == 0;
+#pragma unroll
+    for (int S = L - 1; S >= 0; --S) {
+      const int stride = 1 << S;
+      if (stride == 1) {
+        const unsigned long long hi = a > b ? a : b, lo = a > b ? b : a;
+        a = desc ? hi : lo;
+        b = desc ? lo : hi;
+      } else if (stride <= 32) {
+        const bool take_max = ((i0 & stride) == 0) == desc;
+        a = keep(a, shfl_xor64(a, stride >> 1), take_max);
+        b = keep(b, shfl_xor64(b, stride >> 1), take_max);
+      } else {
+        s.sel[i0] = a;
+        s.sel[i1] = b;
+        asm volatile("bar.sync 1, %0;" ::"n"(kSortThreads) : "memory");
+        const bool take_max = ((i0 & stride) == 0) == desc;
+        const unsigned long long oa = s.sel[i0 ^ stride], ob = s.sel[i1 ^ stride];
+        a = keep(a, oa, take_max);
+        b = keep(b, ob, take_max);
+        asm volatile("bar.sync 1, %0;" ::"n"(kSortThreads) : "memory");
+      }
+    }
+  }
+  if (i0 < k) out[i0] = uint32_t(i0) < want ? int32_t(0xffffffffu - uint32_t(a & 0xffffffffull)) : -1;
+  if (i1 < k) out[i1] = uint32_t(i1) < want ? int32_t(0xffffffffu - uint32_t(b & 0xffffffffull)) : -1;
 }
 
 __global__ void __launch_bounds__(kThreads) topk_f32_kernel(const float* __restrict__ scores, int n, long long ld, int k,
@@ -211,54 +261,16 @@ __global__ void __launch_bounds__(kThreads) topk_f32_kernel(const float* __restr
     }
   }
   __syncthreads();
-  // Sort size = power of two >= max(k, 64) (<= 1024), two elements per thread, descending; padding 0 sorts last.
-  int size = 64;
-  while (size < k) size <<= 1;
-  const int i0 = 2 * tid, i1 = i0 + 1;
-  const bool active = i0 < size;  // whole warps: size / 2 is a multiple of 32
-  unsigned long long a = uint32_t(i0) < want ? s.sel[i0 & (kMaxK - 1)] : 0ull;
-  unsigned long long b = uint32_t(i1) < want ? s.sel[i1 & (kMaxK - 1)] : 0ull;
-  __syncthreads();
-  const auto keep = [](unsigned long long mine, unsigned long long other, bool take_max) {
-    return take_max == (mine > other) ? mine : other;
-  };
-  const auto shfl64 = [](unsigned long long v, int m) {
-    const uint32_t lo = __shfl_xor_sync(0xffffffffu, uint32_t(v), m);
-    const uint32_t hi = __shfl_xor_sync(0xffffffffu, uint32_t(v >> 32), m);
-    return (static_cast<unsigned long long>(hi) << 32) | lo;
-  };
-  for (int len = 2; len <= size; len <<= 1) {
-    for (int stride = len >> 1; stride > 0; stride >>= 1) {
-      const bool desc = (i0 & len) == 0;
-      if (stride == 1) {
-        const unsigned long long hi = a > b ? a : b, lo = a > b ? b : a;
-        a = desc ? hi : lo;
-        b = desc ? lo : hi;
-      } else if (stride <= 32) {
-        if (active) {
-          const bool lower = (i0 & stride) == 0;
-          const unsigned long long oa = shfl64(a, stride >> 1), ob = shfl64(b, stride >> 1);
-          a = keep(a, oa, lower == desc);
-          b = keep(b, ob, lower == desc);
-        }
-      } else {
-        if (active) {
-          s.sel[i0] = a;
-          s.sel[i1] = b;
-        }
-        __syncthreads();
-        if (active) {
-          const bool lower = (i0 & stride) == 0;
-          const unsigned long long oa = s.sel[i0 ^ stride], ob = s.sel[i1 ^ stride];
-          a = keep(a, oa, lower == desc);
-          b = keep(b, ob, lower == desc);
-        }
-        __syncthreads();
-      }
-    }
+  // Sort 2^log_size >= max(k, 64) (<= 1024) words, two per thread, descending; padding 0 sorts last.
+  int log_size = 6;
+  while ((1 << log_size) < k) ++log_size;
+  switch (log_size) {
+    case 6: sort_and_write<6>(s, tid, k, want, out); break;
+    case 7: sort_and_write<7>(s, tid, k, want, out); break;
+    case 8: sort_and_write<8>(s, tid, k, want, out); break;
+    case 9: sort_and_write<9>(s, tid, k, want, out); break;
+    default: sort_and_write<10>(s, tid, k, want, out); break;
   }
-  if (i0 < k) out[i0] = uint32_t(i0) < want ? int32_t(0xffffffffu - uint32_t(a & 0xffffffffull)) : -1;
-  if (i1 < k) out[i1] = uint32_t(i1) < want ? int32_t(0xffffffffu - uint32_t(b & 0xffffffffull)) : -1;
 }
 
 }  // namespace pkv_topkf
