@@ -65,7 +65,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", type=int, default=int(os.environ.get("PKV_BENCH_GRAPH", "1")),
                     help="1 (default): the 43 layer calls of a step are captured once into a CUDA graph and replayed; 0: called directly")
-    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk"], default="decode43",
+    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk", "snapshot"], default="decode43",
                     help="decode43 is the benchmark line; the others measure the remaining operations of the path")
     return ap.parse_args()
 
@@ -1093,6 +1093,60 @@ def run_topk(args):
                      "bit_exact_check": {"ok": ok32}}})
 
 
+def run_snapshot(args):
+    """Slot-state snapshots (the part of a prefix hit that block tables do not cover): 43 layers x 5 per-slot segments
+    (a 128 x 512 bf16 window, two 8 x 1152 fp32 compressor rings, two 8 x 256 fp32 indexer rings: 215 segments, 9.3 MB
+    per slot), 64 slots, 16 saves then 16 restores per step (152 MB of snapshots: more than L2), each step ONE library
+    call and one launch per direction. Measured with the
+    snapshots in HBM and in pinned host memory (where the reference keeps them); checked byte for byte on the device."""
+    torch, capi, lib = _cuda_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(8)
+    slots, snaps, nops = NSEQ, 16, 16
+    per_layer = [128 * 512 * 2, 8 * 1152 * 4, 8 * 1152 * 4, 8 * 256 * 4, 8 * 256 * 4]
+    sizes = per_layer * LAYERS
+    bufs = [torch.randint(0, 256, (slots, b), generator=g, device=dev, dtype=torch.uint8) for b in sizes]
+    segs = (capi.PkvStateSeg * len(sizes))()
+    off = 0
+    for i, (t, b) in enumerate(zip(bufs, sizes)):
+        segs[i] = capi.PkvStateSeg(t.data_ptr(), b, off)
+        off += b
+    snap_bytes = (off + 4095) // 4096 * 4096
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    save = (capi.PkvStateOp * nops)(*[capi.PkvStateOp(1 + 4 * i, i) for i in range(nops)])          # slot -> snapshot i
+    restore = (capi.PkvStateOp * nops)(*[capi.PkvStateOp(2 + 4 * i, i) for i in range(nops)])       # snapshot i -> another slot
+    out = {}
+    for where in ("hbm", "pinned_host"):
+        snap = (torch.zeros(snaps * snap_bytes, dtype=torch.uint8, device=dev) if where == "hbm"
+                else torch.zeros(snaps * snap_bytes, dtype=torch.uint8).pin_memory())
+
+        def step():
+            capi.check(lib.pkv_state_copies(segs, len(sizes), save, nops, snap.data_ptr(), snap_bytes, snaps, slots, 1, sp))
+            capi.check(lib.pkv_state_copies(segs, len(sizes), restore, nops, snap.data_ptr(), snap_bytes, snaps, slots, 0, sp))
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        reps = max(args.steps, 5) if where == "hbm" else 3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        ok = all(bool(torch.equal(t[2 + 4 * i], t[1 + 4 * i])) for t in bufs[:10] + bufs[-5:] for i in range(nops))
+        nbytes = 2 * 2 * nops * off          # save and restore, each byte read once and written once
+        out[where] = {"GBps": round(nbytes / (ms * 1e-3) / 1e9, 1), "ms_per_step": round(ms, 3), "ok": ok}
+        del snap
+    _emit("snapshot", out["hbm"]["GBps"], out["hbm"]["ms_per_step"], {
+        "config": {"workload": f"{nops} saves + {nops} restores of {len(sizes)} segments, {off / 1e6:.1f} MB per slot, "
+                               "one launch per direction (pkv_state_copies)"},
+        "snapshots_in_hbm": out["hbm"], "snapshots_in_pinned_host": out["pinned_host"],
+        "bit_exact_check": {"ok": out["hbm"]["ok"] and out["pinned_host"]["ok"]}})
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -1105,6 +1159,8 @@ def main():
         run_sharded(args)
     elif args.workload == "topk":
         run_topk(args)
+    elif args.workload == "snapshot":
+        run_snapshot(args)
     else:
         run_ours(args)
 

@@ -207,6 +207,24 @@ PKV_API int pkv_topk_f32(const float* scores, int T, int n, long long ld, int k,
  * query's incomplete pool, then -1. The result is an index list in the format the gather takes. */
 PKV_API int pkv_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, pkv_stream_t stream);
 
+/* Slot-state snapshots — ResidentModel::state_copies, src/engine/resident.hip:545-557. pkv_state_seg is the
+ * reference's SnapSeg (src/engine/resident.hpp:180-183): a per-slot state buffer (slot s at dev + s * bytes) and its
+ * offset in a snapshot; pkv_state_op is StateOp (src/engine/step.hpp:32-34). For every op and every segment,
+ * save != 0 copies the slot's slice into snapshot op.snapshot (at snap_base + snapshot * snap_bytes + off), save == 0
+ * copies it back — the reference's loop of copy_kernel calls, here one launch per 256 segments x 32 ops. segs and ops
+ * are HOST arrays; snap_base is any memory the device can address: mapped pinned host memory as in the reference
+ * (resident.hip:538-541) or device memory. An op outside [0, num_snapshots) x [0, max_slots) fails with the
+ * reference's message "step: bad state op" before anything is launched. Ops of one call must not overlap each other. */
+typedef struct pkv_state_seg {
+  void* dev;
+  size_t bytes, off;
+} pkv_state_seg;
+typedef struct pkv_state_op {
+  int32_t slot, snapshot;
+} pkv_state_op;
+PKV_API int pkv_state_copies(const pkv_state_seg* segs, int nsegs, const pkv_state_op* ops, int nops, void* snap_base,
+                             size_t snap_bytes, int num_snapshots, int max_slots, int save, pkv_stream_t stream);
+
 /* pkv_topk_bf16 for callers that cannot hand the library any device memory of their own and cannot let it allocate
  * either — an engine thread that is recording its step into a CUDA graph (cudaMalloc is illegal while a stream is
  * capturing), a latency-critical decode loop (cudaMalloc/cudaFree synchronise the whole device), or a plugin host that

@@ -40,6 +40,7 @@ _SIGS = {
     "orc_topk_bf16": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_topk_f32": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_idx_expand": (None, [_vp, _vp, _vp, _i, _i, _i]),
+    "orc_state_copies": (None, [_vp, _vp, _vp, _i, _vp, _vp, _i, _vp, C.c_size_t, _i]),
     "orc_gather_rows_fp8": (None, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "orc_hardware_threads": (_i, []),
 }
@@ -156,6 +157,18 @@ def topk_f32(scores, n, k, threads=1):
     idx = np.empty((T, k), np.int32)
     lib().orc_topk_f32(_p(scores), T, n, ld, k, _p(idx), threads)
     return idx
+
+
+def state_copies(bufs, seg_off, ops, snap, snap_bytes, save):
+    """bufs: uint8 arrays [slots][bytes per slot] (modified in place when save is false); seg_off: each one's offset in
+    a snapshot; ops: (slot, snapshot) pairs; snap: uint8 [snapshots * snap_bytes] (modified in place when save)."""
+    n = len(bufs)
+    dev = np.array([b.ctypes.data for b in bufs], np.uint64)
+    nbytes = np.array([b.shape[1] for b in bufs], np.uint64)
+    off = np.array(seg_off, np.uint64)
+    slot = np.array([o[0] for o in ops], np.int32)
+    sn = np.array([o[1] for o in ops], np.int32)
+    lib().orc_state_copies(_p(dev), _p(nbytes), _p(off), n, _p(slot), _p(sn), len(ops), _p(snap), snap_bytes, int(save))
 
 
 def idx_expand(pools, pos, pool):

@@ -405,6 +405,19 @@ void orc_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int3
     }
 }
 
+// src/engine/resident.hip:545-557 (state_copies): for every op and segment one copy between the slot's slice
+// (dev + slot * bytes) and the snapshot (snap + snapshot * snap_bytes + off). Host memory on both sides here.
+void orc_state_copies(uint8_t* const* seg_dev, const size_t* seg_bytes, const size_t* seg_off, int nsegs, const int32_t* op_slot,
+                      const int32_t* op_snapshot, int nops, uint8_t* snap, size_t snap_bytes, int save) {
+  for (int o = 0; o < nops; ++o)
+    for (int i = 0; i < nsegs; ++i) {
+      uint8_t* slot = seg_dev[i] + size_t(op_slot[o]) * seg_bytes[i];
+      uint8_t* sn = snap + size_t(op_snapshot[o]) * snap_bytes + seg_off[i];
+      if (save) std::memcpy(sn, slot, seg_bytes[i]);
+      else std::memcpy(slot, sn, seg_bytes[i]);
+    }
+}
+
 int orc_hardware_threads() { return int(std::thread::hardware_concurrency()); }
 
 }  // extern "C"

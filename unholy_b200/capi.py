@@ -36,6 +36,14 @@ class PkvStep(C.Structure):
                  "Q", "k")] + [(n, C.c_void_p) for n in ("tables", "chunks", "q_chunk", "q_visible")]
 
 
+class PkvStateSeg(C.Structure):
+    _fields_ = [("dev", C.c_void_p), ("bytes", C.c_size_t), ("off", C.c_size_t)]
+
+
+class PkvStateOp(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("snapshot", C.c_int32)]
+
+
 class PkvTopkGroup(C.Structure):
     _fields_ = [("off", C.c_size_t), ("rows", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("idx_off", C.c_int32)]
 
@@ -68,6 +76,7 @@ _SIGS = {
     "pkv_topk_batch_scratch_words": (_sz, [C.POINTER(PkvTopkGroup), _i]),
     "pkv_topk_bf16_batch": (_i, [_vp, C.POINTER(PkvTopkGroup), _i, _vp, _vp, _sz, _vp]),
     "pkv_topk_f32": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp]),
+    "pkv_state_copies": (_i, [C.POINTER(PkvStateSeg), _i, C.POINTER(PkvStateOp), _i, _vp, _sz, _i, _i, _i, _vp]),
     "pkv_idx_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_copy_pages": (_i, [C.POINTER(PkvPoolDesc), _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_device_alloc": (_i, [C.POINTER(_vp), _sz]),

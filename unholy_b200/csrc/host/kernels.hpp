@@ -123,6 +123,14 @@ inline void glm_topk(const float* scores, int ld, int n, int cols, int k, int32_
 inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
   pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
 }
+// ResidentModel::state_copies (src/engine/resident.hip:545-557): SnapSeg and StateOp keep their field names.
+using SnapSeg = pkv_state_seg;
+using StateOp = pkv_state_op;
+inline void state_copies(const SnapSeg* segs, int nsegs, const StateOp* ops, int nops, void* snap_base, size_t snap_bytes,
+                         int num_snapshots, int max_slots, bool save, cudaStream_t st) {
+  pkv_throw(pkv_state_copies(segs, nsegs, ops, nops, snap_base, snap_bytes, num_snapshots, max_slots, save ? 1 : 0,
+                             reinterpret_cast<pkv_stream_t>(st)), "state_copies");
+}
 inline int glm_sel_count(int p, int k, int pool) {
   const int full = (p + 1) / pool;
   return (full < k ? full : k) * pool + (p + 1) % pool;
