@@ -182,8 +182,9 @@ PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, in
 
 /* topk_bf16_batch — src/kernels/indexer.hpp:76-94 (TopkRows / TopkBatch), src/kernels/indexer.hip:878-902: several
  * score blocks in one call (the decode chunks of a step): group g's rows [rows][n] start at scores + off (elements),
- * its index lists [rows][k] at idx + idx_off (elements); per row the same result as pkv_topk_bf16. The groups run one
- * after the other on the stream and share `scratch` (at least pkv_topk_batch_scratch_words words). */
+ * its index lists [rows][k] at idx + idx_off (elements); per row the same result as pkv_topk_bf16. All groups run in
+ * one launch of thread-block clusters (32 groups per launch) when every group has k <= 2048 and n <= 655,360; else one
+ * after the other on the stream, sharing `scratch` (at least pkv_topk_batch_scratch_words words). */
 typedef struct pkv_topk_group {
   size_t off;
   int32_t rows, n, k, idx_off;

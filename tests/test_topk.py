@@ -55,7 +55,8 @@ def test_oracle_topk_matches_contract(kind):
 @pytest.mark.parametrize("kind", ["normal", "ties", "masked", "special"])
 @pytest.mark.parametrize("T,n,ld,k", [(37, 5000, 5000, 512), (64, 131072, 131072, 2048), (3, 8192, 8200, 2048),
                                       (4, 8193, 8193, 100), (2, 300, 304, 2048), (1, 1, 8, 1), (5, 40000, 40000, 2051),
-                                      (6, 1000, 1003, 64), (2, 524288, 524288, 2048), (1, 524289, 524289, 300), (1, 800000, 800000, 300), (16, 40000, 40000, 1000),
+                                      (6, 1000, 1003, 64), (2, 524288, 524288, 2048), (1, 524289, 524289, 300),
+                                      (1, 800000, 800000, 300), (16, 40000, 40000, 1000),
                                       (3, 7, 9, 2), (2, 65, 65, 129), (2, 655360, 655360, 2048)])
 def test_topk_bf16_gpu(pkv, cuda, kind, T, n, ld, k):
     """Both paths of pkv_topk_bf16 (knob 7: 0 = one launch of thread-block clusters where the shape allows it — k <= 2048,
@@ -154,29 +155,41 @@ def test_idx_expand_gpu(pkv, cuda, n, k, pool):
 
 
 @pytest.mark.gpu
-def test_topk_batch_groups(pkv, cuda):
+@pytest.mark.parametrize("many", [False, True])
+def test_topk_batch_groups(pkv, cuda, many):
     """Several score blocks with their own row counts, key counts and k in one call (the decode chunks of a step):
-    each group's lists equal the oracle's for that block."""
+    each group's lists equal the oracle's for that block. Knob 7 = 0 runs all groups in one launch of thread-block
+    clusters (32 groups per launch: `many` has 40, one of them empty), 1 runs them one after the other through the
+    scratch."""
     g = tl.rng(75)
     shapes = [(3, 9000, 512), (1, 300, 512), (5, 20000, 2048), (2, 64, 16)]
-    blocks = [scores_case(g, T, n, n, kind) for (T, n, k), kind in zip(shapes, ("normal", "masked", "ties", "special"))]
+    if many:
+        shapes = shapes + [(0, 100, 8)] + [(1 + i % 3, 500 + 37 * i, 64 + i) for i in range(35)]
+    kinds = ("normal", "masked", "ties", "special")
+    blocks = [scores_case(g, max(T, 1), n, n, kinds[i % 4]) for i, (T, n, k) in enumerate(shapes)]
     flat = np.concatenate([b.reshape(-1) for b in blocks])
     groups = (capi.PkvTopkGroup * len(shapes))()
     off = idx_off = 0
     for i, (T, n, k) in enumerate(shapes):
         groups[i].off, groups[i].rows, groups[i].n, groups[i].k, groups[i].idx_off = off, T, n, k, idx_off
-        off += T * n
+        off += max(T, 1) * n
         idx_off += T * k
     words = pkv.pkv_topk_batch_scratch_words(groups, len(shapes))
     assert words == max(pkv.pkv_topk_scratch_words(T, n, k) for T, n, k in shapes)
     d_s = tl.dev(cuda, flat)
     d_scratch = cuda.full((words * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
-    d_idx = cuda.full((idx_off * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
-    capi.check(pkv.pkv_topk_bf16_batch(d_s.data_ptr(), groups, len(shapes), d_idx.data_ptr(), d_scratch.data_ptr(), words,
-                                       tl.stream_ptr(cuda)))
-    cuda.cuda.synchronize()
-    got = tl.host(d_idx, np.int32)
-    o = 0
-    for (T, n, k), b in zip(shapes, blocks):
-        assert np.array_equal(got[o:o + T * k].reshape(T, k), orc.topk_bf16(b, n, k)), (T, n, k)
-        o += T * k
+    try:
+        for path in (0, 1):
+            capi.check(pkv.pkv_tune(7, path))
+            d_idx = cuda.full((idx_off * 4,), 0x5A, dtype=cuda.uint8, device="cuda")
+            capi.check(pkv.pkv_topk_bf16_batch(d_s.data_ptr(), groups, len(shapes), d_idx.data_ptr(), d_scratch.data_ptr(),
+                                               words, tl.stream_ptr(cuda)))
+            cuda.cuda.synchronize()
+            got = tl.host(d_idx, np.int32)
+            o = 0
+            for (T, n, k), b in zip(shapes, blocks):
+                assert np.array_equal(got[o:o + T * k].reshape(T, k), orc.topk_bf16(b[:T], n, k)), (path, T, n, k)
+                o += T * k
+    finally:
+        capi.check(pkv.pkv_tune(7, 0))
+    assert tl.device_status(pkv) == 0

@@ -21,6 +21,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/unholy_pkv.h"
 
@@ -444,10 +445,14 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
   return PKV_OK;
 }
 
-// pkv_topk_cluster.cu: the whole selection in one launch of 8-CTA clusters, for the shapes it takes.
+// pkv_topk_cluster.cu: the whole selection in one launch of thread-block clusters, for the shapes it takes.
+struct pkv_topk_cluster_group {
+  long long off, ld, idx_off;
+  int rows, n, k, row0;
+};
 bool pkv_topk_cluster_eligible(int T, int n, int k);
-int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, cudaStream_t stream,
-                            bool* usable, std::string& err);
+int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group* groups, int ngroups, int32_t* idx,
+                            cudaStream_t stream, bool* usable, std::string& err);
 extern int pkv_g_topk_path;
 
 // One cluster launch when the shape and the device allow it, else the four launches through `scratch`.
@@ -455,7 +460,8 @@ int pkv_topk_dispatch(const uint16_t* scores, int T, int n, long long ld, int k,
                       cudaStream_t stream, std::string& err) {
   if (pkv_g_topk_path != 1 && pkv_topk_cluster_eligible(T, n, k)) {
     bool usable = false;
-    if (const int rc = pkv_topk_cluster_launch(scores, T, n, ld, k, idx, stream, &usable, err)) return rc;
+    const pkv_topk_cluster_group g{0, ld, 0, T, n, k, 0};
+    if (const int rc = pkv_topk_cluster_launch(scores, &g, 1, idx, stream, &usable, err)) return rc;
     if (usable) return PKV_OK;
   }
   return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, stream, err);
@@ -507,14 +513,37 @@ int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, in
     pkv_g_err = "pkv_topk_bf16_batch: scratch must be 8-byte aligned and hold pkv_topk_batch_scratch_words() words";
     return PKV_ERR_ARG;
   }
-  // The groups run one after the other on the stream, so they can share the scratch.
+  for (int g = 0; g < ngroups; ++g)
+    if (groups[g].rows > 0)
+      if (const int rc = pkv_topk_check(scores + groups[g].off, groups[g].rows, groups[g].n, groups[g].n, groups[g].k,
+                                        idx + groups[g].idx_off, pkv_g_err))
+        return rc;
+  // All groups in one launch of thread-block clusters (32 groups per launch) when every group's shape allows it.
+  if (pkv_g_topk_path != 1 && ngroups > 0) {
+    std::vector<pkv_topk_cluster_group> cg;
+    long long rows = 0;
+    bool ok = true;
+    for (int g = 0; g < ngroups && ok; ++g) {
+      const pkv_topk_group& q = groups[g];
+      if (q.rows <= 0) continue;
+      ok = pkv_topk_cluster_eligible(q.rows, q.n, q.k);
+      cg.push_back({(long long)q.off, q.n, q.idx_off, q.rows, q.n, q.k, 0});
+      rows += q.rows;
+    }
+    if (ok && rows > 0 && rows <= 65535) {
+      bool usable = false;
+      if (const int rc = pkv_topk_cluster_launch(scores, cg.data(), int(cg.size()), idx, reinterpret_cast<cudaStream_t>(stream),
+                                                 &usable, pkv_g_err))
+        return rc;
+      if (usable) return PKV_OK;
+    }
+  }
+  // Otherwise the groups run one after the other on the stream, so they can share the scratch.
   for (int g = 0; g < ngroups; ++g) {
     const pkv_topk_group& q = groups[g];
     if (q.rows <= 0) continue;
-    const uint16_t* sc = scores + q.off;
-    int32_t* out = idx + q.idx_off;
-    if (const int rc = pkv_topk_check(sc, q.rows, q.n, q.n, q.k, out, pkv_g_err)) return rc;
-    if (const int rc = pkv_topk_dispatch(sc, q.rows, q.n, q.n, q.k, out, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
+    if (const int rc = pkv_topk_dispatch(scores + q.off, q.rows, q.n, q.n, q.k, idx + q.idx_off, scratch,
+                                         reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
       return rc;
   }
   return PKV_OK;

@@ -31,6 +31,7 @@
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <string>
@@ -39,9 +40,16 @@
 
 namespace cg = cooperative_groups;
 
+// One block of rows of a launch (shared with pkv_topk.cu, which fills these in).
+struct pkv_topk_cluster_group {
+  long long off, ld, idx_off;
+  int rows, n, k, row0;
+};
+
 namespace pkv_topkc {
 
 constexpr int kMaxCluster = 8;
+constexpr int kMaxGroups = 32;
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxK = 2048;
@@ -64,6 +72,13 @@ struct __align__(16) Shared {
   uint32_t over;           // this CTA's keys above the window
   uint32_t pub_above, pub_ties;  // this CTA's selected keys above the threshold, and its ties: read after barrier C
   uint32_t bin, need;
+};
+
+// The rows of one launch: up to kMaxGroups blocks of `rows` rows of n scores (row r of a block at scores + off + r * ld,
+// its k indices at idx + idx_off + r * k); row0 = the block's first row in the launch.
+struct Batch {
+  int ngroups, slice_max;
+  pkv_topk_cluster_group g[kMaxGroups];
 };
 
 template <class F>
@@ -254,17 +269,22 @@ __device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, 
   return total;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores, int n, long long ld,
-                                                                   int k, int32_t* __restrict__ idx, int slice) {
-  extern __shared__ __align__(16) uint16_t s_keys[];  // keys [slice + 16], then group maxima [(slice + 16) / 8 + 8]
+__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores,
+                                                                   int32_t* __restrict__ idx,
+                                                                   const __grid_constant__ Batch B) {
+  extern __shared__ __align__(16) uint16_t s_keys[];  // keys [slice_max + 16], then group maxima [(slice_max + 16) / 8 + 8]
   __shared__ Shared s;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rank = int(cluster.block_rank()), csize = int(cluster.num_blocks());
-  const int row = blockIdx.y;
-  const uint16_t* rp = scores + size_t(row) * size_t(ld);
+  // blockIdx.y is a row of the launch; the groups' rows follow one another (row0 ascending)
+  int gi = 0;
+  while (gi + 1 < B.ngroups && B.g[gi + 1].row0 <= int(blockIdx.y)) ++gi;
+  const int n = B.g[gi].n, k = B.g[gi].k, row = int(blockIdx.y) - B.g[gi].row0;
+  const uint16_t* rp = scores + B.g[gi].off + (long long)row * B.g[gi].ld;
+  const int slice = ((n + csize - 1) / csize + 7) & ~7;
   const int lo = min(n, rank * slice), cnt = min(n, lo + slice) - lo;
   // Position p of the cache holds element lo + p - mis, so 16-byte groups of the row are 16-byte groups of the cache.
   const int mis = int((reinterpret_cast<uintptr_t>(rp) >> 1) & 7u);
@@ -272,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   const int groups = padded >> 3;            // groups of 8 keys
   const int sgroups = (groups + 7) >> 3;     // groups of 8 group maxima = 64 keys
   const uint4* s_groups = reinterpret_cast<const uint4*>(s_keys);
-  uint16_t* s_gmax = s_keys + slice + 16;
+  uint16_t* s_gmax = s_keys + B.slice_max + 16;
   const uint4* s_sg = reinterpret_cast<const uint4*>(s_gmax);
 
   // ---- 1: load, cache, the largest key of every group of 8, histogram of those maxima (top 12 bits) ----
@@ -493,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   if (rank != 0) return;
 
   // ---- sort in CTA 0: 2^log_size words (128..2048), four per thread, descending ----
-  int32_t* out = idx + size_t(row) * size_t(k);
+  int32_t* out = idx + B.g[gi].idx_off + (long long)row * k;
   switch (log_size) {
     case 7: sort_and_write<7>(s, tid, k, want, out); break;
     case 8: sort_and_write<8>(s, tid, k, want, out); break;
@@ -519,18 +539,19 @@ static size_t smem_bytes(int slice) { return size_t(slice + 16) * 2 + size_t((sl
 
 // CTAs per row: the fewest whose slices fit in shared memory, then doubled while the launch stays within about one
 // CTA per SM and a slice keeps at least 4096 keys.
-static int cluster_size_for(int T, int n, int sms) {
+static int cluster_size_for(int rows, int n_max, int sms) {
   using namespace pkv_topkc;
   int c = 1;
-  while (c < kMaxCluster && (n + c - 1) / c > kMaxSlice) c *= 2;
-  while (c < kMaxCluster && (long long)T * c * 2 <= sms + sms / 8 && n / (c * 2) >= 4096) c *= 2;
+  while (c < kMaxCluster && (n_max + c - 1) / c > kMaxSlice) c *= 2;
+  while (c < kMaxCluster && (long long)rows * c * 2 <= sms + sms / 8 && n_max / (c * 2) >= 4096) c *= 2;
   return c;
 }
 
-// Launches the cluster kernel; returns PKV_OK, or PKV_ERR_CUDA with `err` set. `usable` (per device, found on the first
-// call) is false when the device cannot co-schedule the largest cluster: the caller then takes the four-launch path.
-int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, cudaStream_t stream,
-                            bool* usable, std::string& err) {
+// Launches the cluster kernel for up to 32 blocks of rows per launch (more blocks: more launches); returns PKV_OK, or
+// PKV_ERR_CUDA with `err` set. `usable` (per device, found on the first call) is false when the device cannot
+// co-schedule the largest cluster: the caller then takes the four-launch path. Every block must be eligible.
+int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group* groups, int ngroups, int32_t* idx,
+                            cudaStream_t stream, bool* usable, std::string& err) {
   using namespace pkv_topkc;
   constexpr int kMaxDevices = 64;
   static thread_local signed char state[kMaxDevices];  // 0 unknown, 1 usable, -1 not
@@ -570,16 +591,30 @@ int pkv_topk_cluster_launch(const uint16_t* scores, int T, int n, long long ld, 
   }
   *usable = state[dev] == 1;
   if (!*usable) return PKV_OK;
-  const int csize = cluster_size_for(T, n, sm_count[dev]);
-  const int slice = ((n + csize - 1) / csize + 7) & ~7;
-  attr[0].val.clusterDim.x = unsigned(csize);
-  c.gridDim = dim3(unsigned(csize), unsigned(T));
-  c.dynamicSmemBytes = smem_bytes(slice);
-  c.numAttrs = 2;
-  e = cudaLaunchKernelEx(&c, topk_cluster_kernel, scores, n, ld, k, idx, slice);
-  if (e != cudaSuccess) {
-    err = std::string("top-k cluster launch: ") + cudaGetErrorString(e);
-    return PKV_ERR_CUDA;
+  for (int g0 = 0; g0 < ngroups; g0 += kMaxGroups) {
+    Batch B;
+    B.ngroups = 0;
+    int rows = 0, n_max = 1;
+    for (int g = g0; g < ngroups && g < g0 + kMaxGroups; ++g) {
+      if (groups[g].rows <= 0) continue;
+      B.g[B.ngroups] = groups[g];
+      B.g[B.ngroups].row0 = rows;
+      rows += groups[g].rows;
+      n_max = std::max(n_max, groups[g].n);
+      ++B.ngroups;
+    }
+    if (rows == 0) continue;
+    const int csize = cluster_size_for(rows, n_max, sm_count[dev]);
+    B.slice_max = ((n_max + csize - 1) / csize + 7) & ~7;
+    attr[0].val.clusterDim.x = unsigned(csize);
+    c.gridDim = dim3(unsigned(csize), unsigned(rows));
+    c.dynamicSmemBytes = smem_bytes(B.slice_max);
+    c.numAttrs = 2;
+    e = cudaLaunchKernelEx(&c, topk_cluster_kernel, scores, idx, B);
+    if (e != cudaSuccess) {
+      err = std::string("top-k cluster launch: ") + cudaGetErrorString(e);
+      return PKV_ERR_CUDA;
+    }
   }
   return PKV_OK;
 }
