@@ -65,7 +65,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", type=int, default=int(os.environ.get("PKV_BENCH_GRAPH", "1")),
                     help="1 (default): the 43 layer calls of a step are captured once into a CUDA graph and replayed; 0: called directly")
-    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk", "snapshot"], default="decode43",
+    ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk", "snapshot", "gather_fp8"], default="decode43",
                     help="decode43 is the benchmark line; the others measure the remaining operations of the path")
     return ap.parse_args()
 
@@ -1147,6 +1147,62 @@ def run_snapshot(args):
         "bit_exact_check": {"ok": out["hbm"]["ok"] and out["pinned_host"]["ok"]}})
 
 
+def run_gather_fp8(args):
+    """Gather with dequantisation over fp8 latent rows (GLM-style pools: e4m3 [rows][512] + e8m0 [rows][8], 256 rows per
+    page): 64 query rows of one sequence, 2048 entries each, out bf16 [64][2048][512]. Per entry 520 B read and 1024 B
+    written; pool 1M rows (0.5 GB of codes), far larger than L2. Checked on the device against torch's own decode of the
+    same codes (e4m3 -> float, times 2^scale, to bf16: exact)."""
+    torch, capi, lib = _cuda_setup()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    width, block, rpp, T, k = 512, 64, 256, NSEQ, K_SEL
+    rows = (1 << 16) if args.small else (1 << 20)
+    pages = rows // rpp
+    codes = torch.randint(0, 256, (rows, width), generator=g, device=dev, dtype=torch.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x38                    # no NaN patterns: the check compares values
+    scales = torch.randint(120, 134, (rows, width // block), generator=g, device=dev, dtype=torch.uint8)
+    table = torch.randperm(pages, generator=g, device=dev).to(torch.int32)
+    idx = torch.randint(0, rows, (T, k), generator=g, device=dev, dtype=torch.int32)
+    idx[:, -5:] = -1
+    vis = torch.full((T,), rows, dtype=torch.int32, device=dev)
+    vis[0] = rows // 2
+    out = torch.empty(T, k, width, dtype=torch.bfloat16, device=dev)
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        capi.check(lib.pkv_gather_rows_fp8(codes.data_ptr(), scales.data_ptr(), table.data_ptr(), rpp, width, block,
+                                           idx.data_ptr(), vis.data_ptr(), T, k, out.data_ptr(), sp))
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    reps = max(args.steps, 10)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / reps * 1e3
+    # check 4 query rows: physical row = table[r // rpp] * rpp + r % rpp
+    ok = True
+    for t in (0, 1, T // 2, T - 1):
+        r = idx[t].long()
+        masked = (r < 0) | (r >= vis[t])
+        rc = r.clamp(min=0)
+        phys = table[rc // rpp].long() * rpp + rc % rpp
+        val = codes[phys].view(torch.float8_e4m3fn).float().view(k, width // block, block)
+        val = val * torch.exp2(scales[phys].float() - 127.0).unsqueeze(-1)
+        want = val.view(k, width).to(torch.bfloat16)
+        want[masked] = 0
+        ok = ok and bool(torch.equal(out[t].view(torch.int16), want.view(torch.int16)))
+    nbytes = T * k * (width + width // block + width * 2)
+    _emit("gather_fp8", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
+        "config": {"workload": f"{T} x {k} entries of fp8 rows (512 e4m3 + 8 e8m0) -> bf16, pool of {rows} rows (pkv_gather_rows_fp8)"},
+        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok}})
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -1161,6 +1217,8 @@ def main():
         run_topk(args)
     elif args.workload == "snapshot":
         run_snapshot(args)
+    elif args.workload == "gather_fp8":
+        run_gather_fp8(args)
     else:
         run_ours(args)
 

@@ -514,6 +514,42 @@ def test_gather_rows_fp8_dequant(pkv, cuda, width, block, rpp, k):
     assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
 
 
+def test_gather_rows_fp8_every_code_and_scale(pkv, cuda):
+    """Every e4m3 bit pattern (zeros, subnormals, both NaN codes) under scales from 2^-127 to 2^127 and the NaN scale:
+    results in bf16's subnormal range, overflow to infinity and NaN all equal the oracle's scalar arithmetic (scale
+    byte 0 decodes to +0 and 255 to +inf, as the reference's e8m0_to_f32 does: src/kernels/dev.hip.hpp:96)."""
+    g = tl.rng(29)
+    width, block, rpp, pages, T, k = 512, 64, 256, 4, 2, 700
+    n = pages * rpp
+    table = shuffled_table(g, pages)
+    codes = g.integers(0, 256, size=(n, width), dtype=np.uint8)
+    codes[:256, :] = np.arange(256, dtype=np.uint8)[:, None]          # rows of one code each
+    codes[256:300, :] &= 0x7E                                           # rows without any NaN code (the paired decode)
+    scales = g.choice(np.array([0, 1, 5, 100, 119, 120, 126, 127, 128, 140, 200, 246, 247, 254, 255], np.uint8),
+                      size=(n, width // block))
+    vis = np.array([n, n], np.int32)
+    idx = np.stack([g.permutation(n)[:k], g.permutation(n)[:k]]).astype(np.int32)
+    idx[0, :300] = np.arange(300)                                      # logical rows; the table scatters them
+    phys_codes, phys_scales = np.zeros_like(codes), np.zeros_like(scales)
+    for r in range(n):                                                 # logical row r lives at table[r // rpp] * rpp + r % rpp
+        p = int(table[r // rpp]) * rpp + r % rpp
+        phys_codes[p], phys_scales[p] = codes[r], scales[r]
+    want = orc.gather_rows_fp8(phys_codes, phys_scales, table, rpp, block, idx, vis)
+    d_c, d_s, d_t, d_idx, d_vis = (tl.dev(cuda, a) for a in (phys_codes, phys_scales, table, idx, vis))
+    d_out = cuda.full((want.size * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    capi.check(pkv.pkv_gather_rows_fp8(d_c.data_ptr(), d_s.data_ptr(), d_t.data_ptr(), rpp, width, block, d_idx.data_ptr(),
+                                       d_vis.data_ptr(), T, k, d_out.data_ptr(), tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    got = tl.host(d_out, np.uint16, want.shape)
+    def is_nan(a):
+        return ((a & 0x7F80) == 0x7F80) & ((a & 0x7F) != 0)
+    # NaN results (a NaN code, or 0 x inf under the scale byte 255) must be NaN; their payload is the processor's
+    bad = np.argwhere((got != want) & ~(is_nan(got) & is_nan(want)))
+    examples = [(int(codes[idx[t, e], c]), int(scales[idx[t, e], c // block]), hex(int(got[t, e, c])), hex(int(want[t, e, c])))
+                for t, e, c in bad[:12]]
+    assert len(bad) == 0, f"{len(bad)} values differ; (code, scale, got, want): {examples}"
+
+
 def test_copy_between_device_and_pinned_host(pkv, cuda):
     """The snapshot save / restore primitive: the reference's state_copies moves slot state between device memory and
     pinned host staging with copy_kernel, i.e. with ordinary loads and stores issued by SMs

@@ -16,6 +16,8 @@
 //   * quantisation keeps 8 values per thread and reduces the block maximum with warp shuffles;
 //   * block-table entries are bounds-checked; a bad entry is skipped and recorded in a status word, never dereferenced;
 //     the only device-side wait (an mbarrier) is bounded and records when it gives up.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -811,8 +813,46 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
 }
 
 // Gather with dequantisation for fp8 rows (the gather loop of src/kernels/glm_fast.hip:190-227): entry -> physical
-// row -> e4m3 codes [width] and one e8m0 scale per `block` values -> bf16 = code * 2^scale (exact). One thread per 16
-// codes: a 16-byte load, sixteen decodes, two 16-byte stores. Masked entries give zero rows.
+// row -> e4m3 codes [width] and one e8m0 scale per `block` values -> bf16 = code * 2^scale (exact). One unit = 16
+// codes: a 16-byte load, sixteen decodes, two 16-byte stores; a thread has four units in flight. Masked entries give
+// zero rows.
+//
+// Decoding two codes at a time on the conversion hardware: an e4m3 byte b read as the fp16 pattern
+// (b & 0x80) << 8 | (b & 0x7f) << 7 is the same number divided by 256, subnormals and zeros included (fp16 has the
+// e4m3 exponent field with bias 15 instead of 7); fp16 -> fp32 is exact, the product with 2^(scale - 127 + 8) is exact
+// (a power of two, no underflow past fp32's subnormals), and fp32 -> bf16 rounds to nearest even as the scalar
+// f32_to_bf16_bits does. The two NaN codes, scale byte 0 (the factor is +0 in the reference's decode, not 2^-127) and
+// scale bytes above 246 (no finite fp32 factor) take the scalar path.
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t q, bool high, float factor) {
+  const uint32_t w = __byte_perm(q, 0u, high ? 0x4342u : 0x4140u);  // bytes (b0, b1) or (b2, b3), one per 16-bit lane
+  const uint32_t h = ((w & 0x00800080u) << 8) | ((w & 0x007f007fu) << 7);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+  const __nv_bfloat162 o = __floats2bfloat162_rn(f.x * factor, f.y * factor);
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+__device__ __forceinline__ void dequant_unit(const uint4& q, uint32_t scale_bits, uint32_t* w16) {
+  const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
+  const uint32_t low7 = 0x7f7f7f7fu;
+  const bool any_nan = __vcmpeq4(q.x & low7, low7) | __vcmpeq4(q.y & low7, low7) | __vcmpeq4(q.z & low7, low7) |
+                       __vcmpeq4(q.w & low7, low7);
+  if (!any_nan && scale_bits - 1u <= 245u) {
+    const float factor = __uint_as_float((scale_bits + 8u) << 23);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w16[2 * i] = dequant_pair(qs[i], false, factor);
+      w16[2 * i + 1] = dequant_pair(qs[i], true, factor);
+    }
+  } else {
+    const float sc = pkv::e8m0_bits_to_f32(scale_bits);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w16[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t code = (qs[i >> 2] >> (8 * (i & 3))) & 0xffu;
+      w16[i >> 1] |= pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(code) * sc) << (16 * (i & 1));
+    }
+  }
+}
 __global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                                                          OneTable tb, int width, int block, const int32_t* __restrict__ idx,
                                                          const int32_t* __restrict__ q_visible, int T, int k,
@@ -834,23 +874,34 @@ __global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restri
     __syncthreads();
     const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
     uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
-    for (int u = threadIdx.x; u < total; u += blockDim.x) {
-      const int r = u / upr, c = u - r * upr;
-      const long long rid = s_rid[r];
-      uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (rid >= 0) {
-        const uint4 q = ld_stream(reinterpret_cast<const uint4*>(codes + size_t(rid) * width) + c);
-        const float sc = pkv::e8m0_bits_to_f32(__ldg(&scales[size_t(rid) * nb + (c * 16) / block]));
-        const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
+    for (int base = 0; base < total; base += 4 * 256) {
+      uint4 q[4];
+      uint32_t sb[4];
+      bool live[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t code = (qs[i >> 2] >> (8 * (i & 3))) & 0xffu;
-          const uint32_t b = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(code) * sc);
-          w16[i >> 1] |= b << (16 * (i & 1));
+      for (int j = 0; j < 4; ++j) {
+        const int u = base + j * 256 + int(threadIdx.x);
+        live[j] = false;
+        if (u < total) {
+          const int r = u / upr, c = u - r * upr;
+          const long long rid = s_rid[r];
+          if (rid >= 0) {
+            live[j] = true;
+            q[j] = ld_stream(reinterpret_cast<const uint4*>(codes + size_t(rid) * width) + c);
+            sb[j] = __ldg(&scales[size_t(rid) * nb + (c * 16) / block]);
+          }
         }
       }
-      st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
-      st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int u = base + j * 256 + int(threadIdx.x);
+        if (u < total) {
+          uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (live[j]) dequant_unit(q[j], sb[j], w16);
+          st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
+          st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
+        }
+      }
     }
     __syncthreads();
   }
