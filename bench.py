@@ -1197,10 +1197,52 @@ def run_gather_fp8(args):
         want = val.view(k, width).to(torch.bfloat16)
         want[masked] = 0
         ok = ok and bool(torch.equal(out[t].view(torch.int16), want.view(torch.int16)))
+    # The same entries as ONE call for 64 sequences with their own block tables (the decode shape): pkv_step_gather_fp8
+    per_seq = rows // T
+    pps = per_seq // rpp
+    tables = table.view(T, pps).contiguous()
+    chunks = torch.tensor([[q, per_seq - 1, 1, q] for q in range(T)], dtype=torch.int32, device=dev)
+    q_chunk = torch.arange(T, dtype=torch.int32, device=dev)
+    vis_b = torch.full((T,), per_seq, dtype=torch.int32, device=dev)
+    idx_b = torch.randint(0, per_seq, (T, k), generator=g, device=dev, dtype=torch.int32)
+    idx_b[:, -5:] = -1
+    step = capi.PkvStep()
+    step.width, step.row_stride, step.rows_per_page, step.max_pages_per_seq, step.num_pages = width, width, rpp, pps, pages
+    step.fp8_block, step.nchunks, step.T, step.Q, step.k = block, T, T, T, k
+    step.tables, step.chunks, step.q_chunk, step.q_visible = (tables.data_ptr(), chunks.data_ptr(), q_chunk.data_ptr(),
+                                                              vis_b.data_ptr())
+    out_b = torch.empty_like(out)
+
+    def call_b():
+        capi.check(lib.pkv_step_gather_fp8(C.byref(step), codes.data_ptr(), scales.data_ptr(), width, block,
+                                           idx_b.data_ptr(), out_b.data_ptr(), sp))
+
+    for _ in range(3):
+        call_b()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        call_b()
+    e1.record()
+    torch.cuda.synchronize()
+    us_b = e0.elapsed_time(e1) / reps * 1e3
+    ok_b = True
+    for t in (0, T // 3, T - 1):
+        r = idx_b[t].long()
+        masked = r < 0
+        rc = r.clamp(min=0)
+        phys = tables[t][rc // rpp].long() * rpp + rc % rpp
+        val = codes[phys].view(torch.float8_e4m3fn).float().view(k, width // block, block)
+        val = val * torch.exp2(scales[phys].float() - 127.0).unsqueeze(-1)
+        want = val.view(k, width).to(torch.bfloat16)
+        want[masked] = 0
+        ok_b = ok_b and bool(torch.equal(out_b[t].view(torch.int16), want.view(torch.int16)))
     nbytes = T * k * (width + width // block + width * 2)
     _emit("gather_fp8", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
         "config": {"workload": f"{T} x {k} entries of fp8 rows (512 e4m3 + 8 e8m0) -> bf16, pool of {rows} rows (pkv_gather_rows_fp8)"},
-        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok}})
+        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok and ok_b},
+        "step_call_64_sequences": {"what": "pkv_step_gather_fp8: 64 sequences x 2048 entries, own block tables, one launch",
+                                   "us_per_call": round(us_b, 2), "GBps": round(nbytes / (us_b * 1e-6) / 1e9, 1), "ok": ok_b}})
 
 
 def main():

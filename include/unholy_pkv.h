@@ -165,6 +165,14 @@ enum {
  * src/kernels/attn_wmma.hip:84). Rows of other chunks appended in the same launch must not be gathered. */
 PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags, pkv_stream_t stream);
 
+/* The fp8 gather with dequantisation (pkv_gather_rows_fp8) for every sequence of a step in one launch: query row t of
+ * the step gathers idx[t][0..k) from the sequence of its chunk (step->q_chunk, chunks, tables, q_visible, Q, k,
+ * rows_per_page, max_pages_per_seq, num_pages as in pkv_step_run; width and row_stride of the step are not used) out of
+ * the fp8 pool codes [rows][width] / scales [rows][width / block] into out bf16 [Q][k][width]. Replaces one
+ * mla_attn launch per chunk's gather loop (src/kernels/glm_fast.hip:190-227, src/model/glm5_fast.hip:276-299). */
+PKV_API int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
+                                const int32_t* idx, uint16_t* out, pkv_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Index-list producer (the step before the gather).
  * ---------------------------------------------------------------------------------------------------------------- */

@@ -550,6 +550,33 @@ def test_gather_rows_fp8_every_code_and_scale(pkv, cuda):
     assert len(bad) == 0, f"{len(bad)} values differ; (code, scale, got, want): {examples}"
 
 
+def test_step_gather_fp8_all_sequences_in_one_launch(pkv, cuda):
+    """pkv_step_gather_fp8: every sequence of a step gathers from its own block table in one launch; per query row the
+    result equals the single-sequence oracle gather with that sequence's table (GLM geometry: 256 rows per page, 512
+    codes + 8 scales per row, 2051 entries)."""
+    g = tl.rng(31)
+    width, block, rpp, k = 512, 64, 256, 2051
+    case = tl.PagedCase(seed=31, nseq=6, len_lo=300, len_hi=5000, num_pages=160, k=k, width=width, rows_per_page=rpp,
+                        with_keys=False, fill=False)
+    nrows = case.num_pages * rpp
+    codes = g.integers(0, 256, size=(nrows, width), dtype=np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3A
+    scales = g.integers(118, 136, size=(nrows, width // block), dtype=np.uint8)
+    idx = case.idx.copy()
+    idx[2, 5] = int(case.q_visible[2]) + 3                     # past the visible rows: a zero row
+    want = np.stack([orc.gather_rows_fp8(codes, scales, case.tables[s], rpp, block, idx[s:s + 1], case.q_visible[s:s + 1])[0]
+                     for s in range(case.nseq)])
+    d = {n: tl.dev(cuda, a) for n, a in dict(codes=codes, scales=scales, tables=case.tables, chunks=case.chunks,
+                                              q_chunk=case.q_chunk, q_vis=case.q_visible, idx=idx).items()}
+    d_out = cuda.full((want.size * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    step = tl.make_step(case, d["tables"], d["chunks"], d["q_chunk"], d["q_vis"])
+    capi.check(pkv.pkv_step_gather_fp8(C.byref(step), d["codes"].data_ptr(), d["scales"].data_ptr(), width, block,
+                                       d["idx"].data_ptr(), d_out.data_ptr(), tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert tl.device_status(pkv) == 0
+    assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
+
+
 def test_copy_between_device_and_pinned_host(pkv, cuda):
     """The snapshot save / restore primitive: the reference's state_copies moves slot state between device memory and
     pinned host staging with copy_kernel, i.e. with ordinary loads and stores issued by SMs

@@ -853,8 +853,23 @@ __device__ __forceinline__ void dequant_unit(const uint4& q, uint32_t scale_bits
     }
   }
 }
+// Where logical row `row` of query row t lives: one sequence's table (the reference-shaped call) ...
+struct OneSeqRows {
+  OneTable tb;
+  __device__ __forceinline__ int begin(int) const { return 0; }
+  __device__ __forceinline__ long long rid(int, int, int row) const { return (long long)one_row(tb, row); }
+};
+// ... or the step's chunk list and block tables (every sequence of a step in one launch; bounds are checked).
+struct StepRows {
+  pkv_step s;
+  // the query row's slot: loaded before (not after) its index entry, so the two chains overlap
+  __device__ __forceinline__ int begin(int t) const { return s.chunks[__ldg(&s.q_chunk[t])].slot; }
+  __device__ __forceinline__ long long rid(int slot, int t, int row) const { return physical_row(s, slot, row, t); }
+};
+template <class ROWS>
 __global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
-                                                         OneTable tb, int width, int block, const int32_t* __restrict__ idx,
+                                                         const __grid_constant__ ROWS rows, int width, int block,
+                                                         const int32_t* __restrict__ idx,
                                                          const int32_t* __restrict__ q_visible, int T, int k,
                                                          uint16_t* __restrict__ out) {
   __shared__ long long s_rid[kGatherRows];
@@ -866,8 +881,9 @@ __global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restri
       const int e = e0 + int(threadIdx.x);
       long long rid = -1;
       if (e < k) {
+        const int slot = rows.begin(t), vis = __ldg(&q_visible[t]);
         const int row = __ldg(&idx[size_t(t) * k + e]);
-        if (row >= 0 && row < __ldg(&q_visible[t])) rid = (long long)one_row(tb, row);
+        if (row >= 0 && row < vis) rid = rows.rid(slot, t, row);
       }
       s_rid[threadIdx.x] = rid;
     }
@@ -1299,7 +1315,28 @@ int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 8)));
-  gather_fp8_kernel<<<grid, 256, 0, stream>>>(codes, scales, OneTable{table, rows_per_page}, width, block, idx, q_visible, T, k, out);
+  gather_fp8_kernel<OneSeqRows><<<grid, 256, 0, stream>>>(codes, scales, OneSeqRows{OneTable{table, rows_per_page}}, width, block,
+                                                          idx, q_visible, T, k, out);
+  PKV_LAUNCH_CHECK("gather_fp8_kernel");
+  return PKV_OK;
+}
+
+int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
+                        const int32_t* idx, uint16_t* out, pkv_stream_t stream) {
+  if (!step) return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: null step");
+  const pkv_step& s = *step;
+  if (s.Q <= 0 || s.k <= 0) return PKV_OK;
+  if (!codes || !scales || !idx || !out || !s.tables || !s.chunks || !s.q_chunk || !s.q_visible)
+    return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: null pointer");
+  if (const int rc = check_quant_shape(s.Q, width, block, "pkv_step_gather_fp8")) return rc;
+  if (width <= 0 || width % 16 != 0 || block % 16 != 0 || s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks <= 0)
+    return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: width must be a positive multiple of 16, the step needs pages and chunks");
+  if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: codes and out must be 16-byte aligned");
+  const long long tiles = (long long)s.Q * ((s.k + kGatherRows - 1) / kGatherRows);
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 8)));
+  gather_fp8_kernel<StepRows><<<grid, 256, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q, s.k, out);
   PKV_LAUNCH_CHECK("gather_fp8_kernel");
   return PKV_OK;
 }
