@@ -866,60 +866,71 @@ struct StepRows {
   __device__ __forceinline__ int begin(int t) const { return s.chunks[__ldg(&s.q_chunk[t])].slot; }
   __device__ __forceinline__ long long rid(int slot, int t, int row) const { return physical_row(s, slot, row, t); }
 };
+// 8 warps move data, a ninth resolves the NEXT tile's entries (index -> block table -> physical row) meanwhile, so the
+// three dependent loads of a resolution are off the data warps' path: one barrier per tile.
+constexpr int kFp8Threads = 256 + 32, kFp8CtasPerSm = 5;
 template <class ROWS>
-__global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
-                                                         const __grid_constant__ ROWS rows, int width, int block,
-                                                         const int32_t* __restrict__ idx,
-                                                         const int32_t* __restrict__ q_visible, int T, int k,
-                                                         uint16_t* __restrict__ out) {
-  __shared__ long long s_rid[kGatherRows];
+__global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(const uint8_t* __restrict__ codes,
+                                                                 const uint8_t* __restrict__ scales,
+                                                                 const __grid_constant__ ROWS rows, int width, int block,
+                                                                 const int32_t* __restrict__ idx,
+                                                                 const int32_t* __restrict__ q_visible, int T, int k,
+                                                                 uint16_t* __restrict__ out) {
+  __shared__ long long s_rid[2][kGatherRows];
   const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows, upr = width >> 4, nb = width / block;
   const long long total_tiles = (long long)T * tiles_per_q;
-  for (long long w = blockIdx.x; w < total_tiles; w += gridDim.x) {
-    const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
-    if (threadIdx.x < kGatherRows) {
-      const int e = e0 + int(threadIdx.x);
-      long long rid = -1;
-      if (e < k) {
-        const int slot = rows.begin(t), vis = __ldg(&q_visible[t]);
-        const int row = __ldg(&idx[size_t(t) * k + e]);
-        if (row >= 0 && row < vis) rid = rows.rid(slot, t, row);
-      }
-      s_rid[threadIdx.x] = rid;
+  const bool resolver = threadIdx.x >= 256;
+  const auto resolve = [&](long long w, int buf) {
+    const int t = int(w / tiles_per_q), e = int(w - (long long)t * tiles_per_q) * kGatherRows + int(threadIdx.x) - 256;
+    long long rid = -1;
+    if (e < k) {
+      const int slot = rows.begin(t), vis = __ldg(&q_visible[t]);
+      const int row = __ldg(&idx[size_t(t) * k + e]);
+      if (row >= 0 && row < vis) rid = rows.rid(slot, t, row);
     }
-    __syncthreads();
-    const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
-    uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
-    for (int base = 0; base < total; base += 4 * 256) {
-      uint4 q[4];
-      uint32_t sb[4];
-      bool live[4];
+    s_rid[buf][threadIdx.x - 256] = rid;
+  };
+  if (resolver && blockIdx.x < total_tiles) resolve(blockIdx.x, 0);
+  __syncthreads();
+  int buf = 0;
+  for (long long w = blockIdx.x; w < total_tiles; w += gridDim.x, buf ^= 1) {
+    if (resolver) {
+      if (w + gridDim.x < total_tiles) resolve(w + gridDim.x, buf ^ 1);
+    } else {
+      const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
+      const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
+      uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
+      for (int base = 0; base < total; base += 4 * 256) {
+        uint4 q[4];
+        uint32_t sb[4];
+        bool live[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int u = base + j * 256 + int(threadIdx.x);
-        live[j] = false;
-        if (u < total) {
-          const int r = u / upr, c = u - r * upr;
-          const long long rid = s_rid[r];
-          if (rid >= 0) {
-            live[j] = true;
-            q[j] = ld_stream(reinterpret_cast<const uint4*>(codes + size_t(rid) * width) + c);
-            sb[j] = __ldg(&scales[size_t(rid) * nb + (c * 16) / block]);
+        for (int j = 0; j < 4; ++j) {
+          const int u = base + j * 256 + int(threadIdx.x);
+          live[j] = false;
+          if (u < total) {
+            const int r = u / upr, c = u - r * upr;
+            const long long rid = s_rid[buf][r];
+            if (rid >= 0) {
+              live[j] = true;
+              q[j] = ld_stream(reinterpret_cast<const uint4*>(codes + size_t(rid) * width) + c);
+              sb[j] = __ldg(&scales[size_t(rid) * nb + (c * 16) / block]);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int u = base + j * 256 + int(threadIdx.x);
+          if (u < total) {
+            uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (live[j]) dequant_unit(q[j], sb[j], w16);
+            st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
+            st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
           }
         }
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int u = base + j * 256 + int(threadIdx.x);
-        if (u < total) {
-          uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          if (live[j]) dequant_unit(q[j], sb[j], w16);
-          st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
-          st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
-        }
-      }
     }
-    __syncthreads();
+    __syncthreads();  // the next tile's rows are resolved, this tile's are no longer read
   }
 }
 
@@ -1314,8 +1325,8 @@ int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32
   const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 8)));
-  gather_fp8_kernel<OneSeqRows><<<grid, 256, 0, stream>>>(codes, scales, OneSeqRows{OneTable{table, rows_per_page}}, width, block,
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
+  gather_fp8_kernel<OneSeqRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, OneSeqRows{OneTable{table, rows_per_page}}, width, block,
                                                           idx, q_visible, T, k, out);
   PKV_LAUNCH_CHECK("gather_fp8_kernel");
   return PKV_OK;
@@ -1335,8 +1346,8 @@ int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_
   const long long tiles = (long long)s.Q * ((s.k + kGatherRows - 1) / kGatherRows);
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * 8)));
-  gather_fp8_kernel<StepRows><<<grid, 256, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q, s.k, out);
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
+  gather_fp8_kernel<StepRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q, s.k, out);
   PKV_LAUNCH_CHECK("gather_fp8_kernel");
   return PKV_OK;
 }
