@@ -67,6 +67,7 @@ def parse_args():
                     help="1 (default): the 43 layer calls of a step are captured once into a CUDA graph and replayed; 0: called directly")
     ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk", "snapshot", "gather_fp8"], default="decode43",
                     help="decode43 is the benchmark line; the others measure the remaining operations of the path")
+    ap.add_argument("--topk-shape", default="", help="rows,keys,k for --workload topk (default: the decode shape 64,131072,2048)")
     return ap.parse_args()
 
 
@@ -1031,6 +1032,8 @@ def run_topk(args):
     g = torch.Generator(device=dev)
     g.manual_seed(6)
     T, n, k = NSEQ, (8192 if args.small else CONTEXT), K_SEL
+    if args.topk_shape:
+        T, n, k = (int(v) for v in args.topk_shape.split(","))
     scores = torch.randn(T, n, generator=g, device=dev).to(torch.bfloat16)
     scores[0, n // 2:] = float("-inf")                      # a row whose later keys are invisible
     words = lib.pkv_topk_scratch_words(T, n, k)
@@ -1086,7 +1089,7 @@ def run_topk(args):
     nbytes32 = T * n32 * 4 + T * k32 * 4
     nbytes = T * n * 2 + T * k * 4
     _emit("topk", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
-        "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16: one launch of thread-block clusters, 2 CTAs per row here; the four-launch path uses {words * 4} B of caller scratch)"},
+        "config": {"workload": f"top-{k} of {n} bf16 scores x {T} rows (pkv_topk_bf16: one launch of thread-block clusters; the four-launch path uses {words * 4} B of caller scratch)"},
         "us_per_call": round(us, 2), "us_per_call_four_launches": round(us_by_path[1], 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok},
         "f32_twin": {"workload": f"top-{k32} of {n32} fp32 scores x {T} rows (pkv_topk_f32, no scratch)",
                      "us_per_call": round(us32, 2), "GBps": round(nbytes32 / (us32 * 1e-6) / 1e9, 1),

@@ -57,10 +57,13 @@ def test_oracle_topk_matches_contract(kind):
                                       (4, 8193, 8193, 100), (2, 300, 304, 2048), (1, 1, 8, 1), (5, 40000, 40000, 2051),
                                       (6, 1000, 1003, 64), (2, 524288, 524288, 2048), (1, 524289, 524289, 300),
                                       (1, 800000, 800000, 300), (16, 40000, 40000, 1000),
-                                      (3, 7, 9, 2), (2, 65, 65, 129), (2, 655360, 655360, 2048)])
+                                      (3, 7, 9, 2), (2, 65, 65, 129), (2, 655360, 655360, 2048),
+                                      (300, 5000, 5003, 512), (200, 20000, 20000, 2048), (180, 40000, 40000, 1000),
+                                      (400, 16384, 16384, 1024), (170, 32768, 32768, 1025)])
 def test_topk_bf16_gpu(pkv, cuda, kind, T, n, ld, k):
     """Both paths of pkv_topk_bf16 (knob 7: 0 = one launch of thread-block clusters where the shape allows it — k <= 2048,
-    n <= 655,360 —, 1 = the four launches through the scratch) against the oracle."""
+    n <= 655,360; CTAs of 1024 threads when the launch fits the SMs, of 512 or 256 threads when there are more rows —,
+    1 = the four launches through the scratch) against the oracle."""
     g = tl.rng(71)
     s = scores_case(g, T, n, ld, kind)
     want = orc.topk_bf16(s, n, k, threads=8)

@@ -50,9 +50,10 @@ namespace pkv_topkc {
 
 constexpr int kMaxCluster = 8;
 constexpr int kMaxGroups = 32;
-constexpr int kThreads = 1024;
-constexpr int kWarps = kThreads / 32;
+constexpr int kMaxThreads = 1024;         // CTAs of 256, 512 or 1024 threads (chosen by the host)
+constexpr int kMaxWarps = kMaxThreads / 32;
 constexpr int kMaxK = 2048;
+constexpr int k256Slice = 16384, k512Slice = 32768;  // the longest slices the smaller CTAs take (64 keys per thread)
 constexpr int kMaxSlice = 81920;          // keys per CTA kept in shared memory (160 KB, and 20 KB of group maxima)
 constexpr int kBins = 4096;               // top 12 bits: four bins per thread
 constexpr uint32_t kNegInfKey = 0x007Fu;  // key of the bf16 pattern 0xFF80; valid keys are above it (their top 12 bits >= 8)
@@ -64,10 +65,10 @@ __device__ __forceinline__ uint32_t key_one(uint32_t b) { return (b & 0x8000u) ?
 struct __align__(16) Shared {
   uint32_t hist0[kBins];   // group maxima by their top 12 bits; then the keys above the window, 16 to a bin; after
                            // barrier C, in CTA 0, the candidates' sort words
-  uint32_t fine[kBins];    // exact counts of the keys base + v of the window
-  int32_t cand_idx[kMaxK];
-  unsigned long long wsum64[kWarps];
-  uint32_t wsum[kWarps], wsum2[kWarps];
+  uint32_t fine[kBins];    // exact counts of the keys base + v of the window; after barrier C, in CTA 0, the
+                           // candidates' indices (cand_idx below)
+  unsigned long long wsum64[kMaxWarps];
+  uint32_t wsum[kMaxWarps], wsum2[kMaxWarps];
   uint32_t floor_pub;      // this CTA's floor: read by the others after barrier A
   uint32_t over;           // this CTA's keys above the window
   uint32_t pub_above, pub_ties;  // this CTA's selected keys above the threshold, and its ties: read after barrier C
@@ -167,7 +168,7 @@ __device__ __forceinline__ void sort_and_write(Shared& s, int tid, int k, uint32
   const uint32_t e[4] = {e0, e1, e2, e3};
   int32_t v[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = uint32_t(4 * tid + j) < want ? s.cand_idx[0xffffu - (e[j] & 0xffffu)] : -1;
+  for (int j = 0; j < 4; ++j) v[j] = uint32_t(4 * tid + j) < want ? reinterpret_cast<const int32_t*>(s.fine)[0xffffu - (e[j] & 0xffffu)] : -1;
   if (4 * tid + 3 < k && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
     reinterpret_cast<int4*>(out)[tid] = make_int4(v[0], v[1], v[2], v[3]);
   } else {
@@ -188,7 +189,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(Shared& s, uint32_t v, 
   }
   if (lane == 31) s.wsum[warp] = inc;
   __syncthreads();
-  const uint32_t w = s.wsum[lane];
+  const uint32_t w = lane < int(blockDim.x >> 5) ? s.wsum[lane] : 0u;
   uint32_t before = lane < warp ? w : 0u, all = w;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -218,25 +219,29 @@ __device__ __forceinline__ unsigned long long block_exclusive_scan(Shared& s, un
   return before + inc - v;
 }
 
-// One suffix scan over a 4096-bin histogram (each thread owns four consecutive bins): of this CTA alone (nc == 0,
+// One suffix scan over a 4096-bin histogram (each thread owns 4096 / THREADS consecutive bins): of this CTA alone (nc == 0,
 // plain shared-memory reads) or summed over CTAs 0 .. nc - 1 of the cluster (distributed shared memory). Returns the
 // total; when need_fn(total) > 0, s.bin is the highest bin with (count above it) < need <= (count from it up) and
 // s.need = need - (count above it). Two barriers; the caller reads s.bin / s.need after the call.
-template <class NeedFn>
+template <int THREADS, class NeedFn>
 __device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, Shared& s, uint32_t* hist, int nc,
                                                     NeedFn&& need_fn) {
+  constexpr int PER = kBins / THREADS, WARPS = THREADS / 32;  // this thread's bins: PER consecutive ones
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint32_t r[4] = {0, 0, 0, 0};
-  if (nc == 0) {
-    const uint4 h = *reinterpret_cast<const uint4*>(&hist[4 * tid]);
-    r[0] = h.x, r[1] = h.y, r[2] = h.z, r[3] = h.w;
-  } else {
-    for (int c = 0; c < nc; ++c) {
-      const uint4 h = *reinterpret_cast<const uint4*>(cluster.map_shared_rank(&hist[4 * tid], c));
-      r[0] += h.x, r[1] += h.y, r[2] += h.z, r[3] += h.w;
+  uint32_t r[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) r[j] = 0;
+  for (int c = 0; c < (nc == 0 ? 1 : nc); ++c) {
+    const uint32_t* h = nc == 0 ? hist : cluster.map_shared_rank(hist, c);
+#pragma unroll
+    for (int j = 0; j < PER; j += 4) {
+      const uint4 v = *reinterpret_cast<const uint4*>(&h[PER * tid + j]);
+      r[j] += v.x, r[j + 1] += v.y, r[j + 2] += v.z, r[j + 3] += v.w;
     }
   }
-  const uint32_t local = r[0] + r[1] + r[2] + r[3];
+  uint32_t local = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) local += r[j];
   uint32_t sfx = local;  // inclusive suffix sum over threads (higher bins first)
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -245,7 +250,7 @@ __device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, 
   }
   if (lane == 0) s.wsum[warp] = sfx;
   __syncthreads();
-  const uint32_t w = s.wsum[lane];
+  const uint32_t w = lane < WARPS ? s.wsum[lane] : 0u;
   uint32_t higher = lane > warp ? w : 0u, total = w;  // the totals of the warps above this one, and of all warps
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -257,9 +262,9 @@ __device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, 
   if (need > 0) {
     uint32_t above = sfx - local;
 #pragma unroll
-    for (int j = 3; j >= 0; --j) {
+    for (int j = PER - 1; j >= 0; --j) {
       if (above < need && above + r[j] >= need) {
-        s.bin = uint32_t(4 * tid + j);
+        s.bin = uint32_t(PER * tid + j);
         s.need = need - above;
       }
       above += r[j];
@@ -269,9 +274,11 @@ __device__ __forceinline__ uint32_t reduce_and_pick(cg::cluster_group& cluster, 
   return total;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_t* __restrict__ scores,
-                                                                   int32_t* __restrict__ idx,
-                                                                   const __grid_constant__ Batch B) {
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, kMaxThreads / THREADS) topk_cluster_kernel(const uint16_t* __restrict__ scores,
+                                                                                      int32_t* __restrict__ idx,
+                                                                                      const __grid_constant__ Batch B) {
+  constexpr int kThreads = THREADS, PER = kBins / THREADS;  // PER consecutive histogram bins per thread
   extern __shared__ __align__(16) uint16_t s_keys[];  // keys [slice_max + 16], then group maxima [(slice_max + 16) / 8 + 8]
   __shared__ Shared s;
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -337,10 +344,11 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
   // below it can be selected.
   {
     const uint32_t valid_groups =
-        reduce_and_pick(cluster, s, s.hist0, 0, [&](uint32_t v) { return v >= uint32_t(k) ? uint32_t(k) : 0u; });
+        reduce_and_pick<THREADS>(cluster, s, s.hist0, 0, [&](uint32_t v) { return v >= uint32_t(k) ? uint32_t(k) : 0u; });
     if (tid == 0) s.floor_pub = valid_groups >= uint32_t(k) ? (s.bin << 4) : (kNegInfKey + 1u);
     // hist0 now becomes the coarse histogram (16 keys per bin) of the keys above the exact window, see below
-    *reinterpret_cast<uint4*>(&s.hist0[4 * tid]) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < PER; j += 4) *reinterpret_cast<uint4*>(&s.hist0[PER * tid + j]) = make_uint4(0, 0, 0, 0);
   }
   cluster.sync();  // barrier A: the floors
   uint32_t base = 0;
@@ -402,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
     cluster.sync();  // barrier B: fine, over (and the coarse histogram) of every CTA are complete
     uint32_t over_all = 0;
     for (int c = 0; c < csize; ++c) over_all += *cluster.map_shared_rank(&s.over, c);
-    const uint32_t in_window = reduce_and_pick(cluster, s, s.fine, csize, [&](uint32_t v) {
+    const uint32_t in_window = reduce_and_pick<THREADS>(cluster, s, s.fine, csize, [&](uint32_t v) {
       const uint32_t w = round == 0 ? min(uint32_t(k), v + over_all) : want;
       return w > over_all ? w - over_all : 0u;
     });
@@ -418,13 +426,14 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
       }
       break;
     }
-    // The threshold is above the window (round 0 only: the second window holds it by construction).
-    reduce_and_pick(cluster, s, s.hist0, csize, [&](uint32_t) { return want; });
+    // The threshold is above the window (first window only: the second window holds it by construction).
+    reduce_and_pick<THREADS>(cluster, s, s.hist0, csize, [&](uint32_t) { return want; });
     const uint32_t coarse_bin = s.bin;
     cluster.sync();  // everyone has read this CTA's fine, over and coarse histogram
     base = coarse_bin << 4;
     window = 16;
-    *reinterpret_cast<uint4*>(&s.fine[4 * tid]) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < PER; j += 4) *reinterpret_cast<uint4*>(&s.fine[PER * tid + j]) = make_uint4(0, 0, 0, 0);
     if (tid == 0) s.over = 0;
     __syncthreads();
   }
@@ -432,14 +441,14 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
     // This CTA's selected keys above the threshold and its ties, published for the others.
     uint32_t mine = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (4 * tid + j > vstar && uint32_t(4 * tid + j) < window) mine += s.fine[4 * tid + j];
+    for (int j = 0; j < PER; ++j)
+      if (PER * tid + j > vstar && uint32_t(PER * tid + j) < window) mine += s.fine[PER * tid + j];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
     if (lane == 0) s.wsum2[warp] = mine;
     __syncthreads();
     if (warp == 0) {
-      uint32_t t = s.wsum2[lane];
+      uint32_t t = lane < THREADS / 32 ? s.wsum2[lane] : 0u;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
       if (lane == 0) {
@@ -463,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const uint16_
     for (int i = int(want) + tid; i < (1 << log_size); i += kThreads) s.hist0[i] = 0;  // padding sorts last
   if (want > 0) {
     uint32_t* cand_key = cluster.map_shared_rank(s.hist0, 0);
-    int32_t* cand_idx = cluster.map_shared_rank(s.cand_idx, 0);
+    int32_t* cand_idx = reinterpret_cast<int32_t*>(cluster.map_shared_rank(s.fine, 0));
     // The listed groups are in index order and every thread takes a contiguous run of them: one exclusive scan over
     // the threads' counts (keys above the threshold in the low word, ties in the high word) gives every thread the
     // places of its keys.
@@ -571,19 +580,23 @@ int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t c;
   std::memset(&c, 0, sizeof(c));
-  c.blockDim = dim3(kThreads);
+  c.blockDim = dim3(kMaxThreads);
   c.stream = stream;
   c.attrs = attr;
   if (state[dev] == 0) {
     const size_t max_smem = smem_bytes(kMaxSlice);
-    e = cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(max_smem));
+    e = cudaFuncSetAttribute(topk_cluster_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(max_smem));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(topk_cluster_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes(k512Slice)));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(topk_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes(k256Slice)));
     int clusters = 0, sms = 0;
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e == cudaSuccess) {
       c.gridDim = dim3(kMaxCluster, 1);
       c.dynamicSmemBytes = max_smem;
       c.numAttrs = 1;
-      e = cudaOccupancyMaxActiveClusters(&clusters, topk_cluster_kernel, &c);
+      e = cudaOccupancyMaxActiveClusters(&clusters, topk_cluster_kernel<1024>, &c);
     }
     if (e != cudaSuccess) cudaGetLastError();  // not sticky: clear it
     state[dev] = (e == cudaSuccess && clusters > 0 && sms > 0) ? 1 : -1;
@@ -610,7 +623,21 @@ int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group
     c.gridDim = dim3(unsigned(csize), unsigned(rows));
     c.dynamicSmemBytes = smem_bytes(B.slice_max);
     c.numAttrs = 2;
-    e = cudaLaunchKernelEx(&c, topk_cluster_kernel, scores, idx, B);
+    // One CTA of 1024 threads per SM when the launch fits the SMs anyway (a decode batch at long context); with more
+    // rows than that, smaller CTAs so that two or four rows share an SM and fill each other's barrier and latency gaps.
+    int k_max = 1;
+    for (int g = 0; g < B.ngroups; ++g) k_max = std::max(k_max, B.g[g].k);
+    const bool one_wave = (long long)rows * csize <= sm_count[dev] + sm_count[dev] / 8;
+    if (!one_wave && B.slice_max <= k256Slice && k_max <= 1024) {
+      c.blockDim = dim3(256);
+      e = cudaLaunchKernelEx(&c, topk_cluster_kernel<256>, scores, idx, B);
+    } else if (!one_wave && B.slice_max <= k512Slice) {
+      c.blockDim = dim3(512);
+      e = cudaLaunchKernelEx(&c, topk_cluster_kernel<512>, scores, idx, B);
+    } else {
+      c.blockDim = dim3(1024);
+      e = cudaLaunchKernelEx(&c, topk_cluster_kernel<1024>, scores, idx, B);
+    }
     if (e != cudaSuccess) {
       err = std::string("top-k cluster launch: ") + cudaGetErrorString(e);
       return PKV_ERR_CUDA;
