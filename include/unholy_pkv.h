@@ -173,6 +173,15 @@ PKV_API int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, i
 PKV_API int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
                                 const int32_t* idx, uint16_t* out, pkv_stream_t stream);
 
+/* pkv_step_gather_fp8 with the list expansion folded in: instead of a token list the caller passes what the top-k over
+ * pools wrote — pools [Q][kp] (valid pools first) and the queries' positions pos [Q] — and entry j of query row t is
+ * what glm_idx_expand (src/kernels/glm_fast.hpp:115-122, src/kernels/glm_fast.hip:737-748) would have written at
+ * idx[t][j]; out is bf16 [Q][kp * pool + pool - 1][width] (step->k is not used). Saves the expanded list's round trip
+ * through memory and one launch. */
+PKV_API int pkv_step_gather_fp8_pools(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
+                                      const int32_t* pools, const int32_t* pos, int kp, int pool, uint16_t* out,
+                                      pkv_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Index-list producer (the step before the gather).
  * ---------------------------------------------------------------------------------------------------------------- */

@@ -577,6 +577,42 @@ def test_step_gather_fp8_all_sequences_in_one_launch(pkv, cuda):
     assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
 
 
+def test_step_gather_fp8_from_pool_lists(pkv, cuda):
+    """pkv_step_gather_fp8_pools: the selected pools and the positions go in, the expansion happens during address
+    resolution; equals the oracle's idx_expand followed by its fp8 gather, per sequence."""
+    g = tl.rng(32)
+    width, block, rpp, kp, pool = 512, 64, 256, 37, 4
+    k = kp * pool + pool - 1
+    case = tl.PagedCase(seed=32, nseq=5, len_lo=40, len_hi=4000, num_pages=120, k=k, width=width, rows_per_page=rpp,
+                        with_keys=False, fill=False)
+    nrows = case.num_pages * rpp
+    codes = g.integers(0, 256, size=(nrows, width), dtype=np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3A
+    scales = g.integers(118, 136, size=(nrows, width // block), dtype=np.uint8)
+    pos = (case.q_visible - 1).astype(np.int32)                    # each query sits at its sequence's last row
+    pos[0] = 2                                                     # fewer rows than one pool: only the tail entries
+    pools = np.full((case.nseq, kp), -1, np.int32)
+    for s in range(case.nseq):
+        full = (int(pos[s]) + 1) // pool
+        m = min(full, kp)
+        pools[s, :m] = g.choice(full, size=m, replace=False)
+    vis = (pos + 1).astype(np.int32)
+    idx = orc.idx_expand(pools, pos, pool)
+    assert idx.shape == (case.nseq, k)
+    want = np.stack([orc.gather_rows_fp8(codes, scales, case.tables[s], rpp, block, idx[s:s + 1], vis[s:s + 1])[0]
+                     for s in range(case.nseq)])
+    d = {n: tl.dev(cuda, a) for n, a in dict(codes=codes, scales=scales, tables=case.tables, chunks=case.chunks,
+                                              q_chunk=case.q_chunk, q_vis=vis, pools=pools, pos=pos).items()}
+    d_out = cuda.full((want.size * 2,), 0x5A, dtype=cuda.uint8, device="cuda")
+    step = tl.make_step(case, d["tables"], d["chunks"], d["q_chunk"], d["q_vis"])
+    capi.check(pkv.pkv_step_gather_fp8_pools(C.byref(step), d["codes"].data_ptr(), d["scales"].data_ptr(), width, block,
+                                             d["pools"].data_ptr(), d["pos"].data_ptr(), kp, pool, d_out.data_ptr(),
+                                             tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert tl.device_status(pkv) == 0
+    assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
+
+
 def test_copy_between_device_and_pinned_host(pkv, cuda):
     """The snapshot save / restore primitive: the reference's state_copies moves slot state between device memory and
     pinned host staging with copy_kernel, i.e. with ordinary loads and stores issued by SMs

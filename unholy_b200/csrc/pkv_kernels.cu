@@ -866,6 +866,22 @@ struct StepRows {
   __device__ __forceinline__ int begin(int t) const { return s.chunks[__ldg(&s.q_chunk[t])].slot; }
   __device__ __forceinline__ long long rid(int slot, int t, int row) const { return physical_row(s, slot, row, t); }
 };
+// Entries given as selected pools instead of a token list: entry j of query row t is what glm_idx_expand
+// (src/kernels/glm_fast.hip:737-748) would have written at idx[t][j] — the tokens of the min((p + 1) / pool, kp) valid
+// pools, then the (p + 1) % pool tokens of the query's incomplete pool, then -1 — computed where it is needed.
+struct PoolList {
+  const int32_t* pools;  // [T][kp]; nullptr: the entries come from idx
+  const int32_t* pos;    // [T]
+  int kp, pool;
+  __device__ __forceinline__ int entry(int t, int j) const {
+    const int p = __ldg(&pos[t]);
+    const int full = (p + 1) / pool, valid = full < kp ? full : kp, tail = (p + 1) % pool;
+    if (j < valid * pool) return __ldg(&pools[size_t(t) * kp + j / pool]) * pool + j % pool;
+    if (j < valid * pool + tail) return p + 1 - tail + (j - valid * pool);
+    return -1;
+  }
+};
+
 // 8 warps move data, a ninth resolves the NEXT tile's entries (index -> block table -> physical row) meanwhile, so the
 // three dependent loads of a resolution are off the data warps' path: one barrier per tile.
 constexpr int kFp8Threads = 256 + 32, kFp8CtasPerSm = 5;
@@ -875,7 +891,7 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
                                                                  const __grid_constant__ ROWS rows, int width, int block,
                                                                  const int32_t* __restrict__ idx,
                                                                  const int32_t* __restrict__ q_visible, int T, int k,
-                                                                 uint16_t* __restrict__ out) {
+                                                                 uint16_t* __restrict__ out, const PoolList pl) {
   __shared__ long long s_rid[2][kGatherRows];
   const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows, upr = width >> 4, nb = width / block;
   const long long total_tiles = (long long)T * tiles_per_q;
@@ -885,7 +901,7 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
     long long rid = -1;
     if (e < k) {
       const int slot = rows.begin(t), vis = __ldg(&q_visible[t]);
-      const int row = __ldg(&idx[size_t(t) * k + e]);
+      const int row = pl.pools ? pl.entry(t, e) : __ldg(&idx[size_t(t) * k + e]);
       if (row >= 0 && row < vis) rid = rows.rid(slot, t, row);
     }
     s_rid[buf][threadIdx.x - 256] = rid;
@@ -1327,29 +1343,44 @@ int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32
   const int sms = d.ok ? d.sms : 148;
   const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
   gather_fp8_kernel<OneSeqRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, OneSeqRows{OneTable{table, rows_per_page}}, width, block,
-                                                          idx, q_visible, T, k, out);
+                                                          idx, q_visible, T, k, out, PoolList{nullptr, nullptr, 0, 0});
+  PKV_LAUNCH_CHECK("gather_fp8_kernel");
+  return PKV_OK;
+}
+
+// Shared by the two step-wide fp8 gathers: entries from idx [Q][k], or from pools [Q][kp] + pos (k = kp * pool + pool - 1).
+static int step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
+                           const int32_t* idx, const PoolList& pl, int k, uint16_t* out, cudaStream_t stream, const char* name) {
+  if (!step) return fail(PKV_ERR_ARG, std::string(name) + ": null step");
+  const pkv_step& s = *step;
+  if (s.Q <= 0 || k <= 0) return PKV_OK;
+  if (!codes || !scales || !(idx || pl.pools) || !out || !s.tables || !s.chunks || !s.q_chunk || !s.q_visible)
+    return fail(PKV_ERR_ARG, std::string(name) + ": null pointer");
+  if (const int rc = check_quant_shape(s.Q, width, block, name)) return rc;
+  if (width <= 0 || width % 16 != 0 || block % 16 != 0 || s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks <= 0)
+    return fail(PKV_ERR_ARG, std::string(name) + ": width must be a positive multiple of 16, the step needs pages and chunks");
+  if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, std::string(name) + ": codes and out must be 16-byte aligned");
+  const long long tiles = (long long)s.Q * ((k + kGatherRows - 1) / kGatherRows);
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
+  gather_fp8_kernel<StepRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q,
+                                                                k, out, pl);
   PKV_LAUNCH_CHECK("gather_fp8_kernel");
   return PKV_OK;
 }
 
 int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
                         const int32_t* idx, uint16_t* out, pkv_stream_t stream) {
-  if (!step) return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: null step");
-  const pkv_step& s = *step;
-  if (s.Q <= 0 || s.k <= 0) return PKV_OK;
-  if (!codes || !scales || !idx || !out || !s.tables || !s.chunks || !s.q_chunk || !s.q_visible)
-    return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: null pointer");
-  if (const int rc = check_quant_shape(s.Q, width, block, "pkv_step_gather_fp8")) return rc;
-  if (width <= 0 || width % 16 != 0 || block % 16 != 0 || s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks <= 0)
-    return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: width must be a positive multiple of 16, the step needs pages and chunks");
-  if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, "pkv_step_gather_fp8: codes and out must be 16-byte aligned");
-  const long long tiles = (long long)s.Q * ((s.k + kGatherRows - 1) / kGatherRows);
-  const DeviceInfo& d = device_info();
-  const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
-  gather_fp8_kernel<StepRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q, s.k, out);
-  PKV_LAUNCH_CHECK("gather_fp8_kernel");
-  return PKV_OK;
+  return step_gather_fp8(step, codes, scales, width, block, idx, PoolList{nullptr, nullptr, 0, 0}, step ? step->k : 0, out, stream,
+                         "pkv_step_gather_fp8");
+}
+
+int pkv_step_gather_fp8_pools(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
+                              const int32_t* pools, const int32_t* pos, int kp, int pool, uint16_t* out, pkv_stream_t stream) {
+  if (kp <= 0 || pool <= 0 || !pools || !pos) return fail(PKV_ERR_ARG, "pkv_step_gather_fp8_pools: pools, pos, kp > 0 and pool > 0 are required");
+  return step_gather_fp8(step, codes, scales, width, block, nullptr, PoolList{pools, pos, kp, pool}, kp * pool + pool - 1, out, stream,
+                         "pkv_step_gather_fp8_pools");
 }
 
 int pkv_copy_pages(const pkv_pool_desc* pools, int npools, const int32_t* src_ids, const int32_t* dst_ids, int n,
