@@ -155,6 +155,10 @@ enum {
   PKV_DO_KEYS_FP4 = 2, /* quantise layer.keys into layer.key_pool_fp4 */
   PKV_DO_KEYS_FP8 = 4, /* quantise layer.keys into layer.key_fp8_codes / key_fp8_scales */
   PKV_DO_GATHER = 8,   /* gather layer.idx rows into layer.gathered */
+  PKV_KEYS_HADAMARD = 32, /* rotate every 128-wide key row by hadamard128 (src/kernels/ref_elem.hip:111-135, bf16 result)
+                             before it is quantised: the reference's hadamard128 + store_rows_fp4 pair of
+                             compress_chunk (src/model/forward_ref.hip:736-738) in the append itself; layer.keys is
+                             not modified */
   PKV_VARIANT_BULK = 256 /* gather through the bulk-copy (TMA) pipeline instead of vector loads */
 };
 
@@ -218,6 +222,11 @@ PKV_API int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* gr
  * never selected. k <= 1024 as in the reference (PKV_ERR_ARG beyond). No scratch: one CTA per row selects in shared
  * memory. T <= 0 or n <= 0 returns PKV_OK without a launch. */
 PKV_API int pkv_topk_f32(const float* scores, int T, int n, long long ld, int k, int32_t* idx, pkv_stream_t stream);
+
+/* hadamard128 — src/kernels/ref.hpp:63, src/kernels/ref_elem.hip:111-135,310-313: in place, every segment of 128 bf16
+ * values of x [nseg][128] becomes its Hadamard transform (seven fp32 butterfly stages in the reference's order, times
+ * 128^-0.5, rounded to bf16). x must be 16-byte aligned. */
+PKV_API int pkv_hadamard128(uint16_t* x, size_t nseg, pkv_stream_t stream);
 
 /* glm_idx_expand — src/kernels/glm_fast.hpp:115-122, src/kernels/glm_fast.hip:737-748,915-920. Selected pools
  * device int32 [n][k] (a top-k's output: valid pools first) and the queries' positions pos [n] -> the compact token

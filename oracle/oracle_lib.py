@@ -40,6 +40,7 @@ _SIGS = {
     "orc_topk_bf16": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_topk_f32": (None, [_vp, _i, _i, C.c_longlong, _i, _vp, _i]),
     "orc_idx_expand": (None, [_vp, _vp, _vp, _i, _i, _i]),
+    "orc_hadamard128": (None, [_vp, C.c_size_t]),
     "orc_state_copies": (None, [_vp, _vp, _vp, _i, _vp, _vp, _i, _vp, C.c_size_t, _i]),
     "orc_gather_rows_fp8": (None, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "orc_hardware_threads": (_i, []),
@@ -169,6 +170,13 @@ def state_copies(bufs, seg_off, ops, snap, snap_bytes, save):
     slot = np.array([o[0] for o in ops], np.int32)
     sn = np.array([o[1] for o in ops], np.int32)
     lib().orc_state_copies(_p(dev), _p(nbytes), _p(off), n, _p(slot), _p(sn), len(ops), _p(snap), snap_bytes, int(save))
+
+
+def hadamard128(x):
+    """In place on a contiguous uint16 (bf16 bits) array whose size is a multiple of 128."""
+    assert x.dtype == np.uint16 and x.flags.c_contiguous and x.size % 128 == 0
+    lib().orc_hadamard128(_p(x), x.size // 128)
+    return x
 
 
 def idx_expand(pools, pos, pool):

@@ -418,6 +418,25 @@ void orc_state_copies(uint8_t* const* seg_dev, const size_t* seg_bytes, const si
     }
 }
 
+// src/kernels/ref_elem.hip:111-135 (hadamard128_kernel): per 128-value segment seven butterfly stages in fp32,
+// (b[i], b[i + h]) <- (a + c, a - c) for i = (t / h) * 2h + t % h, t = 0..63, then * 128^-0.5 and bf16 rounding, in place.
+void orc_hadamard128(uint16_t* x, size_t nseg) {
+  for (size_t g = 0; g < nseg; ++g) {
+    uint16_t* p = x + g * 128;
+    float b[128];
+    for (int i = 0; i < 128; ++i) b[i] = bf16_to_f32(p[i]);
+    for (int h = 1; h < 128; h <<= 1)
+      for (int t = 0; t < 64; ++t) {
+        const int i = (t / h) * 2 * h + (t % h);
+        const float a = b[i], c = b[i + h];
+        b[i] = a + c;
+        b[i + h] = a - c;
+      }
+    const float sc = 0.08838834764831845f;
+    for (int i = 0; i < 128; ++i) p[i] = f32_to_bf16(b[i] * sc);
+  }
+}
+
 int orc_hardware_threads() { return int(std::thread::hardware_concurrency()); }
 
 }  // extern "C"

@@ -10,6 +10,7 @@ _LIB_PATH = _PKG / "lib" / "libunholy_pkv.so"
 PKV_OK, PKV_ERR_ARG, PKV_ERR_CUDA, PKV_ERR_DEVICE, PKV_ERR_LIMIT = range(5)
 PKV_MAX_LAYERS = 48
 PKV_DO_ROWS, PKV_DO_KEYS_FP4, PKV_DO_KEYS_FP8, PKV_DO_GATHER, PKV_VARIANT_BULK = 1, 2, 4, 8, 256
+PKV_KEYS_HADAMARD = 32
 
 c_i32p = C.POINTER(C.c_int32)
 c_u8p = C.POINTER(C.c_uint8)
@@ -71,6 +72,7 @@ _SIGS = {
     "pkv_step_run": (_i, [C.POINTER(PkvStep), C.POINTER(PkvLayer), _i, _i, _vp]),
     "pkv_step_gather_fp8": (_i, [C.POINTER(PkvStep), _vp, _vp, _i, _i, _vp, _vp, _vp]),
     "pkv_step_gather_fp8_pools": (_i, [C.POINTER(PkvStep), _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp]),
+    "pkv_hadamard128": (_i, [_vp, _sz, _vp]),
     "pkv_topk_scratch_words": (_sz, [_i, _i, _i]),
     "pkv_topk_bf16": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp, _sz, _vp]),
     "pkv_topk_static_scratch_words": (_sz, []),

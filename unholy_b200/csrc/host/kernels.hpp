@@ -123,6 +123,10 @@ inline void glm_topk(const float* scores, int ld, int n, int cols, int k, int32_
 inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
   pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
 }
+// src/kernels/ref.hpp:63.
+inline void hadamard128(bf16* x, size_t nseg, cudaStream_t st) {
+  pkv_throw(pkv_hadamard128(x, nseg, reinterpret_cast<pkv_stream_t>(st)), "hadamard128");
+}
 // ResidentModel::state_copies (src/engine/resident.hip:545-557): SnapSeg and StateOp keep their field names.
 using SnapSeg = pkv_state_seg;
 using StateOp = pkv_state_op;

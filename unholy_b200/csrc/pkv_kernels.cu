@@ -250,8 +250,9 @@ constexpr int kGatherUnroll = 6;            // 32 rows x 72 vectors = 384 thread
 // One 128-wide key row held by 16 consecutive lanes (8 values each, lane j of the row in `j`): MXFP4 and / or fp8
 // quantisation and the stores into the row's place (physical row `rid`; negative: nothing is stored). Every lane of the
 // warp must call it: the block maxima and the row's four MXFP4 scale bytes travel by shuffles.
-__device__ __forceinline__ void quantise_key_row(const pkv_step& s, const pkv_layer& ly, const float* v, long long rid, int j,
-                                                 bool fp4, bool fp8) {
+__device__ __forceinline__ void quantise_key_row(const pkv_step& s, const pkv_layer& ly, float* v, long long rid, int j,
+                                                 bool fp4, bool fp8, bool rotate) {
+  if (rotate) pkv::hadamard128_lanes(v, j);  // PKV_KEYS_HADAMARD: the reference's hadamard128 in front of store_rows_fp4
   const float a8 = pkv::absmax8(v);
   if (fp4) {
     const uint32_t se = pkv::fp4_scale_exp(pkv::group_max(a8, 4));
@@ -336,7 +337,7 @@ __device__ void append_tile(const StepParams& P, const pkv_layer& ly, int t_firs
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
-    quantise_key_row(s, ly, v, rid, j, fp4, fp8);
+    quantise_key_row(s, ly, v, rid, j, fp4, fp8, (P.flags & PKV_KEYS_HADAMARD) != 0);
   }
   __syncthreads();
 }
@@ -472,7 +473,7 @@ __device__ __forceinline__ void quantise_staged_keys(const StepParams& P, const 
     const long long rid = r < nrows ? rids[r] : -1;
     float v[8];
     pkv::unpack8(*reinterpret_cast<const uint4*>(stage + size_t(r < ROWS ? r : 0) * (PKV_FP4_ROW_DIM * 2) + j * 16), v);
-    quantise_key_row(s, ly, v, rid, j, fp4, fp8);
+    quantise_key_row(s, ly, v, rid, j, fp4, fp8, (P.flags & PKV_KEYS_HADAMARD) != 0);
   }
 }
 
@@ -950,6 +951,25 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
   }
 }
 
+// hadamard128 in place: 16 lanes per 128-value segment, 8 values each.
+__global__ void __launch_bounds__(256) hadamard128_kernel(uint16_t* __restrict__ x, size_t nseg) {
+  const size_t groups = (nseg + 1) / 2 * 2;  // whole warps stay in the loop: the shuffles need every lane
+  for (size_t g = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g < groups; g += (size_t(gridDim.x) * blockDim.x) >> 4) {
+    const int j = threadIdx.x & 15;
+    const bool live = g < nseg;
+    uint4* p = reinterpret_cast<uint4*>(x + (live ? g : 0) * 128) + j;
+    float v[8];
+    pkv::unpack8(live ? *p : make_uint4(0, 0, 0, 0), v);
+    pkv::hadamard128_lanes(v, j);
+    if (live) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = (__float_as_uint(v[2 * i]) >> 16) | (__float_as_uint(v[2 * i + 1]) & 0xffff0000u);
+      *p = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t n) {
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x;
@@ -1201,6 +1221,14 @@ static int quant_launch(int mode, const uint16_t* x, int ldx, uint8_t* q, uint8_
   else if (mode == kFp8Fake) quant_rows_kernel<kFp8Fake><<<grid, 256, 0, stream>>>(x, ldx, nullptr, nullptr, rows, cols, block, vec);
   else quant_rows_kernel<kFp4Fake><<<grid, 256, 0, stream>>>(x, ldx, nullptr, nullptr, rows, cols, block, vec);
   PKV_LAUNCH_CHECK("quant_rows_kernel");
+  return PKV_OK;
+}
+
+int pkv_hadamard128(uint16_t* x, size_t nseg, pkv_stream_t stream) {
+  if (nseg == 0) return PKV_OK;
+  if (!x || !aligned16(x)) return fail(PKV_ERR_ARG, "pkv_hadamard128: x must be a 16-byte aligned device pointer");
+  hadamard128_kernel<<<grid_for((long long)std::min<size_t>(nseg, size_t(1) << 40) * 16, 256, 16), 256, 0, stream>>>(x, nseg);
+  PKV_LAUNCH_CHECK("hadamard128_kernel");
   return PKV_OK;
 }
 

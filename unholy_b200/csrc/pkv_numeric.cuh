@@ -123,4 +123,33 @@ __device__ __forceinline__ uint2 fp8_pack8(const float* v, float sc) {
   return make_uint2(w[0], w[1]);
 }
 
+// Hadamard transform of one 128-value segment held by 16 consecutive lanes, 8 values each (value j * 8 + e in v[e] of
+// lane j of the group), as ewtodd/unholy's hadamard128_kernel does it (src/kernels/ref_elem.hip:111-135): seven
+// butterfly stages h = 1 .. 64 in fp32, (a, c) -> (a + c, a - c) for the pair (i, i + h), then * 128^-0.5 and rounding
+// to bf16. Stages 1, 2, 4 pair values of one lane; stages 8 .. 64 pair lane j with lane j ^ (h / 8): the lower lane
+// keeps own + other, the upper one other - own — the same two operands per result as the reference, so the same
+// bits. Every lane of the warp must call it. On return v holds the bf16-rounded values as floats.
+__device__ __forceinline__ void hadamard128_lanes(float* v, int j) {
+#pragma unroll
+  for (int h = 1; h <= 4; h <<= 1)
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int i = (t / h) * 2 * h + (t % h);
+      const float a = v[i], c = v[i + h];
+      v[i] = a + c;
+      v[i + h] = a - c;
+    }
+#pragma unroll
+  for (int m = 1; m <= 8; m <<= 1) {
+    const bool upper = (j & m) != 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[e], m);
+      v[e] = upper ? o - v[e] : v[e] + o;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = bf16_bits_to_f32(f32_to_bf16_bits(v[e] * 0.08838834764831845f));
+}
+
 }  // namespace pkv
