@@ -65,6 +65,14 @@ PKV_API int pkv_device_status(int* status_out);
 PKV_API int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* pool, const int32_t* table, int rows_per_page,
                    int row_stride, int row0, pkv_stream_t stream);
 
+/* fake_quant_fp8 + store_rows in one pass — the pair compress_chunk issues for KV rows (src/model/forward_ref.hip:739-741:
+ * fake_quant_fp8(rb, d, nrows, d - rope_dim, 64) then store_rows(rb, ...)): the first quant_cols columns of every row
+ * are quantised to e4m3 with one power-of-two scale per `block` values and dequantised (src/kernels/ref_elem.hip:18-41),
+ * the other columns are copied, and the row goes to its place in the pool; `rows` is read once and not modified.
+ * width % block == 0, quant_cols % block == 0, block 32 / 64 / 128, rows and pool 16-byte aligned. */
+PKV_API int pkv_store_rows_fake_fp8(const uint16_t* rows, int n, int width, int quant_cols, int block, uint16_t* pool,
+                                    const int32_t* table, int rows_per_page, int row_stride, int row0, pkv_stream_t stream);
+
 /* store_rows_fp4 — src/kernels/indexer.hpp:20-32, src/kernels/indexer.hip:18-53,802-806.
  * rows [n][128] bf16 -> MXFP4: page p at pool + p*rows_per_page*68; rows_per_page code rows of 64 B (even column =
  * low nibble) followed by rows_per_page scale rows of 4 e8m0 bytes. The reference fixes rows_per_page = 64. */

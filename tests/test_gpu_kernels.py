@@ -613,6 +613,29 @@ def test_step_gather_fp8_from_pool_lists(pkv, cuda):
     assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
 
 
+@pytest.mark.parametrize("width,quant_cols,block,stride", [(576, 512, 64, 576), (576, 512, 64, 640), (512, 512, 128, 512),
+                                                           (128, 64, 32, 128)])
+def test_store_rows_fake_fp8_one_pass(pkv, cuda, width, quant_cols, block, stride):
+    """pkv_store_rows_fake_fp8 equals the reference's pair fake_quant_fp8 (first quant_cols columns) then store_rows
+    (src/model/forward_ref.hip:739-741); the caller's rows stay as they were."""
+    g = tl.rng(33)
+    rpp, pages, row0 = 64, 7, 37
+    n = pages * rpp - row0 - 5
+    table = shuffled_table(g, pages)
+    rows = tl.outlier_rows(g, n, width)
+    pool = tl.normal_bf16(g, (pages * rpp, stride))
+    want = pool.copy()
+    fake = rows.copy()
+    orc.fake_quant_fp8(fake, quant_cols, block)
+    orc.store_rows(fake, want, table, rpp, stride, row0)
+    d_rows, d_pool, d_t = tl.dev(cuda, rows), tl.dev(cuda, pool), tl.dev(cuda, table)
+    capi.check(pkv.pkv_store_rows_fake_fp8(d_rows.data_ptr(), n, width, quant_cols, block, d_pool.data_ptr(), d_t.data_ptr(),
+                                           rpp, stride, row0, tl.stream_ptr(cuda)))
+    cuda.cuda.synchronize()
+    assert np.array_equal(tl.host(d_pool, np.uint16, want.shape), want)
+    assert np.array_equal(tl.host(d_rows, np.uint16, rows.shape), rows)
+
+
 def test_copy_between_device_and_pinned_host(pkv, cuda):
     """The snapshot save / restore primitive: the reference's state_copies moves slot state between device memory and
     pinned host staging with copy_kernel, i.e. with ordinary loads and stores issued by SMs

@@ -123,6 +123,13 @@ inline void glm_topk(const float* scores, int ld, int n, int cols, int k, int32_
 inline void glm_idx_expand(const int32_t* pools, const int32_t* pos, int32_t* idx, int n, int k, int pool, cudaStream_t st) {
   pkv_throw(pkv_idx_expand(pools, pos, idx, n, k, pool, reinterpret_cast<pkv_stream_t>(st)), "glm_idx_expand");
 }
+// fake_quant_fp8(rows, width, n, quant_cols, block) followed by store_rows(rows, n, width, dst, row0) (ref.hpp:24,100;
+// the pair of src/model/forward_ref.hip:739-741) in one pass; rows is not modified.
+inline void store_rows_fake_fp8(const bf16* rows, int n, int width, int quant_cols, int block, PagedRows dst, int row0,
+                                cudaStream_t st) {
+  pkv_throw(pkv_store_rows_fake_fp8(rows, n, width, quant_cols, block, dst.pool, dst.table, dst.rows_per_page, dst.row_stride,
+                                    row0, reinterpret_cast<pkv_stream_t>(st)), "store_rows_fake_fp8");
+}
 // src/kernels/ref.hpp:63.
 inline void hadamard128(bf16* x, size_t nseg, cudaStream_t st) {
   pkv_throw(pkv_hadamard128(x, nseg, reinterpret_cast<pkv_stream_t>(st)), "hadamard128");

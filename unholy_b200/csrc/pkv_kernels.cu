@@ -719,6 +719,39 @@ __global__ void __launch_bounds__(256) store_rows_elem_kernel(const uint16_t* __
   }
 }
 
+// fake_quant_fp8 of a row's first quant_cols columns (blocks of `block`, src/kernels/ref_elem.hip:18-41) and store_rows
+// in one pass: every 16-byte vector of a row is read once, quantised and dequantised where it lies in the quantised
+// columns, and written to its place in the pool. One thread per vector; a block's lanes are neighbours.
+__global__ void __launch_bounds__(256) store_rows_fake_fp8_kernel(const uint16_t* __restrict__ rows, long long total, int vpr,
+                                                                  int quant_vecs, int group, uint16_t* pool, OneTable tb,
+                                                                  int row_stride, int row0) {
+  const long long span = ((total + 31) / 32) * 32;  // whole warps stay in the loop: the shuffles need every lane
+  for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < span; u += (long long)gridDim.x * blockDim.x) {
+    const bool live = u < total;
+    const int r = live ? int(u / vpr) : 0, c = live ? int(u - (long long)r * vpr) : 0;
+    const uint4 raw = live ? ld_stream(reinterpret_cast<const uint4*>(rows) + u) : make_uint4(0, 0, 0, 0);
+    float v[8];
+    pkv::unpack8(raw, v);
+    const float amax = pkv::group_max(pkv::absmax8(v), group);
+    if (!live) continue;
+    uint4* dst = reinterpret_cast<uint4*>(pool + one_row(tb, row0 + r) * size_t(row_stride)) + c;
+    if (c < quant_vecs) {
+      const float sc = pkv::e8m0_bits_to_f32(pkv::fp8_scale_exp(amax));
+      const uint2 codes = pkv::fp8_pack8(v, sc);
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(((i < 2 ? codes.x : codes.y) >> (16 * (i & 1))) & 0xffu) * sc);
+        const uint32_t hi = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(((i < 2 ? codes.x : codes.y) >> (16 * (i & 1) + 8)) & 0xffu) * sc);
+        w[i] = lo | (hi << 16);
+      }
+      st_stream(dst, make_uint4(w[0], w[1], w[2], w[3]));
+    } else {
+      st_stream(dst, raw);
+    }
+  }
+}
+
 // MXFP4 append of 128-wide rows: 16 threads per row.
 __global__ void __launch_bounds__(256) store_rows_fp4_kernel(const uint16_t* __restrict__ rows, int n, uint8_t* pool,
                                                              OneTable tb, int row0) {
@@ -1184,6 +1217,22 @@ int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* pool, const
     store_rows_elem_kernel<<<grid_for(total, 256, 16), 256, 0, stream>>>(rows, total, width, pool, tb, row_stride, row0);
   }
   PKV_LAUNCH_CHECK("store_rows");
+  return PKV_OK;
+}
+
+int pkv_store_rows_fake_fp8(const uint16_t* rows, int n, int width, int quant_cols, int block, uint16_t* pool,
+                            const int32_t* table, int rows_per_page, int row_stride, int row0, pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (!rows || !pool || !table) return fail(PKV_ERR_ARG, "pkv_store_rows_fake_fp8: null pointer");
+  if (const int rc = check_quant_shape(n, quant_cols, block, "pkv_store_rows_fake_fp8")) return rc;
+  if (width <= 0 || width % block != 0 || quant_cols > width || rows_per_page <= 0 || row_stride < width || row_stride % 8 != 0 ||
+      row0 < 0)
+    return fail(PKV_ERR_ARG, "pkv_store_rows_fake_fp8: width must be a multiple of block, quant_cols <= width, row_stride % 8 == 0");
+  if (!aligned16(rows) || !aligned16(pool)) return fail(PKV_ERR_ARG, "pkv_store_rows_fake_fp8: rows and pool must be 16-byte aligned");
+  const long long total = (long long)n * (width / 8);
+  store_rows_fake_fp8_kernel<<<grid_for(total, 256, 16), 256, 0, stream>>>(rows, total, width / 8, quant_cols / 8, block / 8, pool,
+                                                                           OneTable{table, rows_per_page}, row_stride, row0);
+  PKV_LAUNCH_CHECK("store_rows_fake_fp8");
   return PKV_OK;
 }
 
