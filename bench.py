@@ -1240,12 +1240,48 @@ def run_gather_fp8(args):
         want = val.view(k, width).to(torch.bfloat16)
         want[masked] = 0
         ok_b = ok_b and bool(torch.equal(out_b[t].view(torch.int16), want.view(torch.int16)))
+    # The GLM-style decode chain for one layer: pool scores -> top-512 pools -> (expansion folded into) the gather of
+    # 2051 token rows per sequence. Two launches; compared on the device with top-k, pkv_idx_expand and the list gather.
+    kp, pool = 512, 4
+    kc = kp * pool + pool - 1
+    npool = per_seq // pool
+    pos = torch.full((T,), per_seq - 1, dtype=torch.int32, device=dev)
+    sc32 = torch.randn(T, npool, generator=g, device=dev)
+    pools = torch.empty(T, kp, dtype=torch.int32, device=dev)
+    out_c = torch.empty(T, kc, width, dtype=torch.bfloat16, device=dev)
+    step_c = capi.PkvStep.from_buffer_copy(step)
+    step_c.k = kc
+
+    def chain():
+        capi.check(lib.pkv_topk_f32(sc32.data_ptr(), T, npool, npool, kp, pools.data_ptr(), sp))
+        capi.check(lib.pkv_step_gather_fp8_pools(C.byref(step_c), codes.data_ptr(), scales.data_ptr(), width, block,
+                                                 pools.data_ptr(), pos.data_ptr(), kp, pool, out_c.data_ptr(), sp))
+
+    for _ in range(3):
+        chain()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        chain()
+    e1.record()
+    torch.cuda.synchronize()
+    us_c = e0.elapsed_time(e1) / reps * 1e3
+    idx_c = torch.empty(T, kc, dtype=torch.int32, device=dev)
+    out_l = torch.empty_like(out_c)
+    capi.check(lib.pkv_idx_expand(pools.data_ptr(), pos.data_ptr(), idx_c.data_ptr(), T, kp, pool, sp))
+    capi.check(lib.pkv_step_gather_fp8(C.byref(step_c), codes.data_ptr(), scales.data_ptr(), width, block, idx_c.data_ptr(),
+                                       out_l.data_ptr(), sp))
+    torch.cuda.synchronize()
+    ok_c = bool(torch.equal(out_c.view(torch.int16), out_l.view(torch.int16)))
     nbytes = T * k * (width + width // block + width * 2)
     _emit("gather_fp8", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
         "config": {"workload": f"{T} x {k} entries of fp8 rows (512 e4m3 + 8 e8m0) -> bf16, pool of {rows} rows (pkv_gather_rows_fp8)"},
-        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok and ok_b},
+        "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok and ok_b and ok_c},
         "step_call_64_sequences": {"what": "pkv_step_gather_fp8: 64 sequences x 2048 entries, own block tables, one launch",
-                                   "us_per_call": round(us_b, 2), "GBps": round(nbytes / (us_b * 1e-6) / 1e9, 1), "ok": ok_b}})
+                                   "us_per_call": round(us_b, 2), "GBps": round(nbytes / (us_b * 1e-6) / 1e9, 1), "ok": ok_b},
+        "glm_decode_chain": {"what": f"pkv_topk_f32 (top-{kp} of {npool} pool scores x {T}) + pkv_step_gather_fp8_pools "
+                                     f"({kc} rows per sequence, expansion folded in): two launches",
+                             "us_per_layer": round(us_c, 2), "equals_expand_then_gather": ok_c}})
 
 
 def main():
