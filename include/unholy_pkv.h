@@ -321,6 +321,17 @@ PKV_API int pkv_pool_seq_open(pkv_pool* p);                 /* new empty sequenc
  * number of tokens covered. boundary_ok[i] (may be NULL = all) says whether the sequence may resume at the end of page
  * i (the reference resumes only where a state snapshot was saved). */
 PKV_API int pkv_pool_match_prefix(pkv_pool* p, int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok);
+/* The same two calls for sequences that hold image blocks: positions are named by 64-bit keys instead of token ids —
+ * token_key of src/engine/engine.cpp:264-270: uint32(token) for text, mix64(image hash + offset in the block) for the
+ * positions of an image block (every image's placeholder tokens are the same few ids, so the tokens alone would name
+ * different images alike). pkv_token_keys fills keys_out [n] from the tokens and the blocks (starts, lens, hashes)
+ * [nimages] in position order; pkv_page_hash_keys is pkv_page_hash over keys. The reference's second image rule,
+ * "never resume inside a whole image block" (engine.cpp:292-296), is the caller's boundary_ok. */
+PKV_API int pkv_token_keys(const int32_t* tokens, int n, const int32_t* starts, const int32_t* lens, const uint64_t* hashes,
+                           int nimages, uint64_t* keys_out);
+PKV_API int pkv_pool_match_prefix_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, const uint8_t* boundary_ok);
+PKV_API int pkv_pool_register_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, int done_pos);
+PKV_API uint64_t pkv_page_hash_keys(const uint64_t* keys, int page_tokens, int page_index);
 PKV_API int pkv_pool_assign_slot(pkv_pool* p, int seq);     /* free_slots_.back(); writes the table row; -1 if none */
 /* alloc_pages (engine.cpp:437-444): pages for positions [0, upto). Returns 1, or 0 (nothing changed) when the pool
  * cannot supply them. */
@@ -336,20 +347,30 @@ PKV_API int pkv_pool_seq_close(pkv_pool* p, int seq);
 /* Copy-on-write fork: the new sequence shares ALL pages of positions [0, ntokens) of `from`, including a partial
  * last page (refs++ each). Returns the new handle. */
 PKV_API int pkv_pool_fork(pkv_pool* p, int from, int ntokens);
-/* Before writing rows [s0, s0+n) of seq: every touched page with refs > 1 is replaced by take_page() in the
- * sequence's table (old refs--). Emits the (src, dst) page pairs whose payload must be duplicated with
- * pkv_copy_pages before the write. Returns the pair count, or -1 when the pool cannot supply the pages. */
+/* Before writing rows [s0, s0+n) of seq: every touched page that is not privately writable — another sequence
+ * references it (refs > 1), or the prefix cache names it (writing in place would leave modified rows under the old
+ * name for a later pkv_pool_match_prefix) — is replaced by take_page() in the sequence's table (old refs--; a named
+ * page whose last reference this was stays cached and becomes evictable). Emits the (src, dst) page pairs whose
+ * payload must be duplicated with pkv_copy_pages before the write. A named page held by this sequence alone loses its
+ * name and is written in place when the pool has no page to spare. Returns the pair count; -1 when the pool cannot
+ * supply the pages or an argument is bad; -2 when cap (or a NULL output) cannot take the pairs. On -1 and -2 NOTHING
+ * has changed: pkv_pool_cow_pairs gives the count to size the arrays with, and the call can be repeated. */
 PKV_API int pkv_pool_cow(pkv_pool* p, int seq, int s0, int n, int32_t* src_out, int32_t* dst_out, int cap);
+PKV_API int pkv_pool_cow_pairs(const pkv_pool* p, int seq, int s0, int n); /* pairs pkv_pool_cow would emit now; -1: no room */
 /* Moves up to `count` pages from the LRU front of the evictable list to the free list (the evict branch of
  * take_page, engine.cpp:239-245, without handing the page out). Returns how many were freed. */
 PKV_API int pkv_pool_free_lru(pkv_pool* p, int count, int32_t* freed_out, int cap);
 /* Hole-filling compaction: with W live pages, live ids >= W (ascending) move into free ids < W (ascending);
  * tables, page info, hash map and LRU entries are rewritten and the free list rebuilt descending. Emits the moves for
- * pkv_copy_pages. Returns the move count. */
+ * pkv_copy_pages. Returns the move count; -2 (and nothing has changed) when cap or a NULL output cannot take the moves
+ * that pkv_pool_compact_pairs counts. */
 PKV_API int pkv_pool_compact(pkv_pool* p, int32_t* src_out, int32_t* dst_out, int cap);
+PKV_API int pkv_pool_compact_pairs(const pkv_pool* p);
 
 /* Migration between two pools (shards): the sequence's pages leave `src` (unref) and are taken from `dst` in
- * logical order; returns the new handle in dst through seq_out and emits the (src page, dst page) pairs. */
+ * logical order; returns the pair count, the new handle in dst through seq_out, and emits the (src page, dst page)
+ * pairs. -1: dst cannot hold the sequence or a bad argument; -2: cap (or a NULL output) is smaller than the sequence's
+ * page count (pkv_pool_seq_pages). Nothing has changed on -1 and -2. */
 PKV_API int pkv_pool_migrate(pkv_pool* src, int seq, pkv_pool* dst, int* seq_out, int32_t* src_out, int32_t* dst_out,
                      int cap);
 

@@ -121,6 +121,30 @@ uint64_t refeng_submit(void* h, const int32_t* prompt, int n, int max_tokens) {
   return d->engine->submit(std::move(r), [](GenOutput&&) {});
 }
 
+// A prompt with image blocks (src/engine/engine.hpp:57-61): block i covers positions [starts[i], starts[i] + lens[i])
+// and is named by hashes[i]; the embedding rows the engine hands to the model are zeros of width 4 (the recording
+// model ignores them).
+uint64_t refeng_submit_images(void* h, const int32_t* prompt, int n, int max_tokens, const int32_t* starts,
+                              const int32_t* lens, const uint64_t* hashes, int nimages) {
+  auto* d = static_cast<Driver*>(h);
+  GenRequest r;
+  r.prompt.assign(prompt, prompt + n);
+  for (int i = 0; i < nimages; ++i) {
+    GenImage im;
+    im.start = starts[i];
+    im.len = lens[i];
+    im.span_start = starts[i];
+    im.span_end = starts[i] + lens[i] - 1;
+    im.hash = hashes[i];
+    im.rows = std::make_shared<const std::vector<uint16_t>>(size_t(lens[i]) * 4, uint16_t(0));
+    r.images.push_back(std::move(im));
+  }
+  r.max_tokens = max_tokens;
+  r.ignore_eos = true;
+  r.sampling.temperature = 0.0f;
+  return d->engine->submit(std::move(r), [](GenOutput&&) {});
+}
+
 int refeng_iterate(void* h) {
   auto* d = static_cast<Driver*>(h);
   const bool did = d->engine->iterate();

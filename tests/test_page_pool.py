@@ -21,6 +21,8 @@ from oracle import build_oracle
 from unholy_b200 import capi
 
 i32p = C.POINTER(C.c_int32)
+u64p = C.POINTER(C.c_uint64)
+u8p = C.POINTER(C.c_uint8)
 
 
 def ptr(a):
@@ -36,6 +38,8 @@ def refeng():
     h.refeng_create.restype, h.refeng_create.argtypes = C.c_void_p, [C.c_int] * 6
     h.refeng_destroy.argtypes = [C.c_void_p]
     h.refeng_submit.restype, h.refeng_submit.argtypes = C.c_uint64, [C.c_void_p, i32p, C.c_int, C.c_int]
+    h.refeng_submit_images.restype = C.c_uint64
+    h.refeng_submit_images.argtypes = [C.c_void_p, i32p, C.c_int, C.c_int, i32p, i32p, u64p, C.c_int]
     h.refeng_iterate.restype, h.refeng_iterate.argtypes = C.c_int, [C.c_void_p]
     h.refeng_trace_len.restype, h.refeng_trace_len.argtypes = C.c_long, [C.c_void_p]
     h.refeng_trace_copy.argtypes = [C.c_void_p, C.c_void_p]
@@ -57,6 +61,8 @@ class Replay:
         self.tokens, self.handle, self.computed = {}, {}, {}
         self.waiting, self.running = deque(), []
         self.saved = set()
+        self.images = {}
+        self.first_hit = {}
         self.cursor = 0
         self.tables_checked = 0
         self.max_cached = 0
@@ -66,16 +72,35 @@ class Replay:
         self.ref.refeng_destroy(self.eng)
         self.pkv.pkv_pool_destroy(self.pool)
 
-    def submit(self, prompt, max_tokens):
+    def submit(self, prompt, max_tokens, images=None):
+        """images: [(start, len, hash)] in position order, or None for a text prompt."""
         a = np.ascontiguousarray(prompt, np.int32)
-        rid = int(self.ref.refeng_submit(self.eng, ptr(a), len(a), max_tokens))
+        if images:
+            st, ln = (np.array([im[j] for im in images], np.int32) for j in (0, 1))
+            hs = np.array([im[2] for im in images], np.uint64)
+            rid = int(self.ref.refeng_submit_images(self.eng, ptr(a), len(a), max_tokens, ptr(st), ptr(ln),
+                                                    hs.ctypes.data_as(u64p), len(images)))
+            self.images[rid] = (st, ln, hs)
+        else:
+            rid = int(self.ref.refeng_submit(self.eng, ptr(a), len(a), max_tokens))
         self.tokens[rid] = list(map(int, a))
         self.waiting.append(rid)
         return rid
 
+    def keys(self, rid):
+        """The sequence's positions as 64-bit page-name keys (text: the token id; image positions: hash and offset)."""
+        t = np.asarray(self.tokens[rid], np.int32)
+        k = np.zeros(len(t), np.uint64)
+        st, ln, hs = self.images.get(rid, (None, None, None))
+        capi.check(self.pkv.pkv_token_keys(ptr(t), len(t), ptr(st) if st is not None else None,
+                                           ptr(ln) if st is not None else None,
+                                           hs.ctypes.data_as(u64p) if st is not None else None,
+                                           0 if st is None else len(st), k.ctypes.data_as(u64p)))
+        return k
+
     def page_hash(self, rid, page_index):
-        t = np.asarray(self.tokens[rid][:(page_index + 1) * self.pt], np.int32)
-        return int(self.pkv.pkv_page_hash(ptr(t), self.pt, page_index))
+        k = self.keys(rid)
+        return int(self.pkv.pkv_page_hash_keys(k.ctypes.data_as(u64p), self.pt, page_index))
 
     def admit(self):
         pkv, pool = self.pkv, self.pool
@@ -84,14 +109,15 @@ class Replay:
             if rid not in self.handle:
                 self.handle[rid] = pkv.pkv_pool_seq_open(pool)
             h = self.handle[rid]
-            toks = np.asarray(self.tokens[rid], np.int32)
+            toks = self.keys(rid)
             limit = (len(toks) - 1) // self.pt
             ok = np.zeros(max(limit, 1), np.uint8)
-            hh = None
-            for i in range(limit):  # a boundary can be resumed only where some sequence saved its state
-                hh = int(pkv.pkv_page_hash(ptr(toks), self.pt, i))
-                ok[i] = hh in self.saved
-            computed = pkv.pkv_pool_match_prefix(pool, h, ptr(toks), len(toks), ok.ctypes.data_as(C.POINTER(C.c_uint8)))
+            blocks = list(zip(*self.images[rid][:2])) if rid in self.images else []
+            for i in range(limit):  # a boundary can be resumed only where some sequence saved its state ...
+                hh = int(pkv.pkv_page_hash_keys(toks.ctypes.data_as(u64p), self.pt, i))
+                b = (i + 1) * self.pt   # ... and never inside a whole image block (engine.cpp:292-296)
+                ok[i] = hh in self.saved and not any(st < b < st + ln for st, ln in blocks)
+            computed = pkv.pkv_pool_match_prefix_keys(pool, h, toks.ctypes.data_as(u64p), len(toks), ok.ctypes.data_as(u8p))
             first = min(len(toks) - computed, self.budget)
             npages = pkv.pkv_pool_seq_pages(pool, h, None, 0)
             need = -(-(computed + first) // self.pt) - npages + len(self.running)
@@ -100,6 +126,7 @@ class Replay:
                 break
             assert pkv.pkv_pool_assign_slot(pool, h) >= 0
             self.computed[rid] = computed
+            self.first_hit.setdefault(rid, computed)
             self.running.append(rid)
             self.waiting.popleft()
 
@@ -141,8 +168,8 @@ class Replay:
                 for seq, slot, s0, cn in chunks:
                     rid, end = int(seq), int(s0 + cn)
                     self.computed[rid] = end
-                    toks = np.asarray(self.tokens[rid], np.int32)
-                    capi.check(pkv.pkv_pool_register(pool, self.handle[rid], ptr(toks), len(toks), end))
+                    toks = self.keys(rid)
+                    capi.check(pkv.pkv_pool_register_keys(pool, self.handle[rid], toks.ctypes.data_as(u64p), len(toks), end))
                     if slot in saves:
                         assert end % self.pt == 0
                         self.saved.add(self.page_hash(rid, end // self.pt - 1))
@@ -243,5 +270,50 @@ def test_prefix_churn_full_size_matches_reference_engine(pkv, refeng):
         assert r.evicted_for_one_request >= num_pages // 4 - 2
         assert r.tables_checked > 1000
         assert pkv.pkv_pool_available(r.pool) == num_pages
+    finally:
+        r.close()
+
+
+def test_image_prompts_match_reference_engine(pkv, refeng):
+    """Prompts that hold image blocks: every image's placeholder tokens are the same ids, so page names come from the
+    image's hash and the offset in the block (engine.cpp:264-270) and a prefix is never resumed inside a block
+    (:292-296). Same placeholder layout with the same image shares pages, with another image it does not; the block
+    tables, prefix-hit lengths and cached-page counts must equal the reference engine's."""
+    g = tl.rng(45)
+    pt = 16
+    r = Replay(pkv, refeng, num_pages=256, page_tokens=pt, slots=4, pps=64, budget=512)
+    try:
+        def prompt(img_hashes, tail):
+            """text, then per image: 40 placeholder tokens (ids 7 7 ... 7) framed by ids 5 and 6, then text."""
+            toks, images = list(range(100, 121)), []
+            for hsh in img_hashes:
+                toks.append(5)
+                images.append((len(toks), 40, hsh))
+                toks += [7] * 40 + [6] + list(range(200, 210))
+            return np.array(toks + list(tail), np.int32), images
+
+        tails = [g.integers(2, 500, size=int(n)).astype(np.int32) for n in (30, 75, 9, 120)]
+        base, base_images = prompt((0xA1, 0xB2), tails[0])
+        ends_in_block, eib_images = prompt((0xE5,), [])
+        ends_in_block = ends_in_block[:64]     # the block covers 22..61: the prompt's last page boundary (48) lies inside it
+        runs = [
+            (base, base_images),                                                  # 0: cold
+            (np.concatenate([base, tails[1]]), base_images),                      # 1: extends 0 with the same images
+            (np.concatenate([base, tails[1]]), [(s_, n_, h_ ^ 0xFF) for s_, n_, h_ in base_images]),   # 2: other images
+            (np.concatenate([base, tails[2]]), [base_images[0], (base_images[1][0], 40, 0xC3)]),       # 3: second differs
+            (ends_in_block, eib_images),                                          # 4: cold; its state is saved before the block
+            (np.concatenate([ends_in_block, tails[3]]), eib_images),              # 5: extends 4
+        ]
+        hits = []
+        for p, images in runs:
+            rid = r.submit(p, 20, images)
+            r.drain()
+            hits.append(r.first_hit[rid])
+        last_boundary = (len(base) - 1) // pt * pt
+        assert hits[0] == 0 and hits[1] == last_boundary        # resumes past both blocks, at the prompt's last boundary
+        assert hits[2] == 0 and hits[3] == 0                    # same token ids, other images: other page names
+        assert hits[4] == 0 and 0 < hits[5] <= eib_images[0][0]  # never resumed inside the block: at or before its start
+        assert r.tables_checked > 10
+        assert pkv.pkv_pool_available(r.pool) == 256
     finally:
         r.close()

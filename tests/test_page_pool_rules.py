@@ -151,6 +151,131 @@ def test_fork_cow_free_lru_compact(pkv):
     pkv.pkv_pool_destroy(pool)
 
 
+def test_cow_never_writes_a_page_the_prefix_cache_names(pkv):
+    """A child forked in the middle of a page whose parent then finishes holds the only reference to a NAMED page.
+    Writing it in place would leave modified rows under the old name; copy-on-write must move the child off it."""
+    pt = 4
+    pool = pkv.pkv_pool_create(8, pt, 4, 8, 1)
+    parent = pkv.pkv_pool_seq_open(pool)
+    toks = np.arange(100, 109, dtype=np.int32)                          # 9 tokens: pages 0, 1 full, page 2 partial
+    assert pkv.pkv_pool_assign_slot(pool, parent) >= 0 and pkv.pkv_pool_alloc(pool, parent, 9) == 1
+    capi.check(pkv.pkv_pool_register(pool, parent, ptr(toks), 9, 9))
+    child = pkv.pkv_pool_fork(pool, parent, 6)                          # shares pages 0 and 1, page 1 only half used
+    assert pkv.pkv_pool_assign_slot(pool, child) >= 0
+    capi.check(pkv.pkv_pool_release(pool, parent))
+    assert list(pages_of(pkv, pool, child)) == [0, 1] and pkv.pkv_pool_page_refs(pool, 1) == 1
+    src, dst = np.zeros(4, np.int32), np.zeros(4, np.int32)
+    assert pkv.pkv_pool_cow_pairs(pool, child, 6, 1) == 1
+    assert pkv.pkv_pool_cow(pool, child, 6, 1, ptr(src), ptr(dst), 4) == 1
+    fresh = int(dst[0])
+    assert int(src[0]) == 1 and fresh not in (0, 1)
+    assert list(pages_of(pkv, pool, child)) == [0, fresh]
+    assert pkv.pkv_pool_page_refs(pool, 1) == 0 and pkv.pkv_pool_page_hash(pool, 1) != 0   # still named, now evictable
+    _, evict = lists(pkv, pool, 8)
+    assert 1 in evict
+    other = pkv.pkv_pool_seq_open(pool)                                 # the parent's prompt again: hits both pages
+    assert pkv.pkv_pool_match_prefix(pool, other, ptr(toks), 9, None) == 8
+    assert list(pages_of(pkv, pool, other)) == [0, 1]                   # ... and page 1 is not the page the child writes
+    assert fresh not in pages_of(pkv, pool, other)
+    check_accounting(pkv, pool, 8, [parent, child, other])
+    assert pkv.pkv_pool_cow(pool, child, 6, 1, ptr(src), ptr(dst), 4) == 0   # the fresh page is private: idempotent
+    pkv.pkv_pool_destroy(pool)
+    # Without a spare page the named page loses its name instead (no copy is possible, none is needed).
+    pool = pkv.pkv_pool_create(2, pt, 4, 8, 1)
+    parent = pkv.pkv_pool_seq_open(pool)
+    toks = np.arange(100, 108, dtype=np.int32)
+    assert pkv.pkv_pool_alloc(pool, parent, 8) == 1
+    capi.check(pkv.pkv_pool_register(pool, parent, ptr(toks), 8, 8))
+    child = pkv.pkv_pool_fork(pool, parent, 6)
+    capi.check(pkv.pkv_pool_release(pool, parent))
+    assert pkv.pkv_pool_available(pool) == 0 and pkv.pkv_pool_cached_count(pool) == 2
+    assert pkv.pkv_pool_cow(pool, child, 6, 1, ptr(src), ptr(dst), 4) == 0
+    assert pkv.pkv_pool_page_hash(pool, 1) == 0 and pkv.pkv_pool_cached_count(pool) == 1
+    other = pkv.pkv_pool_seq_open(pool)
+    assert pkv.pkv_pool_match_prefix(pool, other, ptr(np.append(toks, 1).astype(np.int32)), 9, None) == 4   # page 0 only
+    check_accounting(pkv, pool, 2, [parent, child, other])
+    pkv.pkv_pool_destroy(pool)
+
+
+def test_short_output_arrays_change_nothing(pkv):
+    """compact / cow / migrate with a cap below the pair count (or NULL outputs) return -2 and leave the pool as it
+    was, so the call can be repeated with room; the pair count is available beforehand."""
+    pt = 4
+    pool = pkv.pkv_pool_create(8, pt, 4, 8, 0)
+    a, b = pkv.pkv_pool_seq_open(pool), pkv.pkv_pool_seq_open(pool)
+    for h in (a, b):
+        assert pkv.pkv_pool_assign_slot(pool, h) >= 0 and pkv.pkv_pool_alloc(pool, h, 16) == 1
+    capi.check(pkv.pkv_pool_release(pool, a))                           # pages 0..3 free, b holds 4..7
+    before = list(pages_of(pkv, pool, b))
+    tab = np.ctypeslib.as_array(pkv.pkv_pool_tables(pool), shape=(4, 8)).copy()
+    ms, md = np.zeros(8, np.int32), np.zeros(8, np.int32)
+    assert pkv.pkv_pool_compact_pairs(pool) == 4
+    assert pkv.pkv_pool_compact(pool, ptr(ms), ptr(md), 1) == -2
+    assert pkv.pkv_pool_compact(pool, None, None, 8) == -2
+    assert list(pages_of(pkv, pool, b)) == before
+    assert np.array_equal(np.ctypeslib.as_array(pkv.pkv_pool_tables(pool), shape=(4, 8)), tab)
+    assert pkv.pkv_pool_compact(pool, ptr(ms), ptr(md), 8) == 4          # the retry emits every move
+    assert list(ms[:4]) == before and list(md[:4]) == [0, 1, 2, 3]
+    assert list(pages_of(pkv, pool, b)) == [0, 1, 2, 3]
+    # cow
+    c = pkv.pkv_pool_fork(pool, b, 16)
+    assert pkv.pkv_pool_cow_pairs(pool, c, 0, 16) == 4
+    assert pkv.pkv_pool_cow(pool, c, 0, 16, ptr(ms), ptr(md), 3) == -2
+    assert list(pages_of(pkv, pool, c)) == [0, 1, 2, 3] and pkv.pkv_pool_page_refs(pool, 0) == 2
+    assert pkv.pkv_pool_cow(pool, c, 0, 16, ptr(ms), ptr(md), 4) == 4
+    # migrate
+    dst = pkv.pkv_pool_create(8, pt, 4, 8, 0)
+    out = C.c_int(-1)
+    assert pkv.pkv_pool_migrate(pool, c, dst, C.byref(out), ptr(ms), ptr(md), 3) == -2
+    assert pkv.pkv_pool_migrate(pool, c, dst, C.byref(out), None, None, 8) == -2
+    assert len(pages_of(pkv, pool, c)) == 4 and pkv.pkv_pool_available(dst) == 8
+    assert pkv.pkv_pool_migrate(pool, c, dst, C.byref(out), ptr(ms), ptr(md), 4) == 4
+    pkv.pkv_pool_destroy(pool)
+    pkv.pkv_pool_destroy(dst)
+
+
+def test_image_positions_are_named_by_image_hash_and_offset(pkv):
+    """token_key of src/engine/engine.cpp:264-270: inside an image block a position's key is mix64(hash + offset), so
+    two prompts with the same placeholder tokens but different images do not share pages, and the same image does."""
+    u64p = C.POINTER(C.c_uint64)
+    pt = 4
+    toks = np.array([5, 6, 9, 9, 9, 9, 9, 9, 7, 8, 3, 4, 2], np.int32)   # an image block of six placeholder tokens at 2
+    starts, lens = np.array([2], np.int32), np.array([6], np.int32)
+
+    def mix64(x):
+        m = (1 << 64) - 1
+        x = ((x ^ (x >> 30)) * 0xbf58476d1ce4e5b9) & m
+        x = ((x ^ (x >> 27)) * 0x94d049bb133111eb) & m
+        return x ^ (x >> 31)
+
+    def keys_for(h):
+        k = np.zeros(len(toks), np.uint64)
+        capi.check(pkv.pkv_token_keys(ptr(toks), len(toks), ptr(starts), ptr(lens), np.array([h], np.uint64).ctypes.data_as(u64p), 1,
+                                      k.ctypes.data_as(u64p)))
+        return k
+
+    ka, kb = keys_for(0x1234), keys_for(0x9999)
+    assert list(ka[:2]) == [5, 6] and list(ka[8:]) == [7, 8, 3, 4, 2]
+    assert [int(x) for x in ka[2:8]] == [mix64((0x1234 + i) & ((1 << 64) - 1)) for i in range(6)]
+    text = np.zeros(len(toks), np.uint64)
+    capi.check(pkv.pkv_token_keys(ptr(toks), len(toks), None, None, None, 0, text.ctypes.data_as(u64p)))
+    assert [int(x) for x in text] == [int(t) for t in toks]
+    assert pkv.pkv_page_hash_keys(text.ctypes.data_as(u64p), pt, 2) == pkv.pkv_page_hash(ptr(toks), pt, 2)
+    pool = pkv.pkv_pool_create(16, pt, 4, 8, 1)
+    h = pkv.pkv_pool_seq_open(pool)
+    assert pkv.pkv_pool_alloc(pool, h, len(toks)) == 1
+    capi.check(pkv.pkv_pool_register_keys(pool, h, ka.ctypes.data_as(u64p), len(toks), len(toks)))
+    assert pkv.pkv_pool_page_hash(pool, 1) == pkv.pkv_page_hash_keys(ka.ctypes.data_as(u64p), pt, 1)
+    same, other, plain = (pkv.pkv_pool_seq_open(pool) for _ in range(3))
+    assert pkv.pkv_pool_match_prefix_keys(pool, same, ka.ctypes.data_as(u64p), len(toks), None) == 12
+    assert pkv.pkv_pool_match_prefix_keys(pool, other, kb.ctypes.data_as(u64p), len(toks), None) == 0
+    assert pkv.pkv_pool_match_prefix(pool, plain, ptr(toks), len(toks), None) == 0
+    ok = np.array([1, 0, 1], np.uint8)                                  # "never resume inside a whole image block"
+    capi.check(pkv.pkv_pool_release(pool, same))
+    assert pkv.pkv_pool_match_prefix_keys(pool, same, ka.ctypes.data_as(u64p), len(toks), ok.ctypes.data_as(C.POINTER(C.c_uint8))) == 12
+    pkv.pkv_pool_destroy(pool)
+
+
 def test_migrate_between_pools(pkv):
     a = pkv.pkv_pool_create(32, 8, 4, 16, 1)
     b = pkv.pkv_pool_create(32, 8, 4, 16, 1)

@@ -94,12 +94,18 @@ _SIGS = {
     "pkv_pool_seq_open": (_i, [_vp]),
     "pkv_pool_seq_close": (_i, [_vp, _i]),
     "pkv_pool_match_prefix": (_i, [_vp, _i, c_i32p, _i, c_u8p]),
+    "pkv_token_keys": (_i, [c_i32p, _i, c_i32p, c_i32p, C.POINTER(C.c_uint64), _i, C.POINTER(C.c_uint64)]),
+    "pkv_pool_match_prefix_keys": (_i, [_vp, _i, C.POINTER(C.c_uint64), _i, c_u8p]),
+    "pkv_pool_register_keys": (_i, [_vp, _i, C.POINTER(C.c_uint64), _i, _i]),
+    "pkv_page_hash_keys": (C.c_uint64, [C.POINTER(C.c_uint64), _i, _i]),
     "pkv_pool_assign_slot": (_i, [_vp, _i]),
     "pkv_pool_alloc": (_i, [_vp, _i, _i]),
     "pkv_pool_register": (_i, [_vp, _i, c_i32p, _i, _i]),
     "pkv_pool_release": (_i, [_vp, _i]),
     "pkv_pool_fork": (_i, [_vp, _i, _i]),
     "pkv_pool_cow": (_i, [_vp, _i, _i, _i, c_i32p, c_i32p, _i]),
+    "pkv_pool_cow_pairs": (_i, [_vp, _i, _i, _i]),
+    "pkv_pool_compact_pairs": (_i, [_vp]),
     "pkv_pool_free_lru": (_i, [_vp, _i, c_i32p, _i]),
     "pkv_pool_compact": (_i, [_vp, c_i32p, c_i32p, _i]),
     "pkv_pool_migrate": (_i, [_vp, _i, _vp, C.POINTER(C.c_int), c_i32p, c_i32p, _i]),

@@ -27,6 +27,19 @@ uint64_t chain_page_hash(uint64_t prev, const int32_t* tokens, int page_tokens) 
   return h;
 }
 
+uint64_t chain_page_hash_keys(uint64_t prev, const uint64_t* keys, int page_tokens) {
+  uint64_t h = prev;
+  for (int i = 0; i < page_tokens; ++i) h = mix64(h + 0x9e3779b97f4a7c15ull + keys[i]);
+  return h;
+}
+
+void token_keys(const int32_t* tokens, int n, const int32_t* starts, const int32_t* lens, const uint64_t* hashes, int nimages,
+                uint64_t* keys_out) {
+  for (int p = 0; p < n; ++p) keys_out[p] = uint64_t(uint32_t(tokens[p]));
+  for (int i = nimages - 1; i >= 0; --i)  // earlier blocks overwrite later ones: the first match wins
+    for (int p = std::max(starts[i], 0); p < starts[i] + lens[i] && p < n; ++p) keys_out[p] = mix64(hashes[i] + uint64_t(p - starts[i]));
+}
+
 PagePool::PagePool(int num_pages, int page_tokens, int max_slots, int max_pages_per_seq, bool prefix_cache)
     : page_tokens_(page_tokens), max_slots_(max_slots), width_(max_pages_per_seq), cache_on_(prefix_cache) {
   info_.resize(size_t(num_pages));
@@ -108,14 +121,15 @@ void PagePool::close(int seq) {
   free_handles_.push_back(seq);
 }
 
-void PagePool::hash_upto(Seq& s, const int32_t* tokens, int npages) {
+void PagePool::hash_upto(Seq& s, Keys k, int npages) {
   while (int(s.hashes.size()) < npages) {
-    const size_t i = s.hashes.size();
-    s.hashes.push_back(chain_page_hash(i ? s.hashes.back() : kHashSeed, tokens + i * size_t(page_tokens_), page_tokens_));
+    const size_t i = s.hashes.size(), at = i * size_t(page_tokens_);
+    const uint64_t prev = i ? s.hashes.back() : kHashSeed;
+    s.hashes.push_back(k.keys ? chain_page_hash_keys(prev, k.keys + at, page_tokens_) : chain_page_hash(prev, k.tokens + at, page_tokens_));
   }
 }
 
-int PagePool::match_prefix(int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok) {
+int PagePool::match_prefix(int seq, Keys tokens, int ntokens, const uint8_t* boundary_ok) {
   Seq& s = seqs_[size_t(seq)];
   const int limit = (ntokens - 1) / page_tokens_;  // the last token is always computed
   if (!cache_on_ || limit <= 0 || !s.pages.empty()) return 0;
@@ -156,7 +170,7 @@ bool PagePool::alloc(int seq, int upto) {
   return true;
 }
 
-void PagePool::register_pages(int seq, const int32_t* tokens, int ntokens, int done_pos) {
+void PagePool::register_pages(int seq, Keys tokens, int ntokens, int done_pos) {
   Seq& s = seqs_[size_t(seq)];
   if (!cache_on_) return;
   const int full = std::min({done_pos / page_tokens_, int(s.pages.size()), ntokens / page_tokens_});
@@ -205,26 +219,57 @@ int PagePool::fork(int from, int ntokens) {
   return child;
 }
 
-// Copy-on-write: pages of `seq` that rows [s0, s0 + n) touch and that another sequence also references are replaced
-// by fresh pages; the caller copies the payload of each (old, fresh) pair before writing.
-int PagePool::cow(int seq, int s0, int n, std::vector<std::pair<int32_t, int32_t>>& moves) {
-  Seq& s = seqs_[size_t(seq)];
+void PagePool::unname(Page& pg) {
+  by_hash_.erase(pg.hash);
+  pg.cached = false;
+  pg.hash = 0;
+}
+
+// Copy-on-write: a page of `seq` that rows [s0, s0 + n) touch is not privately writable when another sequence also
+// references it (refs > 1) or when the prefix cache names it (a later match_prefix would share the modified page under
+// the old name). Such a page is replaced by a fresh one and the caller copies the payload of each (old, fresh) pair
+// before writing; the old page keeps its name and, when this was its last reference, becomes evictable. A named page
+// held only by this sequence is written in place after losing its name when the pool has no page to spare.
+int PagePool::cow_pairs(int seq, int s0, int n) const {
+  const Seq& s = seqs_[size_t(seq)];
   if (n <= 0) return 0;
   const int first = s0 / page_tokens_, last = std::min((s0 + n - 1) / page_tokens_, int(s.pages.size()) - 1);
-  int need = 0;
-  for (int i = first; i <= last; ++i) need += info_[size_t(s.pages[size_t(i)])].refs > 1;
-  if (need > available()) return -1;
+  int avail = available(), pairs = 0;
+  for (int i = first; i <= last; ++i) {
+    const Page& pg = info_[size_t(s.pages[size_t(i)])];
+    if (pg.refs > 1) {
+      if (avail-- <= 0) return -1;
+      ++pairs;
+    } else if (pg.cached && avail > 0) {
+      ++pairs;  // takes one page and makes one evictable
+    }
+  }
+  return pairs;
+}
+
+int PagePool::cow(int seq, int s0, int n, std::vector<std::pair<int32_t, int32_t>>& moves) {
+  if (n <= 0) return 0;
+  if (cow_pairs(seq, s0, n) < 0) return -1;
+  Seq& s = seqs_[size_t(seq)];
+  const int first = s0 / page_tokens_, last = std::min((s0 + n - 1) / page_tokens_, int(s.pages.size()) - 1);
+  bool touched = false;
   for (int i = first; i <= last; ++i) {
     const int32_t old = s.pages[size_t(i)];
-    if (info_[size_t(old)].refs <= 1) continue;
+    Page& pg = info_[size_t(old)];
+    if (pg.refs <= 1 && !pg.cached) continue;
+    if (i < s.registered) s.registered = i;  // the private page is unnamed until registered again
+    if (pg.refs <= 1 && available() <= 0) {
+      unname(pg);
+      continue;
+    }
     const int32_t fresh = take_page();
-    --info_[size_t(old)].refs;
+    if (--info_[size_t(old)].refs == 0) lru_push_back(old);  // (only a named page gets here with one reference)
     s.pages[size_t(i)] = fresh;
-    if (i < s.registered) s.registered = i;  // the private copy is unnamed until registered again
     moves.emplace_back(old, fresh);
+    touched = true;
   }
-  if (need) write_table(s);
-  return need;
+  if (touched) write_table(s);
+  return int(moves.size());
 }
 
 // The evict branch of take_page applied `count` times, with the page going to the free list instead of to a caller.
@@ -233,15 +278,19 @@ int PagePool::free_lru(int count, std::vector<int32_t>& freed) {
   while (done < count && lru_head_ >= 0) {
     const int32_t p = lru_head_;
     lru_unlink(p);
-    Page& pg = info_[size_t(p)];
-    by_hash_.erase(pg.hash);
-    pg.cached = false;
-    pg.hash = 0;
+    unname(info_[size_t(p)]);
     free_.push_back(p);
     freed.push_back(p);
     ++done;
   }
   return done;
+}
+
+int PagePool::compact_pairs() const {
+  const int N = num_pages(), W = N - int(free_.size());
+  int holes = 0;
+  for (const int32_t p : free_) holes += p < W;
+  return holes;  // every hole below W is filled by exactly one live page at or above W
 }
 
 // Hole filling: with W live pages, every live id >= W moves into a free id < W (both ascending, paired in order).
@@ -316,6 +365,7 @@ struct pkv_pool {
 };
 
 namespace {
+// Every caller has checked `cap` and the pointers against the pair count BEFORE changing the pool.
 int emit(const std::vector<std::pair<int32_t, int32_t>>& moves, int32_t* src_out, int32_t* dst_out, int cap) {
   if (int(moves.size()) > cap || ((!src_out || !dst_out) && !moves.empty())) return -2;
   for (size_t i = 0; i < moves.size(); ++i) {
@@ -349,6 +399,26 @@ int pkv_pool_match_prefix(pkv_pool* p, int seq, const int32_t* tokens, int ntoke
   if (!p || !p->impl.valid(seq) || (!tokens && ntokens > 0)) return -1;
   return p->impl.match_prefix(seq, tokens, ntokens, boundary_ok);
 }
+int pkv_pool_match_prefix_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, const uint8_t* boundary_ok) {
+  if (!p || !p->impl.valid(seq) || (!keys && nkeys > 0)) return -1;
+  return p->impl.match_prefix(seq, pkv::PagePool::Keys{nullptr, keys}, nkeys, boundary_ok);
+}
+int pkv_pool_register_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, int done_pos) {
+  if (!p || !p->impl.valid(seq) || (!keys && nkeys > 0)) return PKV_ERR_ARG;
+  p->impl.register_pages(seq, pkv::PagePool::Keys{nullptr, keys}, nkeys, done_pos);
+  return PKV_OK;
+}
+int pkv_token_keys(const int32_t* tokens, int n, const int32_t* starts, const int32_t* lens, const uint64_t* hashes, int nimages,
+                   uint64_t* keys_out) {
+  if (n < 0 || nimages < 0 || (n > 0 && (!tokens || !keys_out)) || (nimages > 0 && (!starts || !lens || !hashes))) return PKV_ERR_ARG;
+  pkv::token_keys(tokens, n, starts, lens, hashes, nimages, keys_out);
+  return PKV_OK;
+}
+uint64_t pkv_page_hash_keys(const uint64_t* keys, int page_tokens, int page_index) {
+  uint64_t h = pkv::kHashSeed;
+  for (int i = 0; i <= page_index; ++i) h = pkv::chain_page_hash_keys(h, keys + size_t(i) * size_t(page_tokens), page_tokens);
+  return h;
+}
 int pkv_pool_assign_slot(pkv_pool* p, int seq) { return p && p->impl.valid(seq) ? p->impl.assign_slot(seq) : -1; }
 int pkv_pool_alloc(pkv_pool* p, int seq, int upto) { return p && p->impl.valid(seq) && p->impl.alloc(seq, upto) ? 1 : 0; }
 int pkv_pool_register(pkv_pool* p, int seq, const int32_t* tokens, int ntokens, int done_pos) {
@@ -367,10 +437,17 @@ int pkv_pool_fork(pkv_pool* p, int from, int ntokens) {
 }
 int pkv_pool_cow(pkv_pool* p, int seq, int s0, int n, int32_t* src_out, int32_t* dst_out, int cap) {
   if (!p || !p->impl.valid(seq) || s0 < 0) return -1;
+  const int pairs = p->impl.cow_pairs(seq, s0, n);
+  if (pairs < 0) return -1;
+  if (pairs > cap || (pairs > 0 && (!src_out || !dst_out))) return -2;  // nothing has changed
   std::vector<std::pair<int32_t, int32_t>> moves;
   if (p->impl.cow(seq, s0, n, moves) < 0) return -1;
   return emit(moves, src_out, dst_out, cap);
 }
+int pkv_pool_cow_pairs(const pkv_pool* p, int seq, int s0, int n) {
+  return p && p->impl.valid(seq) && s0 >= 0 ? p->impl.cow_pairs(seq, s0, n) : -1;
+}
+int pkv_pool_compact_pairs(const pkv_pool* p) { return p ? p->impl.compact_pairs() : -1; }
 int pkv_pool_free_lru(pkv_pool* p, int count, int32_t* freed_out, int cap) {
   if (!p) return -1;
   std::vector<int32_t> freed;
@@ -380,13 +457,16 @@ int pkv_pool_free_lru(pkv_pool* p, int count, int32_t* freed_out, int cap) {
 }
 int pkv_pool_compact(pkv_pool* p, int32_t* src_out, int32_t* dst_out, int cap) {
   if (!p) return -1;
+  const int pairs = p->impl.compact_pairs();
+  if (pairs > cap || (pairs > 0 && (!src_out || !dst_out))) return -2;  // nothing has changed
   std::vector<std::pair<int32_t, int32_t>> moves;
   p->impl.compact(moves);
   return emit(moves, src_out, dst_out, cap);
 }
 int pkv_pool_migrate(pkv_pool* src, int seq, pkv_pool* dst, int* seq_out, int32_t* src_out, int32_t* dst_out, int cap) {
   if (!src || !dst || !seq_out || !src->impl.valid(seq)) return -1;
-  if (int(src->impl.pages(seq).size()) > cap) return -2;
+  const int pairs = int(src->impl.pages(seq).size());
+  if (pairs > cap || (pairs > 0 && (!src_out || !dst_out))) return -2;  // nothing has changed
   std::vector<std::pair<int32_t, int32_t>> moves;
   const int h = pkv::PagePool::migrate(src->impl, seq, dst->impl, moves);
   if (h < 0) return -1;

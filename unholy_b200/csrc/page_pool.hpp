@@ -26,6 +26,12 @@ namespace pkv {
 uint64_t mix64(uint64_t x);
 // Name of page `index` given the previous page's name (or the chain seed for index 0) and the page's tokens.
 uint64_t chain_page_hash(uint64_t prev, const int32_t* tokens, int page_tokens);
+uint64_t chain_page_hash_keys(uint64_t prev, const uint64_t* keys, int page_tokens);
+// token_key of src/engine/engine.cpp:264-270 for every position of a sequence: uint32(token), or for positions inside
+// image block i (starts[i] <= p < starts[i] + lens[i]) mix64(hashes[i] + (p - starts[i])); the first block that holds
+// the position wins, as in the reference's loop.
+void token_keys(const int32_t* tokens, int n, const int32_t* starts, const int32_t* lens, const uint64_t* hashes, int nimages,
+                uint64_t* keys_out);
 constexpr uint64_t kHashSeed = 0x243f6a8885a308d3ull;
 
 class PagePool {
@@ -44,15 +50,32 @@ class PagePool {
   int open();
   void close(int seq);
   bool valid(int seq) const { return seq >= 0 && seq < int(seqs_.size()) && seqs_[size_t(seq)].open; }
-  int match_prefix(int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok);
+  // A sequence's positions are named either by token ids (key = uint32(token), the text rule) or by 64-bit keys the
+  // caller computed (token_keys(): image positions are named by the image's hash and the offset in the block,
+  // src/engine/engine.cpp:264-270). Exactly one of the two pointers is non-null.
+  struct Keys {
+    const int32_t* tokens = nullptr;
+    const uint64_t* keys = nullptr;
+    uint64_t at(size_t i) const { return keys ? keys[i] : uint64_t(uint32_t(tokens[i])); }
+  };
+  int match_prefix(int seq, Keys k, int ntokens, const uint8_t* boundary_ok);
+  int match_prefix(int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok) {
+    return match_prefix(seq, Keys{tokens, nullptr}, ntokens, boundary_ok);
+  }
   int assign_slot(int seq);
   bool alloc(int seq, int upto);
-  void register_pages(int seq, const int32_t* tokens, int ntokens, int done_pos);
+  void register_pages(int seq, Keys k, int ntokens, int done_pos);
+  void register_pages(int seq, const int32_t* tokens, int ntokens, int done_pos) {
+    register_pages(seq, Keys{tokens, nullptr}, ntokens, done_pos);
+  }
   void release(int seq);
 
   int fork(int from, int ntokens);
+  // cow_pairs / compact_pairs: how many (source, destination) pairs the call would emit now; nothing changes.
+  int cow_pairs(int seq, int s0, int n) const;
   int cow(int seq, int s0, int n, std::vector<std::pair<int32_t, int32_t>>& moves);
   int free_lru(int count, std::vector<int32_t>& freed);
+  int compact_pairs() const;
   int compact(std::vector<std::pair<int32_t, int32_t>>& moves);
   static int migrate(PagePool& src, int seq, PagePool& dst, std::vector<std::pair<int32_t, int32_t>>& moves);
 
@@ -87,7 +110,8 @@ class PagePool {
   };
   int32_t take_page();
   void write_table(const Seq& s);
-  void hash_upto(Seq& s, const int32_t* tokens, int npages);
+  void hash_upto(Seq& s, Keys k, int npages);
+  void unname(Page& pg);
   void lru_push_back(int32_t p);
   void lru_unlink(int32_t p);
   void unref(Seq& s);
