@@ -195,7 +195,7 @@ class Workload:
         st = capi.PkvStep()
         st.width = st.row_stride = W
         st.rows_per_page, st.max_pages_per_seq, st.num_pages, st.fp8_block = RPP, self.pps, self.num_pages, 64
-        st.nchunks = st.T = st.Q = NSEQ
+        st.nchunks = st.T = st.Q = st.max_slots = NSEQ
         st.k = K_SEL
         st.tables, st.chunks = t["tables"].data_ptr(), t["chunks"].data_ptr()
         st.q_chunk, st.q_visible = t["q_chunk"].data_ptr(), t["q_visible"].data_ptr()
@@ -576,7 +576,7 @@ def run_prefill(args):
     step = capi.PkvStep()
     step.width = step.row_stride = W
     step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pages, pages, 64
-    step.nchunks, step.T, step.Q, step.k = 1, chunk, 8, K_SEL
+    step.nchunks, step.T, step.Q, step.k, step.max_slots = 1, chunk, 8, K_SEL, 1
     step.tables, step.q_chunk = perm.data_ptr(), q_chunk.data_ptr()
     layers = (capi.PkvLayer * LAYERS)()
     for l in range(LAYERS):
@@ -665,7 +665,7 @@ def run_churn(args):
     step = capi.PkvStep()
     step.width = step.row_stride = W
     step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
-    step.tables = d_tables.data_ptr()
+    step.tables, step.max_slots = d_tables.data_ptr(), slots
     timers = {}
 
     def timed(name, fn, nbytes):
@@ -897,7 +897,7 @@ def run_sharded(args):
     step = capi.PkvStep()
     step.width = step.row_stride = W
     step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
-    step.k = K_SEL
+    step.k, step.max_slots = K_SEL, slots
     step.tables = d_tables.data_ptr()
     layers = (capi.PkvLayer * L)()
     lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(L)]
@@ -1211,7 +1211,7 @@ def run_gather_fp8(args):
     idx_b[:, -5:] = -1
     step = capi.PkvStep()
     step.width, step.row_stride, step.rows_per_page, step.max_pages_per_seq, step.num_pages = width, width, rpp, pps, pages
-    step.fp8_block, step.nchunks, step.T, step.Q, step.k = block, T, T, T, k
+    step.fp8_block, step.nchunks, step.T, step.Q, step.k, step.max_slots = block, T, T, T, k, T
     step.tables, step.chunks, step.q_chunk, step.q_visible = (tables.data_ptr(), chunks.data_ptr(), q_chunk.data_ptr(),
                                                               vis_b.data_ptr())
     out_b = torch.empty_like(out)

@@ -52,9 +52,14 @@ PKV_API int pkv_abi_version(void);
 PKV_API int pkv_tune(int knob, int value);
 
 /* First failed device-side check since the last call (0 = none): bit 0..7 = kind (1 page id out of range,
- * 2 chunk row out of range, 3 bounded wait gave up), the rest = an index identifying the entry. Synchronises the
- * device. The kernels skip the offending access instead of faulting. */
+ * 2 chunk row, chunk index or slot out of range, 3 bounded wait gave up), the rest = an index identifying the entry.
+ * Synchronises the device. The kernels skip the offending access instead of faulting. Kernels that can report: the
+ * step kernels (pkv_step_run, pkv_step_gather_fp8*) and pkv_copy_pages; the others take no ids from device memory
+ * that the host has not already checked. */
 PKV_API int pkv_device_status(int* status_out);
+/* The same check as an error code, ordered after the work queued on `stream` so far: waits for that stream only,
+ * returns PKV_OK, or PKV_ERR_DEVICE with the kind and index in pkv_last_error() (and clears the record). */
+PKV_API int pkv_stream_check(pkv_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------------------------
  * Reference-shaped single-sequence entry points. `table` is ONE slot's row of the block table (device).
@@ -152,9 +157,12 @@ typedef struct pkv_step {
   int32_t T;                 /* batch rows */
   int32_t Q;                 /* query rows */
   int32_t k;                 /* index-list width */
+  int32_t max_slots;         /* block-table rows; a chunk's slot outside [0, max_slots) is reported, not dereferenced */
+  int32_t reserved;          /* 0 */
   const int32_t* tables;     /* device [max_slots][max_pages_per_seq] (src/engine/step.hpp:100) */
   const pkv_chunk* chunks;   /* device [nchunks] */
-  const int32_t* q_chunk;    /* device [Q]: index into chunks of the chunk the query row belongs to */
+  const int32_t* q_chunk;    /* device [Q]: index into chunks of the chunk the query row belongs to (outside
+                                [0, nchunks): reported, the query's rows are zeros) */
   const int32_t* q_visible;  /* device [Q]: logical rows visible to the query (row >= visible is masked) */
 } pkv_step;
 
@@ -198,13 +206,16 @@ PKV_API int pkv_step_gather_fp8_pools(const pkv_step* step, const uint8_t* codes
  * Index-list producer (the step before the gather).
  * ---------------------------------------------------------------------------------------------------------------- */
 
-/* topk_bf16 / topk_bf16_batch with scratch — src/kernels/indexer.hpp:74-94, src/kernels/indexer.hip:408-560,878-902.
+/* topk_bf16 / topk_bf16_batch — src/kernels/indexer.hpp:74-94, src/kernels/indexer.hip:408-560,878-902.
  * scores device bf16 [T][ld] (n <= ld keys per row); idx device int32 [T][k]: per row the min(k, #valid) largest
  * scores ordered (score descending, index ascending), ties at the threshold to the lowest indices, -1 padded; -inf is
- * never selected. k <= 4096. Rows are split over several CTAs; `scratch` is device memory of at least
- * pkv_topk_scratch_words(T, n, k) uint32 words, 8-byte aligned (the reference's topk_split_scratch_words). Its
- * contents need not be initialised (the call clears the few words that must start at zero with a memset on the
- * stream) and are garbage afterwards; two calls that overlap on the GPU must not share it. */
+ * never selected. k <= 4096. As in the reference, `scratch` is OPTIONAL (NULL / 0 words allowed): shapes with
+ * k <= 2048 and n <= 655,360 run as one launch of thread-block clusters that needs none. Other shapes (and pkv_tune
+ * knob 7 = 1) run as four launches through pkv_topk_scratch_words(T, n, k) uint32 words: the caller's `scratch` when it
+ * is 8-byte aligned and large enough (its contents need not be initialised and are garbage afterwards; two calls that
+ * overlap on the GPU must not share it), else the library's built-in 4 MiB array (pkv_topk_bf16_static's: calls that
+ * land there must not overlap on the GPU, and the first such call per device should come before any stream capture),
+ * else PKV_ERR_LIMIT with the word count in the message. */
 PKV_API size_t pkv_topk_scratch_words(int T, int n, int k);
 PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                           size_t scratch_words, pkv_stream_t stream);
@@ -213,7 +224,7 @@ PKV_API int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, in
  * score blocks in one call (the decode chunks of a step): group g's rows [rows][n] start at scores + off (elements),
  * its index lists [rows][k] at idx + idx_off (elements); per row the same result as pkv_topk_bf16. All groups run in
  * one launch of thread-block clusters (32 groups per launch) when every group has k <= 2048 and n <= 655,360; else one
- * after the other on the stream, sharing `scratch` (at least pkv_topk_batch_scratch_words words). */
+ * after the other on the stream, sharing `scratch` (pkv_topk_batch_scratch_words words; optional as for pkv_topk_bf16). */
 typedef struct pkv_topk_group {
   size_t off;
   int32_t rows, n, k, idx_off;

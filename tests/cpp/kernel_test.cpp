@@ -147,6 +147,67 @@ int main() {
     std::printf("topk_rows k > 1024 throws: %s\n", threw ? "yes" : "NO");
     fails += !threw;
   }
+  // ---- topk_bf16 / topk_bf16_batch with the reference's signatures (src/kernels/indexer.hpp:74-94), called the way
+  //      src/model/forward_ref.hip:890-935 calls them: score blocks of several chunks in one buffer, the rest of the
+  //      buffer (possibly very little) offered as scratch; and without any scratch at all ----
+  {
+    const int n0 = 9000, n1 = 700, kk = 512, rows0 = 3, rows1 = 5;
+    std::vector<uint16_t> sc(size_t(rows0) * n0 + size_t(rows1) * n1 + 64);
+    for (auto& v : sc) v = to_bf16(float(int(rng() % 2001) - 1000) * 0.125f);   // many ties
+    Dev<uint16_t> d_sc(sc.size());
+    d_sc.up(sc);
+    Dev<int32_t> d_idx(size_t(rows0 + rows1) * kk), d_one(size_t(rows0) * kk);
+    k::TopkBatch tb;
+    tb.g[tb.ngroups++] = {0, rows0, n0, kk, 0};
+    tb.g[tb.ngroups++] = {size_t(rows0) * n0, rows1, n1, kk, rows0 * kk};
+    const size_t used = size_t(rows0) * n0 + size_t(rows1) * n1;
+    k::topk_bf16_batch(d_sc.p, tb, d_idx.p, nullptr, reinterpret_cast<uint32_t*>(d_sc.p + used), (sc.size() - used) / 2);  // 32 words
+    k::topk_bf16(d_sc.p, rows0, n0, kk, d_one.p, nullptr);
+    CK(cudaDeviceSynchronize());
+    const auto got = d_idx.down(), one = d_one.down();
+    auto f = [](uint16_t b) {
+      uint32_t u = uint32_t(b) << 16;
+      float x;
+      std::memcpy(&x, &u, 4);
+      return x;
+    };
+    size_t diff = 0;
+    for (int gi = 0; gi < 2; ++gi) {
+      const int rows = gi ? rows1 : rows0, n = gi ? n1 : n0;
+      const uint16_t* base = sc.data() + (gi ? size_t(rows0) * n0 : 0);
+      std::vector<int32_t> order(static_cast<size_t>(n));
+      for (int t = 0; t < rows; ++t) {
+        std::iota(order.begin(), order.end(), 0);
+        const uint16_t* row = base + size_t(t) * n;
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return f(row[x]) > f(row[y]); });
+        for (int e = 0; e < kk; ++e) {
+          const int32_t want = e < n ? order[size_t(e)] : -1;
+          diff += got[(gi ? size_t(rows0) * kk : 0) + size_t(t) * kk + e] != want;
+          if (!gi) diff += one[size_t(t) * kk + e] != want;
+        }
+      }
+    }
+    std::printf("topk_bf16 / topk_bf16_batch (reference signatures, 32 words of scratch): %zu entries differ\n", diff);
+    fails += diff != 0;
+    // the four-launch path without caller scratch falls back to the library's own; a shape too large for it throws
+    pkv_tune(7, 1);
+    k::topk_bf16(d_sc.p, rows0, n0, kk, d_one.p, nullptr);
+    CK(cudaDeviceSynchronize());
+    const auto again = d_one.down();
+    size_t d2 = 0;
+    for (size_t i = 0; i < again.size(); ++i) d2 += again[i] != one[i];
+    std::printf("topk_bf16 through the built-in scratch: %zu entries differ\n", d2);
+    fails += d2 != 0;
+    bool threw = false;
+    try {
+      k::topk_bf16(d_sc.p, 4096, 2, 4096, d_one.p, nullptr);   // needs far more scratch than the built-in array holds
+    } catch (const std::runtime_error& e) {
+      threw = std::strstr(e.what(), "scratch") != nullptr;
+    }
+    pkv_tune(7, 0);
+    std::printf("top-k beyond the built-in scratch throws: %s\n", threw ? "yes" : "NO");
+    fails += !threw;
+  }
   // ---- errors are exceptions ----
   {
     bool threw = false;

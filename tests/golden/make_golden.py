@@ -1,5 +1,7 @@
 """Generates tests/golden/quant_golden.npz from the reference's own pure-torch quantisers
-(tools/ref/oracle/kernel.py: act_quant, fp4_act_quant), imported from the reference checkout.
+(tools/ref/oracle/kernel.py: act_quant, fp4_act_quant) and tests/golden/hadamard_golden.npz from its matrix-form
+Hadamard transform (tools/ref/oracle/fast_hadamard_transform.py: x.float() @ H, scaled, back to bf16), both imported
+from the reference checkout.
 
     python tests/golden/make_golden.py [/path/to/reference]
 
@@ -15,6 +17,7 @@ import torch
 
 ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
 sys.path.insert(0, str(ref / "tools" / "ref" / "oracle"))
+import fast_hadamard_transform as ref_hadamard  # noqa: E402  (the reference's module)
 import kernel as ref_kernel  # noqa: E402  (the reference's module)
 
 
@@ -57,6 +60,17 @@ def main():
     dst = Path(__file__).resolve().parent / "quant_golden.npz"
     np.savez_compressed(dst, **out)
     print(dst, {k: v.shape for k, v in list(out.items())[:4]}, dst.stat().st_size)
+    # hadamard128: 96 segments of 128 values (N(0,1), per-row octaves, a zero row, a one-hot row)
+    g = torch.Generator().manual_seed(20261126)
+    x = torch.randn(96, 128, generator=g) * torch.ldexp(torch.ones(96, 1), torch.randint(-6, 7, (96, 1), generator=g))
+    x[0] = 0.0
+    x[1] = 0.0
+    x[1, 77] = 3.0
+    x = x.to(torch.bfloat16)
+    y = ref_hadamard.hadamard_transform(x, scale=128 ** -0.5)
+    dst = Path(__file__).resolve().parent / "hadamard_golden.npz"
+    np.savez_compressed(dst, x=bits(x), y=bits(y))
+    print(dst, dst.stat().st_size)
 
 
 if __name__ == "__main__":

@@ -112,6 +112,7 @@ def make_step(case, d_tables, d_chunks, d_qchunk, d_qvis, T=None, Q=None, fp8_bl
     st = capi.PkvStep()
     st.width, st.row_stride, st.rows_per_page = case.width, case.row_stride, case.rpp
     st.max_pages_per_seq, st.num_pages, st.fp8_block = case.pps, case.num_pages, fp8_block
+    st.max_slots = case.tables.shape[0]
     st.nchunks, st.T = case.chunks.shape[0], case.T if T is None else T
     st.Q, st.k = (case.idx.shape[0] if Q is None else Q), case.k
     st.tables, st.chunks = d_tables.data_ptr(), d_chunks.data_ptr()

@@ -25,13 +25,13 @@ def test_every_declared_symbol_is_exported_and_bound(pkv):
 def test_struct_layouts_match_the_header():
     assert C.sizeof(capi.PkvChunk) == 16
     assert C.sizeof(capi.PkvLayer) == 64
-    assert C.sizeof(capi.PkvStep) == 72
+    assert C.sizeof(capi.PkvStep) == 80
     assert C.sizeof(capi.PkvPoolDesc) == 24
-    assert capi.PkvStep.tables.offset == 40 and capi.PkvStep.q_visible.offset == 64
+    assert capi.PkvStep.max_slots.offset == 40 and capi.PkvStep.tables.offset == 48 and capi.PkvStep.q_visible.offset == 72
 
 
 def test_argument_errors_without_a_device(pkv):
-    assert pkv.pkv_abi_version() == 1
+    assert pkv.pkv_abi_version() == 2
     assert pkv.pkv_store_rows(None, 0, 576, None, None, 64, 576, 0, None) == capi.PKV_OK  # n <= 0 returns early
     assert pkv.pkv_store_rows(None, 4, 576, None, None, 64, 576, 0, None) == capi.PKV_ERR_ARG
     assert b"null pointer" in pkv.pkv_last_error()
@@ -53,6 +53,9 @@ def test_step_run_validates_before_touching_the_device(pkv):
     layers = (capi.PkvLayer * 1)()
     st.width, st.row_stride, st.rows_per_page, st.max_pages_per_seq = 576, 576, 64, 8
     st.nchunks, st.T, st.Q, st.k = 1, 1, 1, 8
+    assert pkv.pkv_step_run(C.byref(st), layers, 1, capi.PKV_DO_ROWS | capi.PKV_DO_GATHER, None) == capi.PKV_ERR_ARG
+    assert b"num_pages and max_slots" in pkv.pkv_last_error()                              # ids are checked against them
+    st.num_pages, st.max_slots = 16, 2
     flags = capi.PKV_DO_ROWS | capi.PKV_DO_GATHER
     assert pkv.pkv_step_run(C.byref(st), layers, 1, flags, None) == capi.PKV_ERR_ARG       # no tables / chunks
     assert b"tables and chunks" in pkv.pkv_last_error()

@@ -382,7 +382,7 @@ def test_config3_chunked_prefill(pkv, cuda, variant):
         step = capi.PkvStep()
         step.width = step.row_stride = W
         step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = rpp, pps, pages, 64
-        step.nchunks, step.T, step.Q, step.k = 1, n, 8, k
+        step.nchunks, step.T, step.Q, step.k, step.max_slots = 1, n, 8, k, tables.shape[0]
         step.tables, step.chunks, step.q_chunk, step.q_visible = (d_tables.data_ptr(), d_chunks.data_ptr(),
                                                                   d_qc.data_ptr(), d_qv.data_ptr())
         layers = tl.make_layers(L)
@@ -444,7 +444,7 @@ def test_full_size_decode_step_properties(pkv, cuda):
     step = capi.PkvStep()
     step.width = step.row_stride = W
     step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = rpp, pps, pages, 64
-    step.nchunks = step.T = step.Q = nseq
+    step.nchunks = step.T = step.Q = step.max_slots = nseq
     step.k = k
     step.tables, step.chunks, step.q_chunk, step.q_visible = (tables.data_ptr(), chunks.data_ptr(), q_chunk.data_ptr(),
                                                                q_vis.data_ptr())

@@ -63,7 +63,7 @@ class Store:
         step = capi.PkvStep()
         step.width = step.row_stride = tl.W
         step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = tl.RPP, self.pps, self.N, 64
-        step.nchunks, step.T, step.Q, step.k = len(chunks), T, 0, 0
+        step.nchunks, step.T, step.Q, step.k, step.max_slots = len(chunks), T, 0, 0, tables.shape[0]
         step.tables, step.chunks = d_tables.data_ptr(), d_chunks.data_ptr()
         layers = tl.make_layers(self.L)
         keep = []

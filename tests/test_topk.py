@@ -115,8 +115,33 @@ def test_topk_argument_errors(pkv):
     assert pkv.pkv_topk_bf16(None, 0, 10, 10, 4, None, None, 0, None) == capi.PKV_OK
     assert pkv.pkv_topk_bf16(16, 1, 10, 10, 5000, 16, 16, 1 << 20, None) == capi.PKV_ERR_LIMIT
     assert pkv.pkv_topk_bf16(16, 1, 10, 4, 4, 16, 16, 1 << 20, None) == capi.PKV_ERR_ARG
-    assert pkv.pkv_topk_bf16(16, 1, 10, 10, 4, 16, None, 0, None) == capi.PKV_ERR_ARG
-    assert b"scratch" in pkv.pkv_last_error()
+
+
+@pytest.mark.gpu
+def test_topk_scratch_is_optional(pkv, cuda):
+    """As in the reference (src/kernels/indexer.hpp:91-92: scratch = nullptr, scratch_words = 0), a caller may pass no
+    scratch or too little: the one-launch path needs none, the four-launch path falls back to the library's built-in
+    array, and only a shape that fits neither is refused, before anything is launched."""
+    g = tl.rng(12)
+    T, n, k = 5, 20000, 300
+    scores = tl.normal_bf16(g, (T, n))
+    want = orc.topk_bf16(scores, n, k)
+    d_s = tl.dev(cuda, scores)
+    st = tl.stream_ptr(cuda)
+    tiny = cuda.zeros(64, dtype=cuda.int32, device="cuda")
+    try:
+        for path in (0, 1):
+            capi.check(pkv.pkv_tune(7, path))
+            for scratch, words in ((None, 0), (tiny.data_ptr(), 64)):
+                d_idx = cuda.full((T * k,), -7, dtype=cuda.int32, device="cuda")
+                capi.check(pkv.pkv_topk_bf16(d_s.data_ptr(), T, n, n, k, d_idx.data_ptr(), scratch, words, st))
+                cuda.cuda.synchronize()
+                assert np.array_equal(tl.host(d_idx, np.int32, (T, k)), want), (path, words)
+        capi.check(pkv.pkv_tune(7, 1))
+        rc = pkv.pkv_topk_bf16(d_s.data_ptr(), 4096, 2, 2, 4096, tiny.data_ptr(), None, 0, st)   # 33 M words: nothing holds them
+        assert rc == capi.PKV_ERR_LIMIT and b"scratch" in pkv.pkv_last_error()
+    finally:
+        capi.check(pkv.pkv_tune(7, 0))
 
 
 def expand_case(g, n, k, pool):

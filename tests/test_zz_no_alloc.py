@@ -1,12 +1,13 @@
 """pkv_topk_bf16_static: the top-k entry point that allocates nothing and brings its own scratch (an array compiled into
 the library), for callers that can neither pass device scratch nor tolerate an allocation. Its index lists must be
-identical to those of pkv_topk_bf16 (which takes caller scratch) on the same scores — checked on two calls in a row,
-the second on different scores, so that whatever the first call left in the shared scratch cannot leak into the second
-result. Collected last on purpose: a run that stops at the first failure has then already run every other test."""
+identical to those of pkv_topk_bf16 (which takes caller scratch) on the same scores, and both must equal the CPU
+oracle's — checked on two calls in a row, the second on different scores, so that whatever the first call left in the
+shared scratch cannot leak into the second result. Collected last on purpose: a run that stops at the first failure has then already run every other test."""
 import numpy as np
 import pytest
 
 import pkv_testlib as tl
+from oracle import oracle_lib as orc
 from unholy_b200 import capi
 
 pytestmark = pytest.mark.gpu
@@ -31,6 +32,7 @@ def test_static_scratch_topk_matches_caller_scratch_topk(pkv, cuda):
         cuda.cuda.synchronize()
         ref, got = tl.host(d_ref, np.int32, (T, k)), tl.host(d_got, np.int32, (T, k))
         assert np.array_equal(got, ref), f"call {call}"   # index lists are integers: identical, no tolerance
+        assert np.array_equal(got, orc.topk_bf16(scores, n, k, threads=8)), f"call {call}: differs from the oracle"
         assert list(got[5 + call, :4]) == [0, 1, 2, 3]
 
 

@@ -34,7 +34,7 @@ class PkvLayer(C.Structure):
 class PkvStep(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("width", "row_stride", "rows_per_page", "max_pages_per_seq", "num_pages", "fp8_block", "nchunks", "T",
-                 "Q", "k")] + [(n, C.c_void_p) for n in ("tables", "chunks", "q_chunk", "q_visible")]
+                 "Q", "k", "max_slots", "reserved")] + [(n, C.c_void_p) for n in ("tables", "chunks", "q_chunk", "q_visible")]
 
 
 class PkvStateSeg(C.Structure):
@@ -59,6 +59,7 @@ _SIGS = {
     "pkv_abi_version": (_i, []),
     "pkv_tune": (_i, [_i, _i]),
     "pkv_device_status": (_i, [C.POINTER(C.c_int)]),
+    "pkv_stream_check": (_i, [_vp]),
     "pkv_store_rows": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_store_rows_fp4": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),
     "pkv_load_rows_fp4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp]),

@@ -95,18 +95,31 @@ inline void gather_rows(PagedRows src, int width, const int32_t* idx, const int3
                             reinterpret_cast<pkv_stream_t>(st)), "gather_rows");
 }
 
-// src/kernels/indexer.hpp:74-94 (top-k with scratch) and src/kernels/glm_fast.hpp:115-122.
-inline size_t topk_scratch_words(int rows, int n, int k) { return pkv_topk_scratch_words(rows, n, k); }
-inline void topk_bf16(const uint16_t* scores, int T, int n, int k, int32_t* idx, cudaStream_t st, uint32_t* scratch,
-                      size_t scratch_words) {
-  pkv_throw(pkv_topk_bf16(scores, T, n, n, k, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)), "topk_bf16");
+// src/kernels/indexer.hpp:74-94: the reference's declarations, argument for argument.
+inline void topk_bf16(const uint16_t* scores, int T, int n, int k, int32_t* idx, cudaStream_t st) {
+  pkv_throw(pkv_topk_bf16(scores, T, n, n, k, idx, nullptr, 0, reinterpret_cast<pkv_stream_t>(st)), "topk_bf16");
 }
-// src/kernels/indexer.hpp:76-94: TopkRows / TopkBatch keep their field names; scratch is required here.
-using TopkRows = pkv_topk_group;
-inline void topk_bf16_batch(const uint16_t* scores, const TopkRows* groups, int ngroups, int32_t* idx, cudaStream_t st,
-                            uint32_t* scratch, size_t scratch_words) {
-  pkv_throw(pkv_topk_bf16_batch(scores, groups, ngroups, idx, scratch, scratch_words, reinterpret_cast<pkv_stream_t>(st)),
-            "topk_bf16_batch");
+struct TopkRows {
+  size_t off;
+  int rows, n, k, idx_off;
+};
+static_assert(sizeof(TopkRows) == sizeof(pkv_topk_group), "TopkRows is passed to the C ABI as pkv_topk_group");
+struct TopkBatch {
+  static constexpr int kMax = 32;
+  int ngroups = 0;
+  TopkRows g[kMax];
+};
+constexpr int kTopkSplitMinKeys = 8192, kTopkSplitMaxRows = 64;
+// The reference sizes the scratch of its several-workgroups-per-row path with this. Here the CTAs of a row exchange
+// through distributed shared memory, so that path needs no scratch: 0. (Shapes outside it, k > 2048 or rows longer
+// than 655,360 keys, use the caller's scratch when it holds topk_scratch_words(rows, n, k) words and the library's
+// built-in array otherwise.)
+inline size_t topk_split_scratch_words(int /*rows*/) { return 0; }
+inline size_t topk_scratch_words(int rows, int n, int k) { return pkv_topk_scratch_words(rows, n, k); }
+inline void topk_bf16_batch(const uint16_t* scores, const TopkBatch& b, int32_t* idx, cudaStream_t st, uint32_t* scratch = nullptr,
+                            size_t scratch_words = 0) {
+  pkv_throw(pkv_topk_bf16_batch(scores, reinterpret_cast<const pkv_topk_group*>(b.g), b.ngroups, idx, scratch, scratch_words,
+                                reinterpret_cast<pkv_stream_t>(st)), "topk_bf16_batch");
 }
 // src/kernels/ref.hpp:107 (k > 1024 throws, as ref_attn.hip:391 does) and src/kernels/glm_fast.hpp:86-93: the same
 // selection; glm_topk keeps its cand argument (unused: one CTA per row selects in shared memory) and its size query.

@@ -230,12 +230,12 @@ __device__ __forceinline__ int find_chunk(const pkv_chunk* __restrict__ chunks, 
 // Physical row id of logical row `lr` of `slot`, or -1 (recorded) when the table entry is unusable.
 __device__ __forceinline__ long long physical_row(const pkv_step& s, int slot, int lr, int tag) {
   const int pg = (s.rows_per_page & (s.rows_per_page - 1)) == 0 ? lr >> (31 - __clz(s.rows_per_page)) : lr / s.rows_per_page;
-  if (lr < 0 || pg >= s.max_pages_per_seq) {
+  if (lr < 0 || pg >= s.max_pages_per_seq || unsigned(slot) >= unsigned(s.max_slots)) {
     report(2, tag);
     return -1;
   }
   const int page = __ldg(&s.tables[size_t(slot) * s.max_pages_per_seq + pg]);
-  if (page < 0 || (s.num_pages > 0 && page >= s.num_pages)) {
+  if (unsigned(page) >= unsigned(s.num_pages)) {
     report(1, tag);
     return -1;
   }
@@ -351,6 +351,10 @@ __device__ __forceinline__ const uint4* gather_source(const StepParams& P, const
   const int row = __ldg(&ly.idx[size_t(q) * s.k + e]);
   const int vis = __ldg(&s.q_visible[q]);
   const int qc = __ldg(&s.q_chunk[q]);
+  if (unsigned(qc) >= unsigned(s.nchunks)) {
+    report(2, q);
+    return nullptr;
+  }
   const pkv_chunk ch = s.chunks[qc];
   if (row < 0 || row >= vis) return nullptr;
   if ((P.flags & PKV_DO_ROWS) && ly.rows && row >= ch.s0 && row < ch.s0 + ch.n)
@@ -897,7 +901,10 @@ struct OneSeqRows {
 struct StepRows {
   pkv_step s;
   // the query row's slot: loaded before (not after) its index entry, so the two chains overlap
-  __device__ __forceinline__ int begin(int t) const { return s.chunks[__ldg(&s.q_chunk[t])].slot; }
+  __device__ __forceinline__ int begin(int t) const {
+    const int qc = __ldg(&s.q_chunk[t]);
+    return unsigned(qc) < unsigned(s.nchunks) ? s.chunks[qc].slot : -1;  // -1: physical_row reports it
+  }
   __device__ __forceinline__ long long rid(int slot, int t, int row) const { return physical_row(s, slot, row, t); }
 };
 // Entries given as selected pools instead of a token list: entry j of query row t is what glm_idx_expand
@@ -1170,7 +1177,7 @@ int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t 
 extern "C" {
 
 const char* pkv_last_error(void) { return g_err.c_str(); }
-int pkv_abi_version(void) { return 1; }
+int pkv_abi_version(void) { return 2; }
 
 int pkv_tune(int knob, int value) {
   Tuning& t = tuning();
@@ -1199,6 +1206,22 @@ int pkv_device_status(int* status_out) {
   if (e != cudaSuccess) return fail_cuda("cudaMemcpyToSymbol", e);
   *status_out = v;
   return PKV_OK;
+}
+
+int pkv_stream_check(pkv_stream_t stream) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(&v, g_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail_cuda("pkv_stream_check", e);
+  if (v == 0) return PKV_OK;
+  const int zero = 0;
+  e = cudaMemcpyToSymbolAsync(g_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail_cuda("pkv_stream_check", e);
+  static const char* const kinds[] = {"?", "page id out of range", "chunk row, chunk index or slot out of range", "bounded wait gave up"};
+  const int kind = v & 0xff;
+  return fail(PKV_ERR_DEVICE, std::string("device-side check failed: ") + kinds[kind >= 1 && kind <= 3 ? kind : 0] + " (entry " +
+                                  std::to_string(v >> 8) + ")");
 }
 
 int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* pool, const int32_t* table, int rows_per_page,
@@ -1329,6 +1352,8 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
     return fail(PKV_ERR_ARG, "pkv_step_run: width and row_stride must be positive multiples of 8 with row_stride >= width");
   if (s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks < 0 || s.T < 0 || s.Q < 0 || s.k < 0)
     return fail(PKV_ERR_ARG, "pkv_step_run: bad geometry");
+  if (s.num_pages <= 0 || s.max_slots <= 0)
+    return fail(PKV_ERR_ARG, "pkv_step_run: num_pages and max_slots must be positive (the kernels check page ids and slots against them)");
   const bool append = (flags & (PKV_DO_ROWS | PKV_DO_KEYS_FP4 | PKV_DO_KEYS_FP8)) != 0 && s.T > 0 && s.nchunks > 0;
   const bool gather = (flags & PKV_DO_GATHER) != 0 && s.Q > 0 && s.k > 0;
   if (!append && !gather) return PKV_OK;
@@ -1436,6 +1461,7 @@ static int step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uin
   if (const int rc = check_quant_shape(s.Q, width, block, name)) return rc;
   if (width <= 0 || width % 16 != 0 || block % 16 != 0 || s.rows_per_page <= 0 || s.max_pages_per_seq <= 0 || s.nchunks <= 0)
     return fail(PKV_ERR_ARG, std::string(name) + ": width must be a positive multiple of 16, the step needs pages and chunks");
+  if (s.num_pages <= 0 || s.max_slots <= 0) return fail(PKV_ERR_ARG, std::string(name) + ": num_pages and max_slots must be positive");
   if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, std::string(name) + ": codes and out must be 16-byte aligned");
   const long long tiles = (long long)s.Q * ((k + kGatherRows - 1) / kGatherRows);
   const DeviceInfo& d = device_info();

@@ -18,7 +18,7 @@
 
 #include "../../include/unholy_pkv.h"
 
-extern thread_local std::string pkv_g_err;  // defined in pkv_kernels.cu: what pkv_last_error() returns
+#include "pkv_internal.hpp"
 
 namespace pkv_state {
 

@@ -63,7 +63,7 @@ __device__ __forceinline__ void load_keys(const uint16_t* __restrict__ r, int ba
   if (base + kPerThread <= hi && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
     for (int v = 0; v < kPerThread / 8; ++v) {
-      const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + v);
+      const uint4 w = __ldcg(reinterpret_cast<const uint4*>(p) + v);
       const uint32_t x[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -219,10 +219,10 @@ __global__ void __launch_bounds__(kThreads) collect_kernel(const uint16_t* __res
   const int lo = sl * kSlice, hi = min(n, lo + kSlice), base = lo + tid * kPerThread;
   uint32_t key[kPerThread];
   load_keys(r, base, hi, key);
-  const uint32_t want = __ldg(&info[kWant]);
+  const uint32_t want = __ldcg(&info[kWant]);
   if (want == 0) return;
-  const uint32_t thr = (__ldg(&info[kHiBin]) << 8) | __ldg(&info[kLoBin]), need_ties = __ldg(&info[kNeedTies]);
-  const uint32_t above_total = __ldg(&info[kAboveTotal]), above_before = __ldg(&offs[0]), ties_before = __ldg(&offs[1]);
+  const uint32_t thr = (__ldcg(&info[kHiBin]) << 8) | __ldcg(&info[kLoBin]), need_ties = __ldcg(&info[kNeedTies]);
+  const uint32_t above_total = __ldcg(&info[kAboveTotal]), above_before = __ldcg(&offs[0]), ties_before = __ldcg(&offs[1]);
   // This thread's counts, packed (above << 16 | ties; a slice holds 8192 keys), and their block-wide exclusive scan.
   uint32_t cnt = 0;
 #pragma unroll
@@ -261,11 +261,11 @@ __global__ void __launch_bounds__(kSortThreads) sort_kernel(const uint32_t* __re
   extern __shared__ unsigned long long s_keys[];
   const int row = blockIdx.x, tid = threadIdx.x;
   const size_t cand_offset = L.cand_offset_words;
-  const uint32_t want = __ldg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
+  const uint32_t want = __ldcg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
   int size = 2;
   while (size < k) size <<= 1;
   const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
-  for (int i = tid; i < size; i += kSortThreads) s_keys[i] = uint32_t(i) < want ? cand[i] : 0ull;
+  for (int i = tid; i < size; i += kSortThreads) s_keys[i] = uint32_t(i) < want ? __ldcg(&cand[i]) : 0ull;
   __syncthreads();
   const int pairs = size >> 1;
   for (int len = 2; len <= size; len <<= 1)
@@ -301,10 +301,10 @@ __global__ void __launch_bounds__(1024) sort_pairs_kernel(const uint32_t* __rest
   extern __shared__ unsigned long long s_keys[];
   const int row = blockIdx.x, tid = threadIdx.x;
   const size_t cand_offset = L.cand_offset_words;
-  const uint32_t want = __ldg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
+  const uint32_t want = __ldcg(&scratch[L.info_offset + size_t(row) * 8 + kWant]);
   const unsigned long long* cand = reinterpret_cast<const unsigned long long*>(scratch + cand_offset) + size_t(row) * k;
   const int i0 = 2 * tid, i1 = i0 + 1;
-  unsigned long long a = uint32_t(i0) < want ? cand[i0] : 0ull, b = uint32_t(i1) < want ? cand[i1] : 0ull;
+  unsigned long long a = uint32_t(i0) < want ? __ldcg(&cand[i0]) : 0ull, b = uint32_t(i1) < want ? __ldcg(&cand[i1]) : 0ull;
   // Position i keeps the larger of the pair when it is the lower position of a descending run (or the upper of an
   // ascending one).
   auto keep = [](unsigned long long mine, unsigned long long other, bool take_max) {
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(256) idx_expand_kernel(const int32_t* __restri
 
 }  // namespace pkv_topk
 
-extern thread_local std::string pkv_g_err;  // defined in pkv_kernels.cu: what pkv_last_error() returns
+#include "pkv_internal.hpp"
 
 // Scratch for pkv_topk_bf16_static: 4 MiB that every GPU which loads the library holds until the process exits.
 // In host code this name is only a handle for the runtime (not a device address): the device address is looked up once
@@ -373,30 +373,26 @@ std::mutex g_static_mu;
 int static_scratch(uint32_t** out, std::string& err) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-    err = std::string("pkv_topk_bf16_static: cudaGetDevice: ") + cudaGetErrorString(e);
+  if (e != cudaSuccess) {
+    err = std::string("built-in top-k scratch: cudaGetDevice: ") + cudaGetErrorString(e);
     return PKV_ERR_CUDA;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    err = "built-in top-k scratch: device ordinal " + std::to_string(dev) + " is outside the " + std::to_string(kMaxDevices) + " this library tracks";
+    return PKV_ERR_LIMIT;
   }
   std::lock_guard<std::mutex> lk(g_static_mu);
   if (!g_static_ptr[dev]) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_topk_static_scratch);
     if (e != cudaSuccess || !p) {
-      err = std::string("pkv_topk_bf16_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
+      err = std::string("built-in top-k scratch: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
       return PKV_ERR_CUDA;
     }
     g_static_ptr[dev] = static_cast<uint32_t*>(p);
   }
   *out = g_static_ptr[dev];
   return PKV_OK;
-}
-}  // namespace
-
-extern "C" {
-
-size_t pkv_topk_scratch_words(int T, int n, int k) {
-  if (T <= 0 || k <= 0) return 0;
-  return pkv_topk::layout(T, n > 0 ? n : 1, k).total_words;
 }
 
 // Launches the four kernels on `stream` with caller-provided scratch. Shared by pkv_topk_bf16 and the entry point that
@@ -445,26 +441,32 @@ int pkv_topk_launch(const uint16_t* scores, int T, int n, long long ld, int k, i
   return PKV_OK;
 }
 
-// pkv_topk_cluster.cu: the whole selection in one launch of thread-block clusters, for the shapes it takes.
-struct pkv_topk_cluster_group {
-  long long off, ld, idx_off;
-  int rows, n, k, row0;
-};
-bool pkv_topk_cluster_eligible(int T, int n, int k);
-int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group* groups, int ngroups, int32_t* idx,
-                            cudaStream_t stream, bool* usable, std::string& err);
-extern int pkv_g_topk_path;
+// The scratch the four-launch path uses: the caller's when it is there, aligned and large enough, else the library's
+// built-in array (the one pkv_topk_bf16_static uses) when the shape fits it.
+int pkv_topk_pick_scratch(uint32_t* scratch, size_t scratch_words, size_t need, uint32_t** out, std::string& err) {
+  if (scratch && scratch_words >= need && (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0) {
+    *out = scratch;
+    return PKV_OK;
+  }
+  if (need <= kStaticScratchWords) return static_scratch(out, err);
+  err = "pkv_topk_bf16: this shape runs as four launches that need " + std::to_string(need) +
+        " uint32 words of 8-byte aligned scratch (pkv_topk_scratch_words); the caller gave " + std::to_string(scratch ? scratch_words : 0) +
+        " and the built-in scratch holds " + std::to_string(kStaticScratchWords);
+  return PKV_ERR_LIMIT;
+}
 
-// One cluster launch when the shape and the device allow it, else the four launches through `scratch`.
+// One cluster launch when the shape and the device allow it (no scratch), else the four launches through scratch.
 int pkv_topk_dispatch(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
-                      cudaStream_t stream, std::string& err) {
+                      size_t scratch_words, cudaStream_t stream, std::string& err) {
   if (pkv_g_topk_path != 1 && pkv_topk_cluster_eligible(T, n, k)) {
     bool usable = false;
     const pkv_topk_cluster_group g{0, ld, 0, T, n, k, 0};
     if (const int rc = pkv_topk_cluster_launch(scores, &g, 1, idx, stream, &usable, err)) return rc;
     if (usable) return PKV_OK;
   }
-  return pkv_topk_launch(scores, T, n, ld, k, idx, scratch, stream, err);
+  uint32_t* use = nullptr;
+  if (const int rc = pkv_topk_pick_scratch(scratch, scratch_words, pkv_topk::layout(T, n > 0 ? n : 1, k).total_words, &use, err)) return rc;
+  return pkv_topk_launch(scores, T, n, ld, k, idx, use, stream, err);
 }
 
 int pkv_topk_check(const uint16_t* scores, int T, int n, long long ld, int k, const int32_t* idx, std::string& err) {
@@ -483,16 +485,20 @@ int pkv_topk_check(const uint16_t* scores, int T, int n, long long ld, int k, co
   return PKV_OK;
 }
 
+}  // namespace
+
+extern "C" {
+
+size_t pkv_topk_scratch_words(int T, int n, int k) {
+  if (T <= 0 || k <= 0) return 0;
+  return pkv_topk::layout(T, n > 0 ? n : 1, k).total_words;
+}
+
 int pkv_topk_bf16(const uint16_t* scores, int T, int n, long long ld, int k, int32_t* idx, uint32_t* scratch,
                   size_t scratch_words, pkv_stream_t stream) {
   if (const int rc = pkv_topk_check(scores, T, n, ld, k, idx, pkv_g_err)) return rc;
   if (T == 0) return PKV_OK;
-  const size_t need = pkv_topk::layout(T, n > 0 ? n : 1, k).total_words;
-  if (!scratch || scratch_words < need || (reinterpret_cast<uintptr_t>(scratch) & 7u)) {
-    pkv_g_err = "pkv_topk_bf16: scratch must be 8-byte aligned and hold pkv_topk_scratch_words(T, n, k) words";
-    return PKV_ERR_ARG;
-  }
-  return pkv_topk_dispatch(scores, T, n, ld, k, idx, scratch, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
+  return pkv_topk_dispatch(scores, T, n, ld, k, idx, scratch, scratch_words, reinterpret_cast<cudaStream_t>(stream), pkv_g_err);
 }
 
 size_t pkv_topk_batch_scratch_words(const pkv_topk_group* groups, int ngroups) {
@@ -506,11 +512,6 @@ int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, in
                         size_t scratch_words, pkv_stream_t stream) {
   if (ngroups < 0 || (ngroups > 0 && !groups)) {
     pkv_g_err = "pkv_topk_bf16_batch: bad group list";
-    return PKV_ERR_ARG;
-  }
-  if (ngroups > 0 && (!scratch || scratch_words < pkv_topk_batch_scratch_words(groups, ngroups) ||
-                      (reinterpret_cast<uintptr_t>(scratch) & 7u))) {
-    pkv_g_err = "pkv_topk_bf16_batch: scratch must be 8-byte aligned and hold pkv_topk_batch_scratch_words() words";
     return PKV_ERR_ARG;
   }
   for (int g = 0; g < ngroups; ++g)
@@ -542,7 +543,7 @@ int pkv_topk_bf16_batch(const uint16_t* scores, const pkv_topk_group* groups, in
   for (int g = 0; g < ngroups; ++g) {
     const pkv_topk_group& q = groups[g];
     if (q.rows <= 0) continue;
-    if (const int rc = pkv_topk_dispatch(scores + q.off, q.rows, q.n, q.n, q.k, idx + q.idx_off, scratch,
+    if (const int rc = pkv_topk_dispatch(scores + q.off, q.rows, q.n, q.n, q.k, idx + q.idx_off, scratch, scratch_words,
                                          reinterpret_cast<cudaStream_t>(stream), pkv_g_err))
       return rc;
   }

@@ -37,14 +37,9 @@
 #include <string>
 
 #include "../../include/unholy_pkv.h"
+#include "pkv_internal.hpp"
 
 namespace cg = cooperative_groups;
-
-// One block of rows of a launch (shared with pkv_topk.cu, which fills these in).
-struct pkv_topk_cluster_group {
-  long long off, ld, idx_off;
-  int rows, n, k, row0;
-};
 
 namespace pkv_topkc {
 
@@ -535,7 +530,7 @@ __global__ void __launch_bounds__(THREADS, kMaxThreads / THREADS) topk_cluster_k
 
 }  // namespace pkv_topkc
 
-extern "C" {  // library-internal (hidden visibility), declared in pkv_topk.cu
+// Library-internal entry points (declared in pkv_internal.hpp).
 
 // Whether the one-launch path takes this shape.
 bool pkv_topk_cluster_eligible(int T, int n, int k) {
@@ -645,5 +640,3 @@ int pkv_topk_cluster_launch(const uint16_t* scores, const pkv_topk_cluster_group
   }
   return PKV_OK;
 }
-
-}  // extern "C"
