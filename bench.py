@@ -61,6 +61,11 @@ def parse_args():
     ap.add_argument("--layers-per-launch", type=int, default=1)
     ap.add_argument("--resident-layers", type=int, default=0, help="0 = as many pools as fit")
     ap.add_argument("--small", action="store_true", help="a reduced pool (for profiler captures and quick checks)")
+    ap.add_argument("--context", type=int, default=0,
+                    help="rows per sequence (default 131072, the benchmark configuration; --small = 8192); a smaller value is "
+                         "for profiler captures, whose device memory must stay within a few GB")
+    ap.add_argument("--repeats", type=int, default=10, help="how many times the block of --steps steps is timed (median reported)")
+    ap.add_argument("--no-ops", action="store_true", help="skip the extra legs (configurations 3 and 4 at N = 1, configuration 5 at N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", type=int, default=int(os.environ.get("PKV_BENCH_GRAPH", "1")),
@@ -135,7 +140,8 @@ class Workload:
     def __init__(self, torch, args, rank: int):
         from unholy_b200 import capi
         self.torch, self.capi, self.lib = torch, capi, capi.lib()
-        self.context = 8192 if args.small else CONTEXT
+        self.context = args.context or (8192 if args.small else CONTEXT)
+        assert self.context % RPP == 0 and self.context >= K_SEL
         self.pps = self.context // RPP
         self.num_pages = NSEQ * self.pps
         self.variant = capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0
@@ -396,14 +402,18 @@ def run_ours(args):
         barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step_fn(0)
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
+    # The block of exactly K steps is timed R times (barrier + synchronize on both sides of every block); the median
+    # block gives `value`, the fastest and slowest give value_max / value_min.
+    block_ms = []
+    for _ in range(max(1, args.repeats)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step_fn(0)
+        e1.record(stream)
+        barrier()
+        block_ms.append(e0.elapsed_time(e1))
     clocks = sampler.stop()
     ok, why = wl.verify()
 
@@ -454,12 +464,14 @@ def run_ours(args):
         e2e_ms = f0.elapsed_time(f1)
         e2e = (e2e_ms, h2d, d2h)
 
-    times = torch.tensor([ms, e2e[0] if e2e else 0.0], dtype=torch.float64, device="cuda")
+    times = torch.tensor(block_ms + [e2e[0] if e2e else 0.0], dtype=torch.float64, device="cuda")
     oks = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)      # every block: the slowest rank's time
         dist.all_reduce(oks, op=dist.ReduceOp.MIN)
-    ms_max, e2e_ms_max = float(times[0]), float(times[1])
+    blocks = sorted(float(t) for t in times[:-1])
+    ms_max, e2e_ms_max = blocks[len(blocks) // 2] if len(blocks) % 2 else 0.5 * (blocks[len(blocks) // 2 - 1] + blocks[len(blocks) // 2]), float(times[-1])
+    ms = float(np.median(block_ms))                        # this rank's own median block (rank 0: the roofline's kernel time)
     all_ok = bool(int(oks[0]))
 
     if rank == 0:
@@ -467,7 +479,7 @@ def run_ours(args):
         total_bytes = step_bytes * world * args.steps
         value = total_bytes / (ms_max * 1e-3) / 1e9
         per_gpu = value / world
-        launches = wl.launches_per_step * args.steps
+        launches = wl.launches_per_step * args.steps          # per timed block of K steps
         # Dominant kernel = the per-layer gather. Its average duration is taken as the timed region divided by the
         # number of layer calls (an upper bound: it charges the small append kernel and launch gaps to it).
         calls = len(wl.groups) * args.steps
@@ -484,6 +496,8 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (pools %.0f GB, outputs %.1f GB per step)" % (
                            wl.resident * wl.num_pages * PAGE_BYTES / 1e9, LAYERS * NSEQ * K_SEL * ROW_BYTES / 1e9),
                        "step_GB_per_gpu": round(step_bytes / 1e9, 3)},
+            "repeats": len(blocks), "value_min": round(total_bytes / (blocks[-1] * 1e-3) / 1e9, 1),
+            "value_max": round(total_bytes / (blocks[0] * 1e-3) / 1e9, 1),
             "decode_step_us": round(ms_max / args.steps * 1e3, 1),
             "pct_of_8TBps_per_gpu": round(per_gpu / 8000 * 100, 2),
             "pct_of_measured_peak_per_gpu": round(per_gpu / peak * 100, 2),
@@ -503,6 +517,14 @@ def run_ours(args):
                            "note": "host rows, keys, index lists, block tables and chunk lists copied in from pinned "
                                    "memory every step (on a copy stream, one step ahead of the kernels); one sequence's "
                                    "gathered tile of the last layer copied back"}
+        if world == 1 and not args.no_ops and not args.small and not args.context:
+            # The other operations of the path at the sizes of benchmark configurations 3 and 4, on the same GPU after
+            # the decode workload's memory has been released.
+            del graphs, wl
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            line["ops"] = extra_ops(args, peak)
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle_lib as orc
             threads = max(1, orc.hardware_threads())
@@ -517,6 +539,29 @@ def run_ours(args):
         sys.exit(3)
 
 
+def extra_ops(args, peak):
+    """Configurations 3 (chunked prefill) and 4 (prefix churn: appends, copy-on-write, compaction) in short form: GB/s
+    over the algorithmic bytes, the fraction of the measured copy peak, and the run's own bit-exact check."""
+    out = {}
+    pre = measure_prefill(args)
+    out["prefill_cfg3"] = {"GBps": pre["value"], "frac_of_measured_peak": round(pre["value"] / peak, 4), "us_per_layer_call": pre["us_per_call"],
+                           "algorithmic_GB": pre["algorithmic_GB"], "bit_exact": pre["bit_exact_check"]["ok"],
+                           "what": pre["config"]["workload"] + "; one library call per (chunk, layer)"}
+    import gc
+    gc.collect()
+    ch = measure_churn(args)
+    names = {"compaction_copy": "compaction_cfg4", "cow_copy": "copy_on_write_cfg4", "prefix_append": "prefix_appends_4096_rows_cfg4",
+             "prefix_append_all_layers_one_launch": "prefix_appends_4096_rows_all_layers_one_launch_cfg4",
+             "append_512": "appends_8x512_rows_cfg4", "append_512_all_layers_one_launch": "appends_8x512_rows_all_layers_one_launch_cfg4"}
+    for k, name in names.items():
+        if k in ch["operations"]:
+            o = ch["operations"][k]
+            out[name] = {"GBps": o["GBps"], "frac_of_measured_peak": round(o["GBps"] / peak, 4), "ms": o["ms"], "algorithmic_GB": o["GB"],
+                         "bit_exact": ch["bit_exact_check"]["ok"]}
+    out["churn_cfg4_what"] = ch["config"]["workload"] + f"; {ch['compaction_moves']} pages moved by compaction, {ch['cow_pages']} duplicated by copy-on-write (one launch)"
+    return out
+
+
 def _cuda_setup():
     import torch
     if not torch.cuda.is_available():
@@ -526,17 +571,25 @@ def _cuda_setup():
     return torch, capi, capi.lib()
 
 
-def _emit(name, value, ms, extra):
+def _result(name, value, ms, extra):
     peak, kind = load_peaks()
     line = {"metric": "paged_kv_" + name + "_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
             "ms_total": round(ms, 3), "higher_is_better": True, "data": "synthetic",
             "pct_of_8TBps": round(value / 80, 2), "pct_of_measured_peak": round(value / peak * 100, 2),
             "peak": peak, "peak_kind": "of " + kind}
     line.update(extra)
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def _emit(name, value, ms, extra):
+    print(json.dumps(_result(name, value, ms, extra)), flush=True)
 
 
 def run_prefill(args):
+    print(json.dumps(measure_prefill(args)), flush=True)
+
+
+def measure_prefill(args):
     """Configuration 3: one sequence filled 0 -> 512k tokens in 4096-token chunks across 43 layers. Per chunk and layer
     ONE library call: 4096 bf16 rows appended into freshly taken, non-contiguous pages, their 128-wide keys quantised to
     fp8 e4m3 (block 64) and MXFP4, and 8 query rows at the chunk's end gathering 2048 positions skewed toward recent
@@ -625,7 +678,7 @@ def run_prefill(args):
         want = pool[ph].clone()
         want[sel < 0] = 0
         ok &= torch.equal(out[l, 7].view(torch.int16), want.view(torch.int16))
-    _emit("prefill", nbytes / (ms * 1e-3) / 1e9, ms, {
+    return _result("prefill", nbytes / (ms * 1e-3) / 1e9, ms, {
         "config": {"workload": f"chunked prefill 0->{total} tokens, {nchunks} chunks x 43 layers, bf16 rows + fp8 + MXFP4 keys, 8 queries x 2048 per chunk",
                    "gather_variant": args.variant},
         "algorithmic_GB": round(nbytes / 1e9, 2), "calls": nchunks * LAYERS, "us_per_call": round(ms * 1e3 / (nchunks * LAYERS), 2),
@@ -633,6 +686,10 @@ def run_prefill(args):
 
 
 def run_churn(args):
+    print(json.dumps(measure_churn(args)), flush=True)
+
+
+def measure_churn(args):
     """Configuration 4: prefix-cache churn on a 1.5M-token pool (24,576 pages, 43 layers of bf16 row + MXFP4 key pools,
     82.5 GB). 64 prefixes of 2k..64k tokens are written and released (their full pages stay cached, later ones evict
     earlier ones LRU-first); 8 live requests take the 8 newest prefixes from the cache (shared full pages), are forked
@@ -686,7 +743,7 @@ def run_churn(args):
         t = np.ctypeslib.as_array(lib.pkv_pool_tables(pool), shape=(slots * pps,))
         d_tables.copy_(torch.from_numpy(t.copy()), non_blocking=False)
 
-    def append(items, name):
+    def append(items, name, also_one_launch=False):
         """items: [(handle, writer, s0, n)], n <= CH in total per call group; all layers, one call per layer."""
         chunk_list, t0 = [], 0
         for h, writer, s0, n in items:
@@ -702,7 +759,13 @@ def run_churn(args):
         def go():
             for l in range(L):
                 capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4, sp))
-        timed(name, go, L * t0 * (2 * ROW_BYTES + KEY_DIM * 2 + 68))
+
+        def go_one_launch():   # the same rows of all 43 layers in ONE launch (possible where every layer's rows exist up front)
+            capi.check(lib.pkv_step_run(C.byref(step), lptr[0], L, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_VARIANT_BULK, sp))
+        nb = L * t0 * (2 * ROW_BYTES + KEY_DIM * 2 + 68)
+        timed(name, go, nb)
+        if also_one_launch:    # writes the same bytes again: positions are rewritten, the pool content does not change
+            timed(name + "_all_layers_one_launch", go_one_launch, nb)
 
     def copy_pages(src, dst, name):
         descs = (capi.PkvPoolDesc * (2 * L))()
@@ -716,11 +779,11 @@ def run_churn(args):
         timed(name, lambda: capi.check(lib.pkv_copy_pages(descs, 2 * L, ids.data_ptr(), ids.data_ptr() + 4 * n, n, N, N, sp)),
               2 * n * L * (PAGE_BYTES + FP4_PAGE_BYTES))
 
-    def write_range(h, writer, s0, end, name):
+    def write_range(h, writer, s0, end, name, also_one_launch=False):
         while s0 < end:
             n = min(CH, end - s0)
             assert lib.pkv_pool_alloc(pool, h, s0 + n) == 1
-            append([(h, writer, s0, n)], name)
+            append([(h, writer, s0, n)], name, also_one_launch and n == CH)
             s0 += n
 
     # phase 1: prefixes written, named, released
@@ -729,7 +792,7 @@ def run_churn(args):
     for j, n in enumerate(lengths):
         h = lib.pkv_pool_seq_open(pool)
         assert lib.pkv_pool_assign_slot(pool, h) >= 0
-        write_range(h, j, 0, int(n), "prefix_append")
+        write_range(h, j, 0, int(n), "prefix_append", also_one_launch=j % 8 == 7)
         capi.check(lib.pkv_pool_register(pool, h, toks[j].ctypes.data_as(i32p), int(n), int(n)))
         capi.check(lib.pkv_pool_seq_close(pool, h))
     # phase 2: 8 live requests on the 8 newest prefixes; each is forked at its unaligned end
@@ -746,17 +809,19 @@ def run_churn(args):
         c = lib.pkv_pool_fork(pool, h, len(prompt))
         assert c >= 0 and lib.pkv_pool_assign_slot(pool, c) >= 0
         live += [[h, list(segs), len(prompt), 100 + r], [c, list(segs), len(prompt), 200 + r]]
-    cow_pairs = 0
-    for rec in live:   # the first append into the shared partial page duplicates it
+    cow_src, cow_dst = [], []
+    for rec in live:   # the first append into the shared partial page duplicates it: the step's pairs are collected ...
         h, segs, n, writer = rec
         assert lib.pkv_pool_alloc(pool, h, n + 512) == 1
         m = lib.pkv_pool_cow(pool, h, n, 512, src.ctypes.data_as(i32p), dst.ctypes.data_as(i32p), 64)
         assert m >= 0
-        if m:
-            copy_pages(src[:m].copy(), dst[:m].copy(), "cow_copy")
-            cow_pairs += m
+        cow_src += src[:m].tolist()
+        cow_dst += dst[:m].tolist()
+    cow_pairs = len(cow_src)
+    if cow_pairs:      # ... and duplicated by ONE launch over all pairs, layers and pools
+        copy_pages(np.array(cow_src, np.int32), np.array(cow_dst, np.int32), "cow_copy")
     for g0 in range(0, len(live), 8):   # 8 sequences x 512 rows = one 4096-row call per layer
-        append([(rec[0], rec[3], rec[2], 512) for rec in live[g0:g0 + 8]], "append_512")
+        append([(rec[0], rec[3], rec[2], 512) for rec in live[g0:g0 + 8]], "append_512", also_one_launch=True)
     for rec in live:
         rec[1].append((rec[3], rec[2], rec[2] + 512))
         rec[2] += 512
@@ -787,11 +852,11 @@ def run_churn(args):
     ok &= st.value == 0
     ops = {k: {"ms": round(v[0], 3), "GB": round(v[1] / 1e9, 3), "GBps": round(v[1] / max(v[0], 1e-9) / 1e6, 1)} for k, v in timers.items()}
     comp = timers.get("compaction_copy", [1.0, 0])
-    _emit("page_compaction", comp[1] / (comp[0] * 1e-3) / 1e9, comp[0], {
+    lib.pkv_pool_destroy(pool)
+    return _result("page_compaction", comp[1] / (comp[0] * 1e-3) / 1e9, comp[0], {
         "config": {"workload": f"prefix churn: {N}-page pool, 43 layers (rows + MXFP4), 64 prefixes {lo}..{hi}, 8 forks + COW, 512-row appends, free 25 % LRU, compact"},
         "operations": ops, "pages_freed_lru": int(nfreed), "compaction_moves": int(moves), "cow_pages": int(cow_pairs),
         "compaction_host_ms": round(t_host * 1e3, 3), "bit_exact_check": {"ok": bool(ok), "what": "all 16 live sequences read back through their block tables after compaction, 3 layers"}})
-    lib.pkv_pool_destroy(pool)
 
 
 def run_sharded(args):

@@ -182,3 +182,76 @@ def test_fork_cow_evict_compact_on_device(pkv, cuda):
         st.check_readback(alive)
     finally:
         st.close()
+
+
+def test_migration_between_two_pools_on_one_device(pkv, cuda):
+    """Migration between shards, with both shards on ONE device: two page pools with their own layer pools (different
+    sizes, different base addresses), pkv_pool_migrate for the bookkeeping and pkv_copy_pages with src_base != dst_base
+    for the payload — the call a destination GPU makes on a peer's mapped pool. The destination's pools must equal the
+    oracle's orc_move_pages byte for byte, the migrated request read back through its NEW block table must equal what
+    was written to it on the source, and the source keeps working. Migration has no reference counterpart (parity
+    unpinned): this pins the stated rule."""
+    g = tl.rng(511)
+    a = Store(pkv, cuda, num_pages=96, slots=8, pps=40, layers=3, seed=5)
+    b = Store(pkv, cuda, num_pages=160, slots=8, pps=40, layers=3, seed=6)
+    try:
+        # the destination is already in use (its free list is not 0, 1, 2, ...), one of its sequences was released again
+        keepers = []
+        for n in (300, 77, 450):
+            h = pkv.pkv_pool_seq_open(b.pool)
+            assert pkv.pkv_pool_assign_slot(b.pool, h) >= 0
+            b.append([(h, n)])
+            keepers.append(h)
+        capi.check(pkv.pkv_pool_seq_close(b.pool, keepers.pop(1)))
+        movers, stay = [], []
+        for i, n in enumerate((1000, 64, 333, 129, 700)):
+            h = pkv.pkv_pool_seq_open(a.pool)
+            assert pkv.pkv_pool_assign_slot(a.pool, h) >= 0
+            a.append([(h, n)])
+            (movers if i % 2 == 0 else stay).append(h)
+        a.check_pools()
+        b.check_pools()
+        arrived = []
+        for h in movers:
+            npages = pkv.pkv_pool_seq_pages(a.pool, h, None, 0)
+            src, dst, out = np.zeros(npages, np.int32), np.zeros(npages, np.int32), C.c_int(-1)
+            free_before = pkv.pkv_pool_free_count(a.pool)
+            m = pkv.pkv_pool_migrate(a.pool, h, b.pool, C.byref(out), ptr(src), ptr(dst), npages)
+            assert m == npages and pkv.pkv_pool_free_count(a.pool) == free_before + npages
+            nh = out.value
+            assert pkv.pkv_pool_assign_slot(b.pool, nh) >= 0
+            descs = (capi.PkvPoolDesc * (2 * a.L))()
+            for l in range(a.L):
+                descs[2 * l].src_base, descs[2 * l].dst_base = a.d_rows[l].data_ptr(), b.d_rows[l].data_ptr()
+                descs[2 * l].page_bytes = tl.PAGE_BYTES
+                descs[2 * l + 1].src_base, descs[2 * l + 1].dst_base = a.d_fp4[l].data_ptr(), b.d_fp4[l].data_ptr()
+                descs[2 * l + 1].page_bytes = tl.FP4_PAGE_BYTES
+                orc.move_pages(a.h_rows[l], b.h_rows[l], tl.PAGE_BYTES, src, dst)
+                orc.move_pages(a.h_fp4[l], b.h_fp4[l], tl.FP4_PAGE_BYTES, src, dst)
+            d_s, d_d = tl.dev(cuda, src), tl.dev(cuda, dst)
+            capi.check(pkv.pkv_copy_pages(descs, 2 * a.L, d_s.data_ptr(), d_d.data_ptr(), npages, a.N, b.N, tl.stream_ptr(cuda)))
+            cuda.cuda.synchronize()
+            b.content[nh], b.length[nh] = a.content.pop(h), a.length.pop(h)
+            arrived.append(nh)
+        a.check_pools()                       # the source pools are only read
+        b.check_pools()                       # destination == oracle mirror, every byte of every layer
+        b.check_readback(arrived + keepers)   # through the new owner's block table
+        a.check_readback(stay)
+        # both shards keep working: the migrated requests decode on, the source reuses the pages that left
+        b.append([(h, 70) for h in arrived])
+        h = pkv.pkv_pool_seq_open(a.pool)
+        assert pkv.pkv_pool_assign_slot(a.pool, h) >= 0
+        a.append([(h, 900)])
+        b.check_pools()
+        a.check_pools()
+        b.check_readback(arrived)
+        a.check_readback(stay + [h])
+        # ids beyond either pool are reported by the kernel, not dereferenced
+        bad_s, bad_d = tl.dev(cuda, np.array([a.N + 3], np.int32)), tl.dev(cuda, np.array([2], np.int32))
+        capi.check(pkv.pkv_copy_pages(descs, 2 * a.L, bad_s.data_ptr(), bad_d.data_ptr(), 1, a.N, b.N, tl.stream_ptr(cuda)))
+        assert pkv.pkv_stream_check(tl.stream_ptr(cuda)) == capi.PKV_ERR_DEVICE and b"page id out of range" in pkv.pkv_last_error()
+        assert pkv.pkv_stream_check(tl.stream_ptr(cuda)) == capi.PKV_OK      # the record was cleared
+        b.check_pools()
+    finally:
+        a.close()
+        b.close()
