@@ -724,6 +724,7 @@ def measure_churn(args):
     step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
     step.tables, step.max_slots = d_tables.data_ptr(), slots
     timers = {}
+    append_variant = capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0
 
     def timed(name, fn, nbytes):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -758,7 +759,7 @@ def measure_churn(args):
 
         def go():
             for l in range(L):
-                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4, sp))
+                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | append_variant, sp))
 
         def go_one_launch():   # the same rows of all 43 layers in ONE launch (possible where every layer's rows exist up front)
             capi.check(lib.pkv_step_run(C.byref(step), lptr[0], L, capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_VARIANT_BULK, sp))

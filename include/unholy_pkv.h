@@ -48,7 +48,11 @@ PKV_API int pkv_abi_version(void);
  * launch on/off; 3: CTAs per SM of the vector kernels; 4: appends as tiles of the bulk launch on/off; 5: tiles whose
  * addresses are resolved together (-1 = by launch size, 0 = a warp's worth); 6: resolve the next batch late (0/1);
  * 7: top-k path (0 = one thread-block-cluster launch where the shape allows it, 1 = always the four launches that use
- * the scratch). The defaults come from PKV_* environment variables. */
+ * the scratch); 8: which bulk pipeline runs a step (-1 = by launch shape, 0 = the single-warp kernel, 1 = the
+ * warp-specialised kernel); 9: polls, of up to a microsecond each, before a device-side wait of the warp-specialised
+ * kernel gives up and reports kind 3 (0 = the default, about two seconds). The defaults come from PKV_* environment
+ * variables. Knob 10 is a test hook, not a performance knob: CTA 0 of the warp-specialised kernel expects 16 bytes more
+ * than its tile number `value` brings (-1 = off), so that its wait runs out without anything being wrong on the GPU. */
 PKV_API int pkv_tune(int knob, int value);
 
 /* First failed device-side check since the last call (0 = none): bit 0..7 = kind (1 page id out of range,

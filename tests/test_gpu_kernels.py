@@ -186,6 +186,22 @@ def test_gather_rows_single_table(pkv, cuda):
     assert np.array_equal(tl.host(d_out, np.uint16, want.shape), want)
 
 
+# The bulk variant has two kernels (a single-warp pipeline and a warp-specialised one, chosen by launch shape): the tests
+# force each in turn through pkv_tune knob 8, encoded here as two extra bits on the variant flag.
+BULK_SINGLE_WARP = capi.PKV_VARIANT_BULK | (1 << 20)
+BULK_SPECIALISED = capi.PKV_VARIANT_BULK | (1 << 21)
+VARIANTS = pytest.mark.parametrize("variant", [0, BULK_SINGLE_WARP, BULK_SPECIALISED], ids=["vec", "bulk-single-warp", "bulk-specialised"])
+
+
+def launch_step(pkv, step, layers, L, flags, stream):
+    pipe = 0 if flags & (1 << 20) else 1 if flags & (1 << 21) else -1
+    capi.check(pkv.pkv_tune(8, pipe))
+    try:
+        capi.check(pkv.pkv_step_run(C.byref(step), layers, L, flags & ~(3 << 20), stream))
+    finally:
+        capi.check(pkv.pkv_tune(8, -1))
+
+
 def run_step(pkv, cuda, case, L, flags, fp8_block=64, poison=True):
     """Runs pkv_step_run over L layers that share the case's tables but own their pools, rows, keys and index lists
     (layer l's inputs are the case's rotated by l). Returns per-layer device results as numpy arrays."""
@@ -211,7 +227,7 @@ def run_step(pkv, cuda, case, L, flags, fp8_block=64, poison=True):
         y.idx, y.gathered = d["idx"].data_ptr(), d["out"].data_ptr()
         keep.append(d)
         per_layer.append((inp, d))
-    capi.check(pkv.pkv_step_run(C.byref(step), layers, L, flags, tl.stream_ptr(cuda)))
+    launch_step(pkv, step, layers, L, flags, tl.stream_ptr(cuda))
     cuda.cuda.synchronize()
     assert tl.device_status(pkv) == 0
     return per_layer
@@ -244,7 +260,7 @@ def check_step(case, per_layer, flags, fp8_block=64):
 ALL = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_KEYS_FP8 | capi.PKV_DO_GATHER
 
 
-@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+@VARIANTS
 def test_step_config1(pkv, cuda, variant):
     """Benchmark configuration 1: 8 sequences of 1024..8192 rows over a 1024-page pool, one appended row each, then a
     2048-entry gather per sequence (-1 padded), all in one launch; every byte against the oracle."""
@@ -252,7 +268,7 @@ def test_step_config1(pkv, cuda, variant):
     check_step(case, run_step(pkv, cuda, case, 1, ALL | variant), ALL)
 
 
-@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+@VARIANTS
 def test_step_layers_and_prefill_chunks(pkv, cuda, variant):
     """Several layers in one launch, chunks of different lengths (decode rows and prefill chunks that cross pages),
     a row stride wider than the row, index lists that include the rows being appended."""
@@ -267,7 +283,7 @@ def test_step_layers_and_prefill_chunks(pkv, cuda, variant):
         check_step(case, run_step(pkv, cuda, case, 3, ALL | variant, fp8_block), ALL, fp8_block)
 
 
-@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+@VARIANTS
 def test_gather_only_and_append_only(pkv, cuda, variant):
     case = tl.PagedCase(seed=3, nseq=4, len_lo=64, len_hi=700, num_pages=64, k=96)
     check_step(case, run_step(pkv, cuda, case, 2, capi.PKV_DO_GATHER | variant), capi.PKV_DO_GATHER)
@@ -275,7 +291,7 @@ def test_gather_only_and_append_only(pkv, cuda, variant):
                capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4)
 
 
-@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+@VARIANTS
 def test_gather_ragged_k(pkv, cuda, variant):
     """k that is not a multiple of the tile, fully masked queries, a query with nothing visible."""
     case = tl.PagedCase(seed=4, nseq=3, len_lo=10, len_hi=90, num_pages=16, k=77)
@@ -299,6 +315,48 @@ def test_bad_page_id_is_reported_not_dereferenced(pkv, cuda):
     status = tl.device_status(pkv)
     assert status & 0xFF == 1
     assert tl.device_status(pkv) == 0  # reading clears it
+
+
+def test_bounded_wait_gives_up_and_the_library_keeps_working(pkv, cuda):
+    """The only device-side waits are mbarrier waits with a poll limit. Made to run out WITHOUT anything going wrong on
+    the GPU: the test hook (pkv_tune knob 10) makes CTA 0 of the warp-specialised kernel expect 16 bytes more than its
+    first tile brings, and knob 9 shortens the limit to a few milliseconds. The kernel must return, the status word
+    must say "bounded wait gave up" (kind 3), pkv_stream_check must return PKV_ERR_DEVICE, and the next launch must
+    produce exact results again."""
+    case = tl.PagedCase(seed=8, nseq=4, len_lo=200, len_hi=900, num_pages=128, k=256)
+    flags = capi.PKV_DO_ROWS | capi.PKV_DO_KEYS_FP4 | capi.PKV_DO_GATHER
+    try:
+        capi.check(pkv.pkv_tune(9, 4000))     # polls of at most a microsecond each
+        capi.check(pkv.pkv_tune(10, 0))       # CTA 0, its first tile
+        run = lambda: run_step(pkv, cuda, case, 1, flags | BULK_SPECIALISED)
+        with pytest.raises(AssertionError):   # run_step asserts a clean status word
+            run()
+    finally:
+        capi.check(pkv.pkv_tune(10, -1))
+        capi.check(pkv.pkv_tune(9, 0))
+    assert tl.device_status(pkv) == 0         # ... which run_step's own status read has cleared
+    # the same again in the steady-state loop of a CTA with several tiles, read through the stream-ordered check
+    case = tl.PagedCase(seed=9, nseq=4, len_lo=2100, len_hi=4000, num_pages=512, k=2048)
+    d_tables, d_chunks = tl.dev(cuda, case.tables), tl.dev(cuda, case.chunks)
+    d_qchunk, d_qvis = tl.dev(cuda, case.q_chunk), tl.dev(cuda, case.q_visible)
+    step = tl.make_step(case, d_tables, d_chunks, d_qchunk, d_qvis)
+    layers = tl.make_layers(1)
+    d_pool, d_idx = tl.dev(cuda, case.pool), tl.dev(cuda, case.idx)
+    d_out = cuda.zeros(case.idx.shape[0] * case.k * case.width * 2, dtype=cuda.uint8, device="cuda")
+    layers[0].row_pool, layers[0].idx, layers[0].gathered = d_pool.data_ptr(), d_idx.data_ptr(), d_out.data_ptr()
+    try:
+        capi.check(pkv.pkv_tune(9, 4000))
+        capi.check(pkv.pkv_tune(10, 2))       # CTA 0's third tile
+        capi.check(pkv.pkv_tune(1, 2))        # two CTAs per SM: 1024 tiles over 296 CTAs
+        launch_step(pkv, step, layers, 1, capi.PKV_DO_GATHER | BULK_SPECIALISED, tl.stream_ptr(cuda))
+        assert pkv.pkv_stream_check(tl.stream_ptr(cuda)) == capi.PKV_ERR_DEVICE
+        assert b"bounded wait gave up" in pkv.pkv_last_error()
+    finally:
+        capi.check(pkv.pkv_tune(10, -1))
+        capi.check(pkv.pkv_tune(9, 0))
+        capi.check(pkv.pkv_tune(1, 0))
+    assert pkv.pkv_stream_check(tl.stream_ptr(cuda)) == capi.PKV_OK
+    check_step(case, run_step(pkv, cuda, case, 1, flags | BULK_SPECIALISED), flags)   # the context is intact
 
 
 def test_copy_pages(pkv, cuda):
@@ -329,7 +387,7 @@ def test_repeat_is_stable(pkv, cuda):
     identical bytes every time."""
     case = tl.PagedCase(seed=6, nseq=4, len_lo=500, len_hi=3000, num_pages=256, k=512)
     first = None
-    for variant in (0, capi.PKV_VARIANT_BULK):
+    for variant in (0, BULK_SINGLE_WARP, BULK_SPECIALISED):
         for _ in range(3):
             per_layer = run_step(pkv, cuda, case, 2, ALL | variant)
             sig = [tl.host(d[k], np.uint8).tobytes() for _, d in per_layer for k in ("pool", "fp4", "codes", "scales", "out")]
@@ -338,7 +396,7 @@ def test_repeat_is_stable(pkv, cuda):
             assert sig == first
 
 
-@pytest.mark.parametrize("variant", [0, capi.PKV_VARIANT_BULK])
+@VARIANTS
 def test_config3_chunked_prefill(pkv, cuda, variant):
     """Benchmark configuration 3, reduced: one sequence grows in chunks (the first short, then 4096 rows each) over
     freshly allocated non-contiguous pages; every chunk appends bf16 rows with 1 % outliers at +-20 and quantises its
@@ -401,7 +459,7 @@ def test_config3_chunked_prefill(pkv, cuda, variant):
             orc.store_rows_fp4_chunks(keys, h_fp4[l], tables, rpp, chunks)
             orc.store_rows_fp8_chunks(keys, 64, h_codes[l], h_scales[l], tables, rpp, chunks)
             wants.append(orc.gather_rows(h_pool[l], tables, rpp, W, W, idx, np.zeros(8, np.int32), q_visible))
-        capi.check(pkv.pkv_step_run(C.byref(step), layers, L, ALL | variant, tl.stream_ptr(cuda)))
+        launch_step(pkv, step, layers, L, ALL | variant, tl.stream_ptr(cuda))
         cuda.cuda.synchronize()
         assert tl.device_status(pkv) == 0
         for l in range(L):

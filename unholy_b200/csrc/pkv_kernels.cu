@@ -99,6 +99,9 @@ struct Tuning {
   int fuse = env_int("PKV_BULK_FUSE", 1);                // the bulk launch carries the step's appends itself
   int batch = env_int("PKV_BULK_BATCH", -1);             // tiles resolved together (0: a full warp's worth; -1: by launch size)
   int resolve_late = env_int("PKV_BULK_RESOLVE_LATE", 0);
+  int pipe = env_int("PKV_PIPE", -1);                    // warp-specialised pipeline: 1 always, 0 never, -1 by launch shape
+  int wait_polls = env_int("PKV_WAIT_POLLS", 1 << 21);   // polls (of up to 1 us each) before a device-side wait gives up
+  int debug_tile = -1;                                   // test hook: CTA 0 over-states the bytes this tile expects
 };
 Tuning& tuning() {
   static Tuning t;
@@ -207,6 +210,8 @@ struct StepParams {
   int resolve_late;  // resolve the next batch when the LAST tile of the current one is issued (else the first)
   int gather_tiles;  // per layer
   int tiles_per_q;
+  int wait_polls;    // polls before a bounded wait gives up (pipe kernel)
+  int debug_tile;    // >= 0: CTA 0 expects 16 bytes more than this tile brings, so its wait runs out (test hook)
   pkv_layer layers[PKV_MAX_LAYERS];
 };
 
@@ -433,6 +438,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// The same with a time limit (nanoseconds) up to which the hardware may keep the thread suspended: the thread wakes as
+// soon as the phase completes, so a loop of these neither spins hot nor oversleeps the way polling with nanosleep does.
+__device__ __forceinline__ uint32_t mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok;
 }
@@ -684,6 +700,312 @@ __global__ void __launch_bounds__(32) step_bulk_kernel(const __grid_constant__ S
     for (int jj = j_fail; jj < mine && jj <= j_fail + ahead; ++jj) {
       const uint32_t bar = smem_addr(&bars[st2]);
       for (int spin = 0; spin < (1 << 18); ++spin) {
+        if (mbar_try_wait(bar, par2)) break;
+        __nanosleep(256);
+      }
+      if (++st2 == STAGES) st2 = 0, par2 ^= 1u;
+    }
+  }
+  bulk_wait_all();
+  __syncwarp();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The bulk pipeline with warp-specialised CTAs. A tile is ROWS rows: an append tile (ROWS batch rows of new KV rows,
+// contiguous in the source, one bulk store per page-contiguous run) or a gather tile (ROWS index entries of one query,
+// one bulk load per row, one bulk store of the contiguous tile). Tiles are dealt round-robin to CTAs.
+//   warp 0, the mover:     streams its CTA's tiles through the ring of STAGES shared-memory stages (loads of
+//                          STAGES - 2 tiles in flight while up to two tiles drain). It computes a tile's kind and
+//                          position itself (arithmetic only) and never loads an index, a chunk or a table entry;
+//   warps 1..kResWarps, the resolvers: run the dependent loads (index entry -> chunk -> block-table entry) for 32 rows
+//                          at a time, one lane per row, taking batches in turn and staying up to kResBatches batches
+//                          ahead of the mover, into a shared-memory ring (a chain is three memory latencies long: one
+//                          warp alone resolves more slowly than the mover moves); the mover picks a row's source
+//                          pointer or pool row up when it needs it (a gather tile when its loads are issued, an append
+//                          tile only when it is stored);
+//   the other warps, key workers (launched only when the step quantises keys): take pairs of key rows grid-wide with plain
+//                          16-byte loads, 16 lanes per row, and write codes and scales; independent of the ring.
+// Every wait (mbarrier) is bounded: after P.wait_polls polls the waiting warp records kind 3 in the status word, raises
+// the CTA's abort flag and the CTA winds down (loads in flight get a second bounded chance to land).
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kResWarps = 1;
+constexpr int kResBatches = 3;
+constexpr int kKeyWarps = 4;
+constexpr int kKeyUnroll = 2;  // units (pairs of key rows) a key worker has in flight
+constexpr int kFirstKeyWarp = 1 + kResWarps;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int STAGES, int ROWS>
+__global__ void __launch_bounds__(32 * (kFirstKeyWarp + kKeyWarps)) step_pipe_kernel(const __grid_constant__ StepParams P) {
+  static_assert(ROWS <= 32 && ROWS % 2 == 0 && 32 % ROWS == 0 && STAGES >= 3, "one lane per row; two stages drain while the others fill");
+  constexpr int kBatch = 32 / ROWS;  // tiles per resolved batch
+  static_assert(STAGES - 2 <= (kResBatches - 1) * kBatch, "the mover may not issue further ahead than the resolver's ring reaches");
+  constexpr unsigned long long kNoRow = ~0ull;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[STAGES];
+  __shared__ __align__(8) unsigned long long res_full[kResBatches], res_empty[kResBatches];
+  __shared__ unsigned long long s_res[kResBatches][32];  // per row: gather source pointer (0: masked) or pool row (kNoRow: none)
+  __shared__ int s_abort;
+  const pkv_step& s = P.s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row_bytes = uint32_t(s.width) * 2u, stage_bytes = row_bytes * ROWS;
+  const unsigned tiles_per_q = unsigned(s.k + ROWS - 1) / ROWS;
+  const unsigned app_tiles = unsigned(P.append_tiles);
+  const unsigned per_layer = app_tiles + unsigned(s.Q) * tiles_per_q;
+  const unsigned total = per_layer * unsigned(P.L);  // the host keeps this below 2^31
+  const unsigned first = blockIdx.x, stride = gridDim.x;
+  const int mine = first < total ? int((total - first + stride - 1) / stride) : 0;
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) mbar_init(smem_addr(&bars[i]), 1);
+#pragma unroll
+    for (int i = 0; i < kResBatches; ++i) {
+      mbar_init(smem_addr(&res_full[i]), 1);
+      mbar_init(smem_addr(&res_empty[i]), 1);
+    }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // Programmatic dependent launch: nothing above touches global memory; everything below waits for the previous
+  // kernel of the stream to have completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  volatile int* abort_flag = &s_abort;
+  auto wait_bounded = [&](uint32_t bar, uint32_t parity, int tag) -> bool {
+    for (int spin = 0; spin < P.wait_polls; ++spin) {  // each poll may stay suspended for up to a microsecond
+      if (mbar_try_wait_for(bar, parity, 1000u)) return true;
+      if ((spin & 255) == 255 && *abort_flag) return false;
+    }
+    report(3, tag);
+    *abort_flag = 1;
+    return false;
+  };
+  // Position of tile w in the launch: (layer, offset in the layer); offsets below app_tiles are append tiles.
+  auto advance = [&](unsigned& layer, unsigned& local, unsigned by) {
+    local += by;
+    while (local >= per_layer) {
+      local -= per_layer;
+      ++layer;
+    }
+  };
+
+  if (warp >= kFirstKeyWarp) {
+    // ---- key workers ----
+    const bool fp4 = (P.flags & PKV_DO_KEYS_FP4) != 0, fp8 = (P.flags & PKV_DO_KEYS_FP8) != 0;
+    if (!P.key_tiles || !(fp4 || fp8)) return;
+    const bool rotate = (P.flags & PKV_KEYS_HADAMARD) != 0;
+    const unsigned upl = unsigned(s.T + 1) / 2, units = upl * unsigned(P.L);  // a unit = two key rows of one layer
+    const unsigned nworkers = gridDim.x * unsigned(blockDim.x / 32 - kFirstKeyWarp);
+    const int j = lane & 15;
+    for (unsigned u0 = blockIdx.x * unsigned(blockDim.x / 32 - kFirstKeyWarp) + unsigned(warp - kFirstKeyWarp); u0 < units;
+         u0 += kKeyUnroll * nworkers) {
+      // kKeyUnroll units per pass: all their key loads and address chains are in flight before the arithmetic starts
+      uint4 raw[kKeyUnroll];
+      long long rid[kKeyUnroll];
+      unsigned layer[kKeyUnroll];
+#pragma unroll
+      for (int i = 0; i < kKeyUnroll; ++i) {
+        const unsigned u = u0 + unsigned(i) * nworkers;
+        rid[i] = -1;
+        raw[i] = make_uint4(0, 0, 0, 0);
+        layer[i] = 0;
+        if (u < units) {
+          layer[i] = u / upl;
+          const int r = int(u - layer[i] * upl) * 2 + (lane >> 4);
+          if (r < s.T) {
+            raw[i] = ld_stream(reinterpret_cast<const uint4*>(P.layers[layer[i]].keys + size_t(r) * PKV_FP4_ROW_DIM) + j);
+            const int c = find_chunk(s.chunks, s.nchunks, r);
+            if (c >= 0) {
+              const pkv_chunk ch = s.chunks[c];
+              rid[i] = physical_row(s, ch.slot, ch.s0 + (r - ch.t0), r);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kKeyUnroll; ++i) {
+        if (u0 + unsigned(i) * nworkers >= units) break;  // (uniform across the warp)
+        const pkv_layer& ly = P.layers[layer[i]];
+        float v[8];
+        pkv::unpack8(raw[i], v);
+        quantise_key_row(s, ly, v, rid[i], j, fp4 && ly.key_pool_fp4, fp8 && ly.key_fp8_codes && ly.key_fp8_scales, rotate);
+      }
+    }
+    return;
+  }
+
+  if (warp >= 1) {
+    // ---- resolver `warp - 1`: batches b = warp - 1, warp - 1 + kResWarps, ...; batch b = this CTA's tiles
+    //      [b * kBatch, (b + 1) * kBatch), lane = (tile in batch, row in tile) ----
+    const int sub = lane / ROWS, r_in = lane % ROWS;
+    unsigned cl = 0, cloc = 0;
+    if (mine > 0) {
+      const unsigned w = first + unsigned((warp - 1) * kBatch + sub) * stride;  // one division per kernel, not per tile
+      cl = w / per_layer;
+      cloc = w - cl * per_layer;
+    }
+    const int nb = (mine + kBatch - 1) / kBatch;
+    for (int b = warp - 1; b < nb; b += kResWarps) {
+      const int slot = b % kResBatches;
+      if (b >= kResBatches) {  // the mover has finished with the batch that used this slot
+        const bool ok = wait_bounded(smem_addr(&res_empty[slot]), uint32_t((b / kResBatches - 1) & 1), int(blockIdx.x));
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      unsigned long long v = 0;
+      if (b * kBatch + sub < mine) {
+        const pkv_layer& ly = P.layers[cl];
+        if (cloc >= app_tiles) {
+          const unsigned g = cloc - app_tiles;
+          const unsigned q = P.tpq_shift >= 0 ? g >> P.tpq_shift : g / tiles_per_q;
+          const unsigned e0 = (g - q * tiles_per_q) * ROWS;
+          v = reinterpret_cast<unsigned long long>(gather_source(P, ly, int(q), int(e0) + r_in));
+        } else {
+          const int row = int(cloc) * ROWS + r_in;
+          long long rid = -1;
+          if (row < s.T) {
+            const int c = find_chunk(s.chunks, s.nchunks, row);
+            if (c >= 0) {
+              const pkv_chunk ch = s.chunks[c];
+              rid = physical_row(s, ch.slot, ch.s0 + (row - ch.t0), row);
+            }
+          }
+          v = rid < 0 ? kNoRow : static_cast<unsigned long long>(rid);
+        }
+        advance(cl, cloc, unsigned(kResWarps * kBatch) * stride);
+      }
+      s_res[slot][lane] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&res_full[slot]));
+    }
+    return;
+  }
+
+  // ---- mover ----
+  struct Tile {
+    unsigned layer, local;
+  };
+  __shared__ Tile s_tile[STAGES];
+  unsigned il = 0, iloc = 0;  // position of the next tile to issue
+  if (mine > 0) {
+    il = first / per_layer;
+    iloc = first - il * per_layer;
+  }
+  int ready = 0, issued = 0;  // batches known to be resolved; tiles whose loads were started
+  bool alive = true;
+  auto ensure = [&](int b) {
+    while (alive && ready <= b) {
+      alive = __all_sync(0xffffffffu, wait_bounded(smem_addr(&res_full[ready % kResBatches]), uint32_t((ready / kResBatches) & 1), int(blockIdx.x)));
+      ++ready;
+    }
+  };
+  // Starts the loads of tile j into stage st.
+  auto issue = [&](int j, int st) {
+    const unsigned layer = il, local = iloc;
+    advance(il, iloc, stride);
+    const pkv_layer& ly = P.layers[layer];
+    unsigned char* stage = smem + size_t(st) * stage_bytes;
+    const uint32_t bar = smem_addr(&bars[st]);
+    const uint32_t extra = (P.debug_tile == j && blockIdx.x == 0) ? 16u : 0u;
+    if (lane == 0) s_tile[st] = Tile{layer, local};
+    if (local >= app_tiles) {
+      ensure(j / kBatch);
+      if (!alive) return;
+      const unsigned long long rv = lane < ROWS ? s_res[(j / kBatch) % kResBatches][(j % kBatch) * ROWS + lane] : 0ull;
+      const uint4* src = reinterpret_cast<const uint4*>(rv);
+      const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
+      if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(valid)) * row_bytes + extra);
+      // Masked rows (and rows past k, which are never stored) are zero-filled by the whole warp, one row at a time.
+      unsigned masked = ~valid & (ROWS == 32 ? 0xffffffffu : ((1u << ROWS) - 1u));
+      while (masked) {
+        const int r = __ffs(masked) - 1;
+        masked &= masked - 1;
+        uint4* z = reinterpret_cast<uint4*>(stage + size_t(r) * row_bytes);
+        for (uint32_t i = lane; i < row_bytes / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+      if (src) bulk_load(smem_addr(stage + size_t(lane) * row_bytes), src, row_bytes, bar);
+    } else {
+      // Batch rows [a, a + nrows): one load of the contiguous source; where the rows go is looked up when they are stored.
+      const int a = int(local) * ROWS, nrows = min(ROWS, s.T - a);
+      if (lane == 0) {
+        mbar_expect_tx(bar, uint32_t(nrows) * row_bytes + extra);
+        bulk_load(smem_addr(stage), reinterpret_cast<const unsigned char*>(ly.rows) + size_t(a) * row_bytes, uint32_t(nrows) * row_bytes, bar);
+      }
+      __syncwarp();
+    }
+    ++issued;
+  };
+
+  constexpr int ahead = STAGES - 2;
+  int st_issue = 0;
+  for (int j = 0; j < ahead && j < mine && alive; ++j) {
+    issue(j, st_issue);
+    st_issue = st_issue + 1 == STAGES ? 0 : st_issue + 1;
+  }
+  int j_done = 0, st = 0;
+  uint32_t parity = 0;
+  for (int j = 0; j < mine && alive; ++j) {
+    // The stage tile j + ahead goes into was drained by tile j - 2; its stores must have finished reading shared memory
+    // (every lane waits on its own bulk groups: append tiles are stored by several lanes).
+    if (j + ahead < mine) {
+      bulk_wait_read<1>();
+      __syncwarp();
+      issue(j + ahead, st_issue);
+      if (!alive) break;
+      st_issue = st_issue + 1 == STAGES ? 0 : st_issue + 1;
+    }
+    alive = __all_sync(0xffffffffu, wait_bounded(smem_addr(&bars[st]), parity, int(blockIdx.x)));
+    if (!alive) break;
+    const Tile t = s_tile[st];
+    const pkv_layer& ly = P.layers[t.layer];
+    unsigned char* stage = smem + size_t(st) * stage_bytes;
+    if (t.local >= app_tiles) {
+      const unsigned g = t.local - app_tiles;
+      const unsigned q = P.tpq_shift >= 0 ? g >> P.tpq_shift : g / tiles_per_q;
+      const unsigned e0 = (g - q * tiles_per_q) * ROWS;
+      const int nrows = min(ROWS, s.k - int(e0));
+      fence_async_smem();  // the zero rows were written through the generic proxy
+      __syncwarp();
+      if (lane == 0) bulk_store(ly.gathered + (size_t(q) * s.k + e0) * s.width, smem_addr(stage), uint32_t(nrows) * row_bytes);
+    } else {
+      ensure(j / kBatch);
+      if (!alive) break;
+      const int a = int(t.local) * ROWS, nrows = min(ROWS, s.T - a);
+      // Runs of rows that are contiguous in the pool leave with one bulk store each.
+      const unsigned long long rv = lane < nrows ? s_res[(j / kBatch) % kResBatches][(j % kBatch) * ROWS + lane] : kNoRow;
+      const long long rid = rv == kNoRow ? -1 : static_cast<long long>(rv);
+      const long long prev = __shfl_up_sync(0xffffffffu, rid, 1);
+      const bool start = rid >= 0 && (lane == 0 || prev < 0 || rid != prev + 1 || s.row_stride != s.width);
+      const unsigned breaks = __ballot_sync(0xffffffffu, start || rid < 0);
+      if (start) {
+        const unsigned higher = lane == 31 ? 0u : (breaks & ~((2u << lane) - 1u));
+        const int next = higher ? __ffs(higher) - 1 : 32;
+        bulk_store(ly.row_pool + size_t(rid) * s.row_stride, smem_addr(stage + size_t(lane) * row_bytes), uint32_t(next - lane) * row_bytes);
+      }
+    }
+    bulk_commit();
+    __syncwarp();
+    if (j % kBatch == kBatch - 1 && lane == 0) mbar_arrive(smem_addr(&res_empty[(j / kBatch) % kResBatches]));
+    j_done = j + 1;
+    if (++st == STAGES) {
+      st = 0;
+      parity ^= 1u;
+    }
+  }
+  if (!alive) {
+    // Gave up: the loads of the tiles already started get a second, bounded chance to land before the CTA's shared
+    // memory is released.
+    int st2 = st;
+    uint32_t par2 = parity;
+    const int polls = min(P.wait_polls, 1 << 18);
+    for (int jj = j_done; jj < issued; ++jj) {
+      const uint32_t bar = smem_addr(&bars[st2]);
+      for (int spin = 0; spin < polls; ++spin) {
         if (mbar_try_wait(bar, par2)) break;
         __nanosleep(256);
       }
@@ -1172,6 +1494,90 @@ int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t 
   }
 }
 
+
+template <int STAGES, int ROWS>
+int launch_pipe(const StepParams& P0, int ctas_per_sm, cudaStream_t st) {
+  StepParams P = P0;
+  P.wait_polls = std::max(1, tuning().wait_polls);
+  P.debug_tile = tuning().debug_tile;
+  P.append_tiles = P0.append_tiles ? (P.s.T + ROWS - 1) / ROWS : 0;
+  const bool keys = P0.key_tiles != 0;
+  // Key workers per CTA: two when a CTA's share of the key rows is small (a chunk of one layer), kKeyWarps when it is
+  // large (many layers per launch): each worker runs its address chains one after the other.
+  const long long key_units = keys ? (long long)P.L * ((P.s.T + 1) / 2) : 0;
+  const int key_warps = !keys ? 0 : (key_units > 8ll * 148 * 7 ? kKeyWarps : 2);
+  const int threads = 32 * (kFirstKeyWarp + key_warps);
+  const size_t smem = size_t(STAGES) * ROWS * size_t(P.s.width) * 2u;
+  if (smem > 224u * 1024u) return fail(PKV_ERR_LIMIT, "pkv_step_run: rows too wide for the bulk pipeline");
+  static thread_local size_t opted[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48u * 1024u && dev >= 0 && dev < 64 && opted[dev] < smem) {
+    const cudaError_t e = cudaFuncSetAttribute(step_pipe_kernel<STAGES, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    opted[dev] = smem;
+  }
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  int per_sm = ctas_per_sm > 0 ? ctas_per_sm : int((227u * 1024u) / (smem + 2048u));
+  int resident = 0;  // registers may allow fewer CTAs than shared memory does
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, step_pipe_kernel<STAGES, ROWS>, threads, smem) == cudaSuccess && resident > 0)
+    per_sm = std::min(per_sm, resident);
+  per_sm = std::max(1, std::min({per_sm, 2048 / threads, 32}));
+  const int tpq = (P.s.k + ROWS - 1) / ROWS;
+  P.tpq_shift = -1;
+  for (int b = 0; b < 31; ++b)
+    if (tpq == (1 << b)) P.tpq_shift = b;
+  const long long tiles = (long long)P.L * ((long long)P.s.Q * tpq + P.append_tiles);
+  const long long key_ctas = keys ? (key_units + key_warps - 1) / key_warps : 0;
+  if (tiles == 0 && key_ctas == 0) return PKV_OK;
+  if (tiles >= (1ll << 31) - (1ll << 20)) return fail(PKV_ERR_LIMIT, "pkv_step_run: more than 2^31 tiles in one launch");
+  const int grid = int(std::max<long long>(1, std::min<long long>(std::max(tiles, key_ctas), (long long)sms * per_sm)));
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(unsigned(threads));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tuning().pdl ? 1 : 0;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, step_pipe_kernel<STAGES, ROWS>, P);
+  if (le != cudaSuccess) return fail_cuda("step_pipe_kernel launch", le);
+  return PKV_OK;
+}
+
+// Which of the two bulk pipelines takes a launch. A long run of gather tiles per CTA (a decode step over long contexts)
+// goes to the single-warp kernel: its CTAs are paced by their own address chains, finish within a few microseconds of
+// each other and the launch ends when the data does, while the free-running movers of the warp-specialised kernel end
+// up to 25 us apart on the same launch (measured on B200: 50.7 against 55.5 us per launch). Launches with few tiles per
+// CTA, long appends and key quantisation go to the warp-specialised kernel (prefill call 11.0 -> 9.0 us, 4096-row
+// appends of 43 layers in one launch 1.6 -> 3.3 TB/s).
+bool use_pipe(const StepParams& P) {
+  const int knob = tuning().pipe;
+  if (knob >= 0) return knob != 0;
+  const bool gather_heavy = (long long)P.s.Q * P.s.k >= 8ll * P.s.T;
+  return !(many_tiles_per_cta(P) && gather_heavy);
+}
+
+int dispatch_pipe(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t st) {
+  if (shape == 0) shape = 308;
+  switch (shape) {  // STAGES * 100 + ROWS
+    case 304: return launch_pipe<3, 4>(P, ctas_per_sm, st);
+    case 404: return launch_pipe<4, 4>(P, ctas_per_sm, st);
+    case 604: return launch_pipe<6, 4>(P, ctas_per_sm, st);
+    case 308: return launch_pipe<3, 8>(P, ctas_per_sm, st);
+    case 408: return launch_pipe<4, 8>(P, ctas_per_sm, st);
+    case 508: return launch_pipe<5, 8>(P, ctas_per_sm, st);
+    case 316: return launch_pipe<3, 16>(P, ctas_per_sm, st);
+    case 416: return launch_pipe<4, 16>(P, ctas_per_sm, st);
+    case 332: return launch_pipe<3, 32>(P, ctas_per_sm, st);
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled shape of the warp-specialised pipeline");
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -1190,6 +1596,9 @@ int pkv_tune(int knob, int value) {
     case 5: t.batch = value; return PKV_OK;
     case 6: t.resolve_late = value; return PKV_OK;
     case 7: pkv_g_topk_path = value; return PKV_OK;
+    case 8: t.pipe = value; return PKV_OK;
+    case 9: t.wait_polls = value > 0 ? value : 1 << 21; return PKV_OK;
+    case 10: t.debug_tile = value; return PKV_OK;
     default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
   }
 }
@@ -1389,7 +1798,7 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
       if (rows_on && (!B.layers[l].rows || !B.layers[l].row_pool)) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks rows or row_pool");
       if (keys_on && !B.layers[l].keys) return fail(PKV_ERR_ARG, "pkv_step_run: a layer lacks keys");
     }
-    return dispatch_bulk(B, bulk_shape, bulk_ctas, stream);
+    return use_pipe(B) ? dispatch_pipe(B, bulk_shape, bulk_ctas, stream) : dispatch_bulk(B, bulk_shape, bulk_ctas, stream);
   }
   P.append_tiles = append ? (s.T + kAppendRows - 1) / kAppendRows : 0;
   P.tiles_per_q = (s.k + kGatherRows - 1) / kGatherRows;
@@ -1409,7 +1818,7 @@ int pkv_step_run(const pkv_step* step, const pkv_layer* layers, int L, int flags
   if (bulk) {
     P.append_tiles = 0;
     P.key_tiles = 0;
-    return dispatch_bulk(P, bulk_shape, bulk_ctas, stream);
+    return use_pipe(P) ? dispatch_pipe(P, bulk_shape, bulk_ctas, stream) : dispatch_bulk(P, bulk_shape, bulk_ctas, stream);
   }
   return PKV_OK;
 }
