@@ -319,6 +319,73 @@ PKV_API int pkv_ipc_open(const unsigned char handle[64], void** ptr_out);
 PKV_API int pkv_ipc_close(void* ptr);
 
 /* ------------------------------------------------------------------------------------------------------------------
+ * The pool sharded over the GPUs of one box by request ownership, with migration between shards: a C++ host object
+ * (one process, one host thread and one stream per shard; no torch, no collective). The reference has no counterpart:
+ * its pools are per card and pages never move (its DESIGN.md:119-123,148-149); the ordering pattern — a pull kernel
+ * behind events — is that of src/engine/resident.hip:213-232,908-910. A shard owns `layers` bf16 row pools (and MXFP4
+ * key pools when key_pools != 0), one page pool (the allocator above) and one block table. Calls on one pkv_shards
+ * object must come from one thread at a time.
+ * ---------------------------------------------------------------------------------------------------------------- */
+typedef struct pkv_shards pkv_shards;
+typedef struct pkv_shard_config {
+  int32_t ngpus;             /* shards; devices[i] of pkv_shards_create is shard i's CUDA device (two shards may share one) */
+  int32_t num_pages;         /* pages per shard */
+  int32_t rows_per_page, width, row_stride;
+  int32_t layers;
+  int32_t max_slots, max_pages_per_seq;
+  int32_t k;                 /* index-list width of the steps */
+  int32_t key_pools;         /* != 0: every layer also has an MXFP4 key pool; its pages move with the row pages */
+} pkv_shard_config;
+typedef struct pkv_shard_io { /* one layer of one shard's step: device pointers on that shard's GPU */
+  const uint16_t* rows;      /* bf16 [Q][width]: the row each local request appends, in pkv_shards_local order */
+  const uint16_t* keys;      /* bf16 [Q][128] or NULL */
+  const int32_t* idx;        /* int32 [Q][k] */
+  uint16_t* gathered;        /* bf16 [Q][k][width] */
+} pkv_shard_io;
+/* Allocates every shard's pools, tables, streams and staging on its device and enables peer access between distinct
+ * devices once. NULL (pkv_last_error) on failure. */
+PKV_API pkv_shards* pkv_shards_create(const pkv_shard_config* cfg, const int* devices);
+PKV_API void pkv_shards_destroy(pkv_shards* s);
+/* A request of `length` rows owned by `shard` (round-robin ownership is request % ngpus, the caller's choice): takes a
+ * slot and pages from that shard's allocator. */
+PKV_API int pkv_shards_add(pkv_shards* s, int request, int shard, int length);
+PKV_API int pkv_shards_remove(pkv_shards* s, int request);
+PKV_API int pkv_shards_owner(const pkv_shards* s, int request);
+PKV_API int pkv_shards_length(const pkv_shards* s, int request);
+PKV_API int pkv_shards_slot(const pkv_shards* s, int request);
+/* The shard's requests that take part in steps, ascending: the order of the rows of pkv_shard_io. Returns the count. */
+PKV_API int pkv_shards_local(const pkv_shards* s, int shard, int32_t* requests_out, int cap);
+PKV_API int pkv_shards_free_pages(const pkv_shards* s, int shard);
+/* Device pointers of a shard (for filling pools and reading requests back with the single-sequence entry points) and
+ * its step stream (a cudaStream_t). pkv_shards_tables uploads the block table first if it changed; the upload is
+ * ordered on the step stream. */
+PKV_API void* pkv_shards_row_pool(pkv_shards* s, int shard, int layer);
+PKV_API void* pkv_shards_key_pool(pkv_shards* s, int shard, int layer);
+PKV_API const int32_t* pkv_shards_tables(pkv_shards* s, int shard);
+PKV_API void* pkv_shards_stream(pkv_shards* s, int shard);
+/* One decode step on every shard at once: each local request appends one row per layer at its length and gathers its
+ * k index entries (one pkv_step_run per layer on the shard's stream, issued by the shard's own host thread); lengths
+ * advance by one. io is [ngpus][layers]. Returns when every shard's launches are queued. */
+PKV_API int pkv_shards_step(pkv_shards* s, const pkv_shard_io* io);
+/* Timing on the device: pkv_shards_mark records event 0 / 1 on every shard's step stream, pkv_shards_elapsed_ms waits
+ * for events 1 and gives the milliseconds between the two per shard (ms_out [ngpus]). pkv_shards_sync waits for all
+ * streams of all shards. */
+PKV_API int pkv_shards_mark(pkv_shards* s, int which);
+PKV_API int pkv_shards_elapsed_ms(pkv_shards* s, float* ms_out);
+PKV_API int pkv_shards_sync(pkv_shards* s);
+/* Migration. begin: each request leaves its shard's steps at once; the destination takes pages from its own
+ * allocator (ids as alloc_pages gives them, logical order) and queues ONE pull of all layers' pages on its migration
+ * stream, behind an event that orders it after the steps already queued on the source. Other requests keep stepping on
+ * both shards meanwhile. end: for every pull whose event has completed (wait != 0: waits on the host for all of them)
+ * the source's pages are released, the destination's later steps are ordered behind the pull and the request joins
+ * the destination's steps; returns how many finished. stats: bytes moved and, per destination shard, the summed
+ * device time of the pull kernels alone (CUDA events on the migration stream). */
+PKV_API int pkv_shards_migrate_begin(pkv_shards* s, const int32_t* requests, const int32_t* dst_shards, int n);
+PKV_API int pkv_shards_migrate_end(pkv_shards* s, int wait);
+PKV_API int pkv_shards_migrate_pending(const pkv_shards* s);
+PKV_API int pkv_shards_migrate_stats(pkv_shards* s, double* bytes_out, float* kernel_ms_out);
+
+/* ------------------------------------------------------------------------------------------------------------------
  * Page pool: the block allocator, prefix-cache bookkeeping and block tables of src/engine/engine.{hpp,cpp}
  * (free_pages_/evictable_/page_by_hash_/page_info_/tables_: engine.hpp:258-306) as a host-side object, plus the
  * copy-on-write, LRU-free and compaction rules. Host only; single-threaded like the engine thread.

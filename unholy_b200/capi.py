@@ -49,6 +49,15 @@ class PkvTopkGroup(C.Structure):
     _fields_ = [("off", C.c_size_t), ("rows", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("idx_off", C.c_int32)]
 
 
+class PkvShardConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("ngpus", "num_pages", "rows_per_page", "width", "row_stride", "layers", "max_slots",
+                                         "max_pages_per_seq", "k", "key_pools")]
+
+
+class PkvShardIo(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("rows", "keys", "idx", "gathered")]
+
+
 class PkvPoolDesc(C.Structure):
     _fields_ = [("src_base", C.c_void_p), ("dst_base", C.c_void_p), ("page_bytes", C.c_uint64)]
 
@@ -90,6 +99,27 @@ _SIGS = {
     "pkv_ipc_export": (_i, [_vp, c_u8p]),
     "pkv_ipc_open": (_i, [c_u8p, C.POINTER(_vp)]),
     "pkv_ipc_close": (_i, [_vp]),
+    "pkv_shards_create": (_vp, [C.POINTER(PkvShardConfig), C.POINTER(C.c_int)]),
+    "pkv_shards_destroy": (None, [_vp]),
+    "pkv_shards_add": (_i, [_vp, _i, _i, _i]),
+    "pkv_shards_remove": (_i, [_vp, _i]),
+    "pkv_shards_owner": (_i, [_vp, _i]),
+    "pkv_shards_length": (_i, [_vp, _i]),
+    "pkv_shards_slot": (_i, [_vp, _i]),
+    "pkv_shards_local": (_i, [_vp, _i, c_i32p, _i]),
+    "pkv_shards_free_pages": (_i, [_vp, _i]),
+    "pkv_shards_row_pool": (_vp, [_vp, _i, _i]),
+    "pkv_shards_key_pool": (_vp, [_vp, _i, _i]),
+    "pkv_shards_tables": (_vp, [_vp, _i]),
+    "pkv_shards_stream": (_vp, [_vp, _i]),
+    "pkv_shards_step": (_i, [_vp, C.POINTER(PkvShardIo)]),
+    "pkv_shards_mark": (_i, [_vp, _i]),
+    "pkv_shards_elapsed_ms": (_i, [_vp, C.POINTER(C.c_float)]),
+    "pkv_shards_sync": (_i, [_vp]),
+    "pkv_shards_migrate_begin": (_i, [_vp, c_i32p, c_i32p, _i]),
+    "pkv_shards_migrate_end": (_i, [_vp, _i]),
+    "pkv_shards_migrate_pending": (_i, [_vp]),
+    "pkv_shards_migrate_stats": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_float)]),
     "pkv_pool_create": (_vp, [_i, _i, _i, _i, _i]),
     "pkv_pool_destroy": (None, [_vp]),
     "pkv_pool_seq_open": (_i, [_vp]),

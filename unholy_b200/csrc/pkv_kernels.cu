@@ -102,6 +102,7 @@ struct Tuning {
   int pipe = env_int("PKV_PIPE", -1);                    // warp-specialised pipeline: 1 always, 0 never, -1 by launch shape
   int wait_polls = env_int("PKV_WAIT_POLLS", 1 << 21);   // polls (of up to 1 us each) before a device-side wait gives up
   int debug_tile = -1;                                   // test hook: CTA 0 over-states the bytes this tile expects
+  int copy_bulk = env_int("PKV_COPY_BULK", 1);           // page moves inside a pool through the bulk-copy ring
 };
 Tuning& tuning() {
   static Tuning t;
@@ -1389,6 +1390,139 @@ __global__ void __launch_bounds__(256) copy_pages_kernel(const __grid_constant__
   }
 }
 
+// Page moves inside one device's pools (copy-on-write, compaction: src_base == dst_base for every pool) through the
+// bulk-copy engine: an item is one piece (at most kBulkPiece bytes) of one page of one pool; single-warp CTAs stride over
+// the items and keep a ring of STAGES pieces rotating (loads of STAGES - 2 pieces in flight while two drain). The
+// (source, destination) page ids of 32 items are looked up at a time, one lane per item, a batch ahead. Never used when
+// a source pool may belong to another device: bulk copies do not read peer memory in this library.
+constexpr unsigned kBulkPiece = 18432;  // a quarter of a 73,728-byte row page
+constexpr int kCopyStages = 4;
+struct PageCopyBulkParams {
+  int npools, n, num_src_pages, num_dst_pages;
+  int wait_polls;
+  const int32_t* src_ids;
+  const int32_t* dst_ids;
+  unsigned first_item[129];  // items before pool p; [npools] = all items
+  pkv_pool_desc pools[128];
+};
+__global__ void __launch_bounds__(32) copy_pages_bulk_kernel(const __grid_constant__ PageCopyBulkParams P) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[kCopyStages];
+  __shared__ const unsigned char* s_src[2][32];
+  __shared__ unsigned char* s_dst[2][32];
+  __shared__ unsigned s_bytes[2][32];
+  __shared__ unsigned char* s_stage_dst[kCopyStages];
+  __shared__ unsigned s_stage_bytes[kCopyStages];
+  const int lane = threadIdx.x;
+  const unsigned total = P.first_item[P.npools];
+  const unsigned first = blockIdx.x, stride = gridDim.x;
+  const int mine = first < total ? int((total - first + stride - 1) / stride) : 0;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < kCopyStages; ++i) mbar_init(smem_addr(&bars[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  auto resolve_batch = [&](int b) {
+    const int j = b * 32 + lane;
+    const unsigned char* src = nullptr;
+    unsigned char* dst = nullptr;
+    unsigned bytes = 0;
+    if (j < mine) {
+      const unsigned item = first + unsigned(j) * stride;
+      int lo = 0, hi = P.npools;  // the pool holding the item: last p with first_item[p] <= item
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (P.first_item[mid] <= item) lo = mid;
+        else hi = mid;
+      }
+      const pkv_pool_desc d = P.pools[lo];
+      const unsigned pieces = unsigned((d.page_bytes + kBulkPiece - 1) / kBulkPiece);
+      const unsigned rel = item - P.first_item[lo], pair = rel / pieces, piece = rel - pair * pieces;
+      const int sp = __ldg(&P.src_ids[pair]), dp = __ldg(&P.dst_ids[pair]);
+      if (unsigned(sp) >= unsigned(P.num_src_pages) || unsigned(dp) >= unsigned(P.num_dst_pages)) {
+        report(1, int(pair));
+      } else {
+        const size_t off = size_t(piece) * kBulkPiece;
+        bytes = unsigned(min(size_t(kBulkPiece), size_t(d.page_bytes) - off));
+        src = static_cast<const unsigned char*>(d.src_base) + size_t(sp) * d.page_bytes + off;
+        dst = static_cast<unsigned char*>(d.dst_base) + size_t(dp) * d.page_bytes + off;
+      }
+    }
+    s_src[b & 1][lane] = src;
+    s_dst[b & 1][lane] = dst;
+    s_bytes[b & 1][lane] = bytes;
+    __syncwarp();
+  };
+  auto issue = [&](int j, int st) {
+    if (lane == 0) {
+      const int slot = (j >> 5) & 1, i = j & 31;
+      const unsigned bytes = s_bytes[slot][i];
+      s_stage_dst[st] = s_dst[slot][i];
+      s_stage_bytes[st] = bytes;
+      const uint32_t bar = smem_addr(&bars[st]);
+      mbar_expect_tx(bar, bytes);  // zero bytes (a skipped item): the phase completes with the arrival alone
+      if (bytes) bulk_load(smem_addr(smem + size_t(st) * kBulkPiece), s_src[slot][i], bytes, bar);
+    }
+    __syncwarp();
+    if ((j & 31) == 0 && ((j >> 5) + 1) * 32 < mine) resolve_batch((j >> 5) + 1);
+  };
+  constexpr int ahead = kCopyStages - 2;
+  if (mine > 0) resolve_batch(0);
+  int st_issue = 0, issued = 0;
+  for (; issued < ahead && issued < mine; ++issued) {
+    issue(issued, st_issue);
+    st_issue = st_issue + 1 == kCopyStages ? 0 : st_issue + 1;
+  }
+  int st = 0, j = 0;
+  uint32_t parity = 0;
+  bool alive = true;
+  for (; j < mine; ++j) {
+    if (issued < mine) {
+      if (lane == 0) bulk_wait_read<1>();  // the stage about to be refilled was drained two items ago
+      __syncwarp();
+      issue(issued++, st_issue);
+      st_issue = st_issue + 1 == kCopyStages ? 0 : st_issue + 1;
+    }
+    const uint32_t bar = smem_addr(&bars[st]);
+    alive = false;
+    for (int spin = 0; spin < P.wait_polls; ++spin)
+      if (mbar_try_wait_for(bar, parity, 1000u)) {
+        alive = true;
+        break;
+      }
+    alive = __all_sync(0xffffffffu, alive);
+    if (!alive) {
+      report(3, int(blockIdx.x));
+      break;
+    }
+    if (lane == 0) {
+      if (s_stage_bytes[st]) bulk_store(s_stage_dst[st], smem_addr(smem + size_t(st) * kBulkPiece), s_stage_bytes[st]);
+      bulk_commit();
+    }
+    __syncwarp();
+    if (++st == kCopyStages) {
+      st = 0;
+      parity ^= 1u;
+    }
+  }
+  if (!alive) {  // the loads already started get a second, bounded chance to land before shared memory is released
+    const int polls = min(P.wait_polls, 1 << 18);
+    for (int jj = j; jj < issued; ++jj) {
+      const uint32_t bar = smem_addr(&bars[st]);
+      for (int spin = 0; spin < polls; ++spin) {
+        if (mbar_try_wait(bar, parity)) break;
+        __nanosleep(256);
+      }
+      if (++st == kCopyStages) st = 0, parity ^= 1u;
+    }
+  }
+  if (lane == 0) bulk_wait_all();
+  __syncwarp();
+}
+
 int grid_for(long long work_items, int threads, int per_sm) {
   const DeviceInfo& d = device_info();
   const long long cap = (long long)(d.ok ? d.sms : 148) * per_sm;
@@ -1599,6 +1733,7 @@ int pkv_tune(int knob, int value) {
     case 8: t.pipe = value; return PKV_OK;
     case 9: t.wait_polls = value > 0 ? value : 1 << 21; return PKV_OK;
     case 10: t.debug_tile = value; return PKV_OK;
+    case 11: t.copy_bulk = value; return PKV_OK;
     default: return fail(PKV_ERR_ARG, "pkv_tune: unknown knob");
   }
 }
@@ -1900,6 +2035,47 @@ int pkv_copy_pages(const pkv_pool_desc* pools, int npools, const int32_t* src_id
   if (n <= 0 || npools <= 0) return PKV_OK;
   if (!pools || !src_ids || !dst_ids) return fail(PKV_ERR_ARG, "pkv_copy_pages: null pointer");
   if (npools > 128) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: more than 128 pools in one call");
+  bool same_pool = tuning().copy_bulk != 0;
+  for (int p = 0; p < npools && same_pool; ++p) same_pool = pools[p].src_base == pools[p].dst_base;
+  if (same_pool) {
+    // Moves inside pools of this device: the bulk-copy ring.
+    PageCopyBulkParams B;
+    std::memset(&B, 0, sizeof(B));
+    B.npools = npools;
+    B.n = n;
+    B.num_src_pages = num_src_pages > 0 ? num_src_pages : 0x7fffffff;
+    B.num_dst_pages = num_dst_pages > 0 ? num_dst_pages : 0x7fffffff;
+    B.wait_polls = std::max(1, tuning().wait_polls);
+    B.src_ids = src_ids;
+    B.dst_ids = dst_ids;
+    unsigned long long items = 0;
+    for (int p = 0; p < npools; ++p) {
+      if (!pools[p].src_base || pools[p].page_bytes == 0 || pools[p].page_bytes % 16 != 0 || !aligned16(pools[p].src_base))
+        return fail(PKV_ERR_ARG, "pkv_copy_pages: pool bases must be 16-byte aligned and page_bytes a multiple of 16");
+      if (pools[p].page_bytes > (1ull << 30)) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: page_bytes above 1 GiB");
+      B.pools[p] = pools[p];
+      B.first_item[p] = unsigned(items);
+      items += (unsigned long long)n * ((pools[p].page_bytes + kBulkPiece - 1) / kBulkPiece);
+      if (items > 0x7fffffffull) return fail(PKV_ERR_LIMIT, "pkv_copy_pages: too many pages in one call");
+    }
+    B.first_item[npools] = unsigned(items);
+    const size_t smem = size_t(kCopyStages) * kBulkPiece;
+    static thread_local bool opted[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !opted[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(copy_pages_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+      opted[dev] = true;
+    }
+    const DeviceInfo& d = device_info();
+    const int sms = d.ok ? d.sms : 148;
+    const int per_sm = int((227u * 1024u) / (smem + 2048u));
+    const unsigned grid = unsigned(std::max<unsigned long long>(1, std::min<unsigned long long>(items, (unsigned long long)sms * per_sm)));
+    copy_pages_bulk_kernel<<<grid, 32, smem, stream>>>(B);
+    PKV_LAUNCH_CHECK("copy_pages_bulk_kernel");
+    return PKV_OK;
+  }
   PageCopyParams P;
   std::memset(&P, 0, sizeof(P));
   P.npools = npools;
