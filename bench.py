@@ -368,6 +368,7 @@ def run_ours(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        host_group = dist.new_group(backend="gloo")      # host-side waits of the extra leg: no kernel spins on a GPU meanwhile
 
     def barrier():
         if world > 1:
@@ -474,16 +475,36 @@ def run_ours(args):
     ms = float(np.median(block_ms))                        # this rank's own median block (rank 0: the roofline's kernel time)
     all_ok = bool(int(oks[0]))
 
+    sharded = None
+    if world > 1 and not args.no_ops and not args.small and not args.context:
+        # Configuration 5 (strong scaling + migration over NVLink) through the library's C++ host: ONE process drives all
+        # the GPUs, so every rank releases its decode workload and rank 0 runs the leg while the others wait on the host.
+        launches_per_step, groups_n, lpl, resident, num_pages = wl.launches_per_step, len(wl.groups), wl.lpl, wl.resident, wl.num_pages
+        del graphs, wl
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
+        if rank == 0:
+            try:
+                sharded = measure_sharded(args, list(range(world)))
+            except Exception as e:   # the headline line is still printed
+                sharded = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.set_device(local)
+        dist.barrier(group=host_group)
+    else:
+        launches_per_step, groups_n, lpl, resident, num_pages = wl.launches_per_step, len(wl.groups), wl.lpl, wl.resident, wl.num_pages
     if rank == 0:
         peak, peak_kind = load_peaks()
         total_bytes = step_bytes * world * args.steps
         value = total_bytes / (ms_max * 1e-3) / 1e9
         per_gpu = value / world
-        launches = wl.launches_per_step * args.steps          # per timed block of K steps
+        launches = launches_per_step * args.steps             # per timed block of K steps
         # Dominant kernel = the per-layer gather. Its average duration is taken as the timed region divided by the
         # number of layer calls (an upper bound: it charges the small append kernel and launch gaps to it).
-        calls = len(wl.groups) * args.steps
-        call_bytes = step_bytes / len(wl.groups)
+        calls = groups_n * args.steps
+        call_bytes = step_bytes / groups_n
         achieved = call_bytes / (ms * 1e-3 / calls) / 1e9
         line = {
             "metric": "paged_kv_gather_append_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
@@ -491,10 +512,10 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16/u8 moves, f32 quantisation",
             "data": "synthetic",
             "config": {"workload": WORKLOAD_NAME if not args.small else "SMALL decode43 (8k context): not the benchmark configuration",
-                       "gather_variant": args.variant, "layers_per_launch": wl.lpl, "cuda_graph": bool(args.graph), "resident_layer_pools": wl.resident,
-                       "pool_GB_per_layer": round(wl.num_pages * (PAGE_BYTES + FP4_PAGE_BYTES) / 1e9, 2),
+                       "gather_variant": args.variant, "layers_per_launch": lpl, "cuda_graph": bool(args.graph), "resident_layer_pools": resident,
+                       "pool_GB_per_layer": round(num_pages * (PAGE_BYTES + FP4_PAGE_BYTES) / 1e9, 2),
                        "l2": "inputs larger than L2 (pools %.0f GB, outputs %.1f GB per step)" % (
-                           wl.resident * wl.num_pages * PAGE_BYTES / 1e9, LAYERS * NSEQ * K_SEL * ROW_BYTES / 1e9),
+                           resident * num_pages * PAGE_BYTES / 1e9, LAYERS * NSEQ * K_SEL * ROW_BYTES / 1e9),
                        "step_GB_per_gpu": round(step_bytes / 1e9, 3)},
             "repeats": len(blocks), "value_min": round(total_bytes / (blocks[-1] * 1e-3) / 1e9, 1),
             "value_max": round(total_bytes / (blocks[0] * 1e-3) / 1e9, 1),
@@ -504,7 +525,7 @@ def run_ours(args):
             "bit_exact_check": {"ok": all_ok, "what": why},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and wl.lpl == 1) else None,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and lpl == 1) else None,
                          "traffic_source": "profiles/step_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
                          "peak_kind": "of " + peak_kind,
                          "kernel": "step_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
@@ -517,6 +538,8 @@ def run_ours(args):
                            "note": "host rows, keys, index lists, block tables and chunk lists copied in from pinned "
                                    "memory every step (on a copy stream, one step ahead of the kernels); one sequence's "
                                    "gathered tile of the last layer copied back"}
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_ops and not args.small and not args.context:
             # The other operations of the path at the sizes of benchmark configurations 3 and 4, on the same GPU after
             # the decode workload's memory has been released.
@@ -861,27 +884,27 @@ def measure_churn(args):
 
 
 def run_sharded(args):
-    """Configuration 5: the pool sharded over the GPUs of one box by request ownership. 64 requests with log-uniform
-    lengths (redrawn until their sum fits ONE GPU's pools, so the same workload runs at every GPU count), 43 layers of
-    bf16 rows, owner = request mod G. A step = per layer one appended row and one 2048-row gather for every local
-    request (one library call per layer). After the timed steps one migration event moves 6 requests to another GPU:
-    the destination pulls the pages of all 43 layers from the source's pool through a CUDA IPC mapping. Strong scaling:
-    the total work per step is the same at every G."""
+    """--workload sharded: configuration 5 on the first --gpus devices of this process (no torchrun needed)."""
     import torch
-    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    n = min(max(1, args.gpus), torch.cuda.device_count())
+    print(json.dumps(measure_sharded(args, list(range(n)))), flush=True)
 
-    from unholy_b200 import capi, shard
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29533")
-    dist.init_process_group("nccl" if world > 1 else "gloo", rank=rank, world_size=world,
-                            **({"device_id": torch.device("cuda", local)} if world > 1 else {}))
+
+def measure_sharded(args, devices):
+    """Configuration 5: the pool sharded over the GPUs of one box by request ownership, driven through the library's
+    C++ host (pkv_shards_*: one process, one host thread and stream per GPU). 64 requests with log-uniform lengths
+    (scaled so that their sum fits ONE GPU's pools: the same workload runs at every GPU count), 43 layers of bf16 rows,
+    owner = request mod G. A step = per layer one appended row and one 2048-row gather for every request (one launch
+    per layer and shard). Strong scaling: the work per step is the same at every G. With G > 1 a second timed block
+    runs the same steps while 6 requests migrate to another GPU (the destination pulls all 43 layers' pages over
+    NVLink on its migration stream); the migrated requests are then read back through their new owner's tables."""
+    import torch
+
+    from unholy_b200 import capi
     lib = capi.lib()
-    dev = torch.device("cuda", local)
-    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    i32p = C.POINTER(C.c_int32)
+    G = len(devices)
     L, NREQ = LAYERS, 64
     budget_tokens = 160_000 if args.small else 2_800_000
     lo, hi = (512, 16384) if args.small else (2048, 1 << 20)
@@ -893,201 +916,168 @@ def run_sharded(args):
     if lengths0.sum() > room:
         lengths0 = lengths0 * (room / lengths0.sum())
     lengths0 = np.maximum(lengths0.astype(np.int64), 64)
-    steps = args.steps
+    steps, warm = args.steps, max(3, args.warmup)
+    total_steps = warm + 2 * steps + 8
     N = int(-(-(budget_tokens + NREQ * RPP) // RPP))          # pages per GPU: room for every request (G = 1 holds all)
-    pps = int(-(-(lengths0.max() + steps + args.warmup + 64) // RPP)) + 1
-    slots = NREQ
-    pool = lib.pkv_pool_create(N, RPP, slots, pps, 0)
-    raw = []
-    for _ in range(L):
-        ptr = C.c_void_p()
-        capi.check(lib.pkv_device_alloc(C.byref(ptr), N * PAGE_BYTES))
-        raw.append(ptr.value)
-    peers = shard.PeerPools(dist, rank, world, raw)
-    transport = shard.DevicePull(torch, peers, [PAGE_BYTES] * L, N)
-    cols = torch.arange(W, device=dev, dtype=torch.int64) * 31
+    pps = int(-(-(lengths0.max() + total_steps + 64) // RPP)) + 1
+    cfg = capi.PkvShardConfig(G, N, RPP, W, W, L, NREQ, pps, K_SEL, 0)
+    S = lib.pkv_shards_create(C.byref(cfg), (C.c_int * G)(*devices))
+    if not S:
+        raise RuntimeError("pkv_shards_create: " + lib.pkv_last_error().decode())
+    i32p = C.POINTER(C.c_int32)
+    streams = [torch.cuda.ExternalStream(lib.pkv_shards_stream(S, g), device=torch.device("cuda", devices[g])) for g in range(G)]
+    cols = [torch.arange(W, device=torch.device("cuda", d), dtype=torch.int64) * 31 for d in devices]
     CH = 4096
-    stage = torch.empty(CH, W, dtype=torch.int16, device=dev)
-    d_tables = torch.zeros(slots * pps, dtype=torch.int32, device=dev)
 
-    def pattern(writer, s0, n, layer):
-        v = (writer * 40503 + (torch.arange(s0, s0 + n, device=dev, dtype=torch.int64) * 9973)[:, None] + layer * 613 + cols[None, :])
+    def pattern(g, writer, s0, n, layer):
+        dev = torch.device("cuda", devices[g])
+        v = (writer * 40503 + (torch.arange(s0, s0 + n, device=dev, dtype=torch.int64) * 9973)[:, None] + layer * 613 + cols[g][None, :])
         return (v & 0x7FFF).to(torch.int16)
 
-    pinned = [torch.empty(slots * pps, dtype=torch.int32).pin_memory() for _ in range(2)]
-    pin_done = [torch.cuda.Event(), torch.cuda.Event()]
-    pin_turn = [0]
-
-    def upload_tables():
-        """set_block_tables (src/engine/engine.cpp:745-748): the whole table, through pinned staging, on the stream."""
-        i = pin_turn[0] = pin_turn[0] ^ 1
-        pin_done[i].synchronize()
-        t = np.ctypeslib.as_array(lib.pkv_pool_tables(pool), shape=(slots * pps,))
-        pinned[i].numpy()[:] = t
-        d_tables.copy_(pinned[i], non_blocking=True)
-        pin_done[i].record()
-
-    seqs, lengths = {}, {}
-    for r in range(NREQ):                                    # owners write their requests (a prefill through the library)
-        if shard.owner(r, world) != rank:
-            continue
-        h = lib.pkv_pool_seq_open(pool)
-        n = int(lengths0[r])
-        assert lib.pkv_pool_assign_slot(pool, h) >= 0 and lib.pkv_pool_alloc(pool, h, n) == 1
-        seqs[r], lengths[r] = h, n
-    upload_tables()
-    for r, h in seqs.items():
-        slot = lib.pkv_pool_seq_slot(pool, h)
-        for l in range(L):
-            for s0 in range(0, lengths[r], CH):
-                n = min(CH, lengths[r] - s0)
-                stage[:n] = pattern(r, s0, n, l)
-                capi.check(lib.pkv_store_rows(stage.data_ptr(), n, W, raw[l], d_tables.data_ptr() + slot * pps * 4, RPP, W, s0, sp))
-    torch.cuda.synchronize()
-    qcap = NREQ if world == 1 else NREQ // world + 16
-    out = torch.empty(L, qcap, K_SEL, W, dtype=torch.int16, device=dev)
-    g = torch.Generator(device=dev)
-    g.manual_seed(50 + rank)
-    idx_of = {}                                              # request -> [L][2048] sorted distinct positions below its length
-
-    def make_idx(r):
-        n = lengths[r]
-        t = torch.empty(L, K_SEL, dtype=torch.int32, device=dev)
-        for l in range(L):
-            t[l] = torch.randperm(n, generator=g, device=dev)[:K_SEL].sort().values.to(torch.int32) if n >= K_SEL else \
-                torch.cat([torch.arange(n, device=dev), torch.full((K_SEL - n,), -1, device=dev)]).to(torch.int32)
-        return t
-
-    for r in seqs:
-        idx_of[r] = make_idx(r)
-    step = capi.PkvStep()
-    step.width = step.row_stride = W
-    step.rows_per_page, step.max_pages_per_seq, step.num_pages, step.fp8_block = RPP, pps, N, 64
-    step.k, step.max_slots = K_SEL, slots
-    step.tables = d_tables.data_ptr()
-    layers = (capi.PkvLayer * L)()
-    lptr = [C.cast(C.byref(layers, l * C.sizeof(capi.PkvLayer)), C.POINTER(capi.PkvLayer)) for l in range(L)]
-    flags = capi.PKV_DO_ROWS | capi.PKV_DO_GATHER | (capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0)
+    for r in range(NREQ):
+        capi.check(lib.pkv_shards_add(S, r, r % G, int(lengths0[r])))
+    for g in range(G):                                       # owners write their requests (a prefill through the library)
+        with torch.cuda.device(devices[g]), torch.cuda.stream(streams[g]):
+            sp = C.c_void_p(streams[g].cuda_stream)
+            tables = lib.pkv_shards_tables(S, g)
+            stage = torch.empty(CH, W, dtype=torch.int16, device="cuda")
+            for r in range(g, NREQ, G):
+                tab = tables + lib.pkv_shards_slot(S, r) * pps * 4
+                for l in range(L):
+                    pool = lib.pkv_shards_row_pool(S, g, l)
+                    for s0 in range(0, int(lengths0[r]), CH):
+                        n = min(CH, int(lengths0[r]) - s0)
+                        stage[:n] = pattern(g, r, s0, n, l)
+                        capi.check(lib.pkv_store_rows(stage.data_ptr(), n, W, pool, tab, RPP, W, s0, sp))
+    capi.check(lib.pkv_shards_sync(S))
+    io = (capi.PkvShardIo * (G * L))()
     keep = {}
 
     def prepare():
-        """Device-side descriptors of the local request set (rebuilt after a migration)."""
-        order = sorted(seqs)
-        Q = len(order)
-        keep["order"] = order
-        keep["idx"] = torch.stack([idx_of[r] for r in order], dim=1).contiguous() if Q else torch.empty(L, 0, K_SEL, dtype=torch.int32, device=dev)
-        keep["rows"] = torch.stack([torch.stack([pattern(r, 0, 1, l)[0] for r in order]) for l in range(L)]) if Q else None
-        keep["q_chunk"] = torch.arange(Q, dtype=torch.int32, device=dev)
-        step.nchunks = step.T = step.Q = Q
-        step.q_chunk = keep["q_chunk"].data_ptr()
-        for l in range(L):
-            y = layers[l]
-            y.row_pool, y.gathered = raw[l], out[l].data_ptr()
-            y.idx = keep["idx"][l].data_ptr()
-            y.rows = keep["rows"][l].data_ptr() if Q else None
+        """Per shard: the rows every local request appends, its index lists and the output buffer, in step order."""
+        for g in range(G):
+            ids = (C.c_int32 * NREQ)()
+            order = list(ids[:lib.pkv_shards_local(S, g, ids, NREQ)])
+            with torch.cuda.device(devices[g]), torch.cuda.stream(streams[g]):
+                dev = torch.device("cuda", devices[g])
+                Q = max(1, len(order))
+                rows = torch.zeros(L, Q, W, dtype=torch.int16, device=dev)
+                idx = torch.full((L, Q, K_SEL), -1, dtype=torch.int32, device=dev)
+                out = keep.get(("out", g))
+                if out is None or out.shape[1] < Q:
+                    out = torch.empty(L, NREQ if G == 1 else min(NREQ, NREQ // G + 16), K_SEL, W, dtype=torch.int16, device=dev)
+                for i, r in enumerate(order):
+                    n = lib.pkv_shards_length(S, r)
+                    gen = torch.Generator(device=dev)
+                    gen.manual_seed(5000 + r)
+                    for l in range(L):
+                        rows[l, i] = pattern(g, r, 0, 1, l)[0]
+                        idx[l, i] = (torch.randperm(n, generator=gen, device=dev)[:K_SEL].sort().values.to(torch.int32) if n >= K_SEL else
+                                     torch.cat([torch.arange(n, device=dev), torch.full((K_SEL - n,), -1, device=dev)]).to(torch.int32))
+                keep[("rows", g)], keep[("idx", g)], keep[("out", g)], keep[("order", g)] = rows, idx, out, order
+                for l in range(L):
+                    x = io[g * L + l]
+                    x.rows, x.idx, x.gathered = rows[l].data_ptr(), idx[l].data_ptr(), out[l].data_ptr()
+        capi.check(lib.pkv_shards_sync(S))
 
-    def one_step():
-        order = keep["order"]
-        for r in order:                                     # positions advance: a new page now and then
-            assert lib.pkv_pool_alloc(pool, seqs[r], lengths[r] + 1) == 1
-        if lib.pkv_pool_dirty(pool):
-            upload_tables()
-        ch = torch.tensor([[lib.pkv_pool_seq_slot(pool, seqs[r]), lengths[r], 1, i] for i, r in enumerate(order)],
-                          dtype=torch.int32).pin_memory()
-        keep["chunks"] = ch.to(dev, non_blocking=True)
-        keep["vis"] = (keep["chunks"][:, 1] + 1).contiguous()
-        step.chunks, step.q_visible = keep["chunks"].data_ptr(), keep["vis"].data_ptr()
-        if order:
-            for l in range(L):
-                capi.check(lib.pkv_step_run(C.byref(step), lptr[l], 1, flags, sp))
-        for r in order:
-            lengths[r] += 1
+    def timed_block(count, between=None):
+        capi.check(lib.pkv_shards_mark(S, 0))
+        for _ in range(count):
+            capi.check(lib.pkv_shards_step(S, io))
+            if between:
+                between()
+        capi.check(lib.pkv_shards_mark(S, 1))
+        ms = (C.c_float * G)()
+        capi.check(lib.pkv_shards_elapsed_ms(S, ms))
+        return max(ms)
 
     prepare()
-    for _ in range(max(3, args.warmup)):
-        one_step()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        one_step()
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
+    for _ in range(warm):
+        capi.check(lib.pkv_shards_step(S, io))
+    capi.check(lib.pkv_shards_sync(S))
+    ms = timed_block(steps)
     step_bytes = L * NREQ * (2 * ROW_BYTES + K_SEL * 2 * ROW_BYTES)    # summed over all GPUs, independent of G
-    # one migration event: 6 requests (seeded choice), dst = (owner + 1 + U) mod G
-    mig = {"GB": 0.0, "ms": 0.0}
-    if world > 1:
+    value = step_bytes * steps / (ms * 1e-3) / 1e9
+    peak, kind = load_peaks()
+    res = {"metric": "paged_kv_sharded_gather_append_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": G, "steps": steps,
+           "step_us": round(ms / steps * 1e3, 1), "scaling": "strong", "per_gpu_GBps": round(value / G, 1),
+           "pct_of_8TBps_per_gpu": round(value / G / 80, 2), "frac_of_measured_peak_per_gpu": round(value / G / peak, 4),
+           "host": "C++ (pkv_shards_*): one process, one host thread and stream per GPU",
+           "config": {"workload": f"sharded pool: 64 requests, lengths log-uniform {lo}..{hi} scaled to fit one GPU (sum {int(lengths0.sum())} "
+                                  f"tokens, longest {int(lengths0.max())}), 43 layers bf16 rows, owner = request mod G, append + top-2048 "
+                                  "gather per request and layer", "pages_per_gpu": N, "step_GB_total": round(step_bytes / 1e9, 3)}}
+    moved = []
+    if G > 1:
         mrng = np.random.Generator(np.random.MT19937(55))
-        movers = mrng.choice(NREQ, size=6, replace=False)
-        plan = {int(r): int((shard.owner(int(r), world) + 1 + mrng.integers(0, world - 1)) % world) for r in movers}
-        outgoing = [(r, d) for r, d in plan.items() if r in seqs and d != rank]
-        moved_len = {r: lengths[r] for r, _ in outgoing}
-        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dist.barrier()
-        m0.record()
-        arrived = shard.migrate(dist, rank, world, pool, seqs, lengths, outgoing, transport, sp, torch.cuda.synchronize)
-        m1.record()
-        torch.cuda.synchronize()
-        mt = torch.tensor([m0.elapsed_time(m1), float(transport.bytes_pulled)], dtype=torch.float64, device=dev)
-        mx = mt.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        dist.all_reduce(mt, op=dist.ReduceOp.SUM)
-        mig = {"GB": round(float(mt[1]) / 1e9, 3), "ms": round(float(mx[0]), 3),
-               "GBps_aggregate": round(float(mt[1]) / max(float(mx[0]), 1e-9) / 1e6, 1),
-               "note": "event time includes the host handshake (object all-gather, barrier) around the pull kernels"}
-        upload_tables()
-        for r, h, n in arrived:
-            idx_of[r] = make_idx(r)
-        for r, _ in outgoing:
-            idx_of.pop(r, None)
+        movers = mrng.choice(NREQ, size=6, replace=False).astype(np.int32)
+        dsts = np.array([(int(r) % G + 1 + int(mrng.integers(0, G - 1))) % G for r in movers], np.int32)
+        moved = [int(r) for r in movers]
+        capi.check(lib.pkv_shards_sync(S))
+        t0 = time.perf_counter()
+        done_at = [None]
+
+        def poll():   # a query only: the movers rejoin after the block, when the step inputs are rebuilt for the new owners
+            if done_at[0] is None and lib.pkv_shards_migrate_landed(S) == len(movers):
+                done_at[0] = time.perf_counter() - t0
+
+        capi.check(lib.pkv_shards_migrate_begin(S, movers.ctypes.data_as(i32p), dsts.ctypes.data_as(i32p), len(movers)))
+        ms_during = timed_block(steps, poll)
+        lib.pkv_shards_migrate_end(S, 1)
+        if done_at[0] is None:
+            done_at[0] = time.perf_counter() - t0
+        nbytes, kms = C.c_double(0), (C.c_float * G)()
+        capi.check(lib.pkv_shards_migrate_stats(S, C.byref(nbytes), kms))
+        into = [0.0] * G                                      # bytes pulled per destination
+        for r, d in zip(movers, dsts):
+            into[int(d)] += -(-(lib.pkv_shards_length(S, int(r))) // RPP) * L * PAGE_BYTES
+        busiest = max(range(G), key=lambda g: kms[g])
+        link = into[busiest] / max(kms[busiest], 1e-6) / 1e6 if kms[busiest] > 0 else 0.0
+        res["migration"] = {
+            "requests": len(movers), "GB": round(nbytes.value / 1e9, 3),
+            "pull_kernels_ms_per_destination": [round(float(x), 3) for x in kms],
+            "GBps_into_busiest_gpu": round(link, 1), "frac_of_900GBps_per_direction": round(link / 900, 3),
+            "host_ms_begin_to_last_pull_landed": round(done_at[0] * 1e3, 3),
+            "step_us_while_migrating": round(ms_during / steps * 1e3, 1),
+            "step_us_without": round(ms / steps * 1e3, 1),
+            "note": "pull kernels timed with CUDA events on the destination's migration stream; the steps of the other 58 requests "
+                    "run on the step streams meanwhile; host time runs from migrate_begin until the last pull's event had completed "
+                    "(queried after every step)"}
         prepare()
-        one_step()                                           # the migrated requests keep decoding on their new owner
-    # verification: every local request read back through its table (2 layers) equals the pattern its writers left
+        capi.check(lib.pkv_shards_step(S, io))               # the migrated requests keep decoding on their new owner
+        capi.check(lib.pkv_shards_sync(S))
+    # verification: requests read back through their owner's table (2 layers) equal the pattern their writers left
     ok = True
-    upload_tables()
-    for r in sorted(seqs)[:6] + [x for x in seqs if world > 1 and x in plan]:
-        n = lengths[r]
-        slot = lib.pkv_pool_seq_slot(pool, seqs[r])
-        idx = torch.arange(n, dtype=torch.int32, device=dev)
-        vis = torch.tensor([n], dtype=torch.int32, device=dev)
-        got = torch.empty(n, W, dtype=torch.int16, device=dev)
-        for l in (0, L - 1):
-            capi.check(lib.pkv_gather_rows(raw[l], d_tables.data_ptr() + slot * pps * 4, RPP, W, W, idx.data_ptr(),
-                                           vis.data_ptr(), 1, n, got.data_ptr(), sp))
-            want = pattern(r, 0, n, l)
-            n0 = int(lengths0[r])
-            want[n0:] = pattern(r, 0, 1, l)[0]               # every decode step appended the same pattern row
-            ok &= bool(torch.equal(got, want))
-    st = C.c_int(0)
-    capi.check(lib.pkv_device_status(C.byref(st)))
-    ok &= st.value == 0
-    okt = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
-    if world > 1:
-        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-    if rank == 0:
-        value = step_bytes * steps / (ms * 1e-3) / 1e9
-        peak, kind = load_peaks()
-        print(json.dumps({
-            "metric": "paged_kv_sharded_gather_append_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
-            "steps": steps, "ms_per_step": round(ms / steps, 4), "scaling": "strong", "higher_is_better": True, "data": "synthetic",
-            "per_gpu_GBps": round(value / world, 1), "pct_of_8TBps_per_gpu": round(value / world / 80, 2),
-            "pct_of_measured_peak_per_gpu": round(value / world / peak * 100, 2),
-            "config": {"workload": f"sharded pool: 64 requests, lengths log-uniform {lo}..{hi} scaled to fit one GPU (sum {int(lengths0.sum())} tokens, longest {int(lengths0.max())}), 43 layers bf16 rows, owner = request mod G, append + top-2048 gather per request and layer",
-                       "pages_per_gpu": N, "step_GB_total": round(step_bytes / 1e9, 3)},
-            "migration": mig, "bit_exact_check": {"ok": bool(int(okt[0]))}}), flush=True)
-    dist.barrier()
-    peers.close()
-    dist.barrier()
-    for ptr in raw:
-        lib.pkv_device_free(C.c_void_p(ptr))
-    lib.pkv_pool_destroy(pool)
-    dist.destroy_process_group()
+    for r in sorted(set(list(range(6)) + moved)):
+        g = lib.pkv_shards_owner(S, r)
+        with torch.cuda.device(devices[g]), torch.cuda.stream(streams[g]):
+            dev = torch.device("cuda", devices[g])
+            sp = C.c_void_p(streams[g].cuda_stream)
+            n = lib.pkv_shards_length(S, r)
+            tab = lib.pkv_shards_tables(S, g) + lib.pkv_shards_slot(S, r) * pps * 4
+            idx = torch.arange(n, dtype=torch.int32, device=dev)
+            vis = torch.tensor([n], dtype=torch.int32, device=dev)
+            got = torch.empty(n, W, dtype=torch.int16, device=dev)
+            for l in (0, L - 1):
+                capi.check(lib.pkv_gather_rows(lib.pkv_shards_row_pool(S, g, l), tab, RPP, W, W, idx.data_ptr(), vis.data_ptr(), 1, n,
+                                               got.data_ptr(), sp))
+                want = pattern(g, r, 0, n, l)
+                want[int(lengths0[r]):] = pattern(g, r, 0, 1, l)[0]   # every decode step appended the same pattern row
+                same = bool(torch.equal(got, want))
+                if not same and os.environ.get("PKV_BENCH_DEBUG"):
+                    bad = (got != want).any(dim=1).nonzero().flatten()
+                    print(f"request {r} (owner {g}, moved {r in moved}) layer {l}: {bad.numel()} rows differ, first {bad[:5].tolist()} of {n} (initial {int(lengths0[r])})", file=sys.stderr)
+                ok &= same
+    for d in devices:
+        with torch.cuda.device(d):
+            st = C.c_int(0)
+            capi.check(lib.pkv_device_status(C.byref(st)))
+            if st.value and os.environ.get("PKV_BENCH_DEBUG"):
+                print(f"device {d}: status {st.value:#x}", file=sys.stderr)
+            ok &= st.value == 0
+    res["bit_exact_check"] = {"ok": bool(ok), "what": "requests (the migrated ones included) read back through their owner's block table, 2 layers"}
+    keep.clear()
+    lib.pkv_shards_destroy(S)
+    return res
 
 
 def run_topk(args):

@@ -382,7 +382,8 @@ PKV_API int pkv_shards_sync(pkv_shards* s);
  * device time of the pull kernels alone (CUDA events on the migration stream). */
 PKV_API int pkv_shards_migrate_begin(pkv_shards* s, const int32_t* requests, const int32_t* dst_shards, int n);
 PKV_API int pkv_shards_migrate_end(pkv_shards* s, int wait);
-PKV_API int pkv_shards_migrate_pending(const pkv_shards* s);
+PKV_API int pkv_shards_migrate_pending(const pkv_shards* s); /* begun and not yet ended */
+PKV_API int pkv_shards_migrate_landed(pkv_shards* s);        /* of those, pulls whose event has completed (a query: nothing changes) */
 PKV_API int pkv_shards_migrate_stats(pkv_shards* s, double* bytes_out, float* kernel_ms_out);
 
 /* ------------------------------------------------------------------------------------------------------------------

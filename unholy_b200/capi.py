@@ -119,6 +119,7 @@ _SIGS = {
     "pkv_shards_migrate_begin": (_i, [_vp, c_i32p, c_i32p, _i]),
     "pkv_shards_migrate_end": (_i, [_vp, _i]),
     "pkv_shards_migrate_pending": (_i, [_vp]),
+    "pkv_shards_migrate_landed": (_i, [_vp]),
     "pkv_shards_migrate_stats": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_float)]),
     "pkv_pool_create": (_vp, [_i, _i, _i, _i, _i]),
     "pkv_pool_destroy": (None, [_vp]),

@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <map>
@@ -120,6 +121,11 @@ struct Shard {
   std::unique_ptr<Worker> worker;
   std::string error;
   int rc = PKV_OK;
+  // The step's launches, captured once per (number of local requests, io pointers) and replayed: the launch parameters
+  // do not change from step to step (positions and block tables are read from device buffers that are refreshed by
+  // stream-ordered uploads in front of every replay).
+  cudaGraphExec_t graph = nullptr;
+  std::vector<const void*> graph_key;
 };
 
 struct Migration {
@@ -136,6 +142,7 @@ struct pkv_shards {
   std::vector<Shard> shards;
   std::map<int, Request> requests;
   std::vector<Migration> pending;
+  bool use_graphs = true;  // PKV_SHARD_GRAPH=0: issue the launches of every step directly
   double migrated_bytes = 0;
   std::vector<float> mig_kernel_ms;  // per destination shard, summed over completed pulls
 };
@@ -214,7 +221,24 @@ int shard_step(pkv_shards& S, int g, const pkv_shard_io* io) {
   step.chunks = sh.d_chunks;
   step.q_chunk = sh.d_qchunk;
   step.q_visible = sh.d_qvis;
+  std::vector<const void*> key{reinterpret_cast<const void*>(size_t(Q))};
   for (int l = 0; l < S.cfg.layers; ++l) {
+    const pkv_shard_io& x = io[size_t(g) * size_t(S.cfg.layers) + size_t(l)];
+    key.insert(key.end(), {x.rows, x.keys, x.idx, x.gathered});
+  }
+  const bool use_graph = S.use_graphs;
+  if (use_graph && sh.graph && key == sh.graph_key) {
+    SH_CUDA(cudaGraphLaunch(sh.graph, sh.step_stream));
+    for (const int r : order) ++S.requests.at(r).length;
+    return PKV_OK;
+  }
+  if (use_graph) {
+    if (sh.graph) cudaGraphExecDestroy(sh.graph);
+    sh.graph = nullptr;
+    SH_CUDA(cudaStreamBeginCapture(sh.step_stream, cudaStreamCaptureModeThreadLocal));
+  }
+  int launch_rc = PKV_OK;
+  for (int l = 0; l < S.cfg.layers && launch_rc == PKV_OK; ++l) {
     const pkv_shard_io& x = io[size_t(g) * size_t(S.cfg.layers) + size_t(l)];
     pkv_layer ly;
     std::memset(&ly, 0, sizeof(ly));
@@ -225,7 +249,23 @@ int shard_step(pkv_shards& S, int g, const pkv_shard_io* io) {
     ly.idx = x.idx;
     ly.gathered = x.gathered;
     const int flags = PKV_DO_ROWS | PKV_DO_GATHER | PKV_VARIANT_BULK | (ly.key_pool_fp4 ? PKV_DO_KEYS_FP4 : 0);
-    if (const int rc = pkv_step_run(&step, &ly, 1, flags, reinterpret_cast<pkv_stream_t>(sh.step_stream))) return rc;
+    launch_rc = pkv_step_run(&step, &ly, 1, flags, reinterpret_cast<pkv_stream_t>(sh.step_stream));
+  }
+  if (use_graph) {
+    cudaGraph_t captured = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(sh.step_stream, &captured);  // (always ends the capture, also after a failed launch)
+    if (launch_rc != PKV_OK) {
+      if (captured) cudaGraphDestroy(captured);
+      return launch_rc;
+    }
+    if (e != cudaSuccess) return fail_cuda("cudaStreamEndCapture", e);
+    const cudaError_t ie = cudaGraphInstantiate(&sh.graph, captured, 0);
+    cudaGraphDestroy(captured);
+    if (ie != cudaSuccess) return fail_cuda("cudaGraphInstantiate", ie);
+    sh.graph_key = key;
+    SH_CUDA(cudaGraphLaunch(sh.graph, sh.step_stream));
+  } else if (launch_rc != PKV_OK) {
+    return launch_rc;
   }
   for (const int r : order) ++S.requests.at(r).length;
   return PKV_OK;
@@ -242,6 +282,7 @@ void free_shard(Shard& sh) {
     cudaFreeHost(st.chunks);
     if (st.used) cudaEventDestroy(st.used);
   }
+  if (sh.graph) cudaGraphExecDestroy(sh.graph);
   if (sh.step_stream) cudaStreamDestroy(sh.step_stream);
   if (sh.mig_stream) cudaStreamDestroy(sh.mig_stream);
   for (auto& e : sh.mark)
@@ -297,6 +338,7 @@ pkv_shards* pkv_shards_create(const pkv_shard_config* cfg, const int* devices) {
   cudaGetDevice(&saved);
   auto S = std::make_unique<pkv_shards>();
   S->cfg = *cfg;
+  if (const char* v = std::getenv("PKV_SHARD_GRAPH")) S->use_graphs = std::atoi(v) != 0;
   S->shards.resize(size_t(cfg->ngpus));
   S->mig_kernel_ms.assign(size_t(cfg->ngpus), 0.0f);
   bool ok = true;
@@ -581,6 +623,16 @@ int pkv_shards_migrate_end(pkv_shards* S, int wait) {
 }
 
 int pkv_shards_migrate_pending(const pkv_shards* S) { return S ? int(S->pending.size()) : -1; }
+
+int pkv_shards_migrate_landed(pkv_shards* S) {
+  if (!S) return -1;
+  int landed = 0;
+  for (const Migration& m : S->pending) {
+    DeviceGuard dg(S->shards[size_t(m.dst)].device);
+    landed += cudaEventQuery(m.done) == cudaSuccess;
+  }
+  return landed;
+}
 
 int pkv_shards_migrate_stats(pkv_shards* S, double* bytes_out, float* kernel_ms_out) {
   if (!S) return fail(PKV_ERR_ARG, "pkv_shards_migrate_stats: null argument");
