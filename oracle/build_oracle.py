@@ -7,6 +7,9 @@
                                    where it lies (through oracle/hip_shim); only when the reference checkout exists.
   oracle/_ref/libref_engine.so     the reference's own engine.cpp + sampler.cpp with oracle/ref_engine_driver.cpp (a
                                    recording StepModel); only when the reference checkout exists.
+  oracle/_ref/step_model_test      the reference's own engine.cpp + sampler.cpp driving the product library through its
+                                   StepModel adaptor (tests/cpp/step_model_test.cpp); only when the reference checkout and
+                                   the built product library exist. Needs a GPU to run.
 
 No reference source is copied: the compiler reads it in place. The _ref outputs are git-ignored and travel to the GPU
 box as binaries; when the checkout is absent the already-built files are used as they are.
@@ -25,6 +28,8 @@ REF_OUT = HERE / "_ref"
 ORACLE_LIB = BUILD / "libpkv_oracle.so"
 REF_NUMERIC_LIB = REF_OUT / "libref_numeric.so"
 REF_ENGINE_LIB = REF_OUT / "libref_engine.so"
+STEP_MODEL_TEST = REF_OUT / "step_model_test"
+ROOT = HERE.parent
 
 
 def _run(cmd):
@@ -48,7 +53,7 @@ def build_oracle(force: bool = False) -> Path:
 
 def build_reference(force: bool = False) -> dict:
     """Compiles the reference's own sources in place. Returns {name: path or None}."""
-    out = {"numeric": None, "engine": None}
+    out = {"numeric": None, "engine": None, "step_model_test": None}
     have = (REFERENCE / "src" / "kernels" / "dev.hip.hpp").exists()
     if have:
         REF_OUT.mkdir(exist_ok=True)
@@ -61,6 +66,16 @@ def build_reference(force: bool = False) -> dict:
             _run(["g++", "-std=c++20", "-O2", "-fPIC", "-shared", "-pthread", f"-I{REFERENCE / 'src'}",
                   str(REFERENCE / "src/engine/engine.cpp"), str(REFERENCE / "src/engine/sampler.cpp"), str(edrv),
                   "-o", str(REF_ENGINE_LIB)])
+        src = ROOT / "tests" / "cpp" / "step_model_test.cpp"
+        hdr = ROOT / "unholy_b200" / "csrc" / "host" / "step_model.hpp"
+        lib = ROOT / "unholy_b200" / "lib" / "libunholy_pkv.so"
+        cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+        if src.exists() and lib.exists() and (force or not _newer(STEP_MODEL_TEST, src, hdr, lib, REFERENCE / "src/engine/engine.cpp")):
+            _run(["g++", "-std=c++20", "-O2", "-pthread", f"-I{REFERENCE / 'src'}", f"-I{cuda / 'include'}", str(src),
+                  str(REFERENCE / "src/engine/engine.cpp"), str(REFERENCE / "src/engine/sampler.cpp"), "-o", str(STEP_MODEL_TEST),
+                  f"-L{lib.parent}", "-lunholy_pkv", f"-L{cuda / 'lib64'}", "-lcudart", "-Wl,-rpath,$ORIGIN/../../unholy_b200/lib"])
+    if STEP_MODEL_TEST.exists():
+        out["step_model_test"] = STEP_MODEL_TEST
     if REF_NUMERIC_LIB.exists():
         out["numeric"] = REF_NUMERIC_LIB
     if REF_ENGINE_LIB.exists():
