@@ -414,6 +414,9 @@ PKV_API int pkv_token_keys(const int32_t* tokens, int n, const int32_t* starts, 
                            int nimages, uint64_t* keys_out);
 PKV_API int pkv_pool_match_prefix_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, const uint8_t* boundary_ok);
 PKV_API int pkv_pool_register_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, int done_pos);
+/* How many leading full pages (at most (nkeys - 1) / page_tokens) the prefix cache names right now — the walk
+ * match_prefix makes (engine.cpp:289-291) before it looks for a boundary with a saved state; nothing changes. */
+PKV_API int pkv_pool_cached_prefix_keys(const pkv_pool* p, const uint64_t* keys, int nkeys);
 PKV_API uint64_t pkv_page_hash_keys(const uint64_t* keys, int page_tokens, int page_index);
 PKV_API int pkv_pool_assign_slot(pkv_pool* p, int seq);     /* free_slots_.back(); writes the table row; -1 if none */
 /* alloc_pages (engine.cpp:437-444): pages for positions [0, upto). Returns 1, or 0 (nothing changed) when the pool
@@ -473,6 +476,52 @@ PKV_API int pkv_pool_free_list(const pkv_pool* p, int32_t* out, int cap);      /
 PKV_API int pkv_pool_evictable_list(const pkv_pool* p, int32_t* out, int cap); /* oldest first */
 /* The chained page hash (engine.cpp:257-280) of page `page_index` of a token sequence. */
 PKV_API uint64_t pkv_page_hash(const int32_t* tokens, int page_tokens, int page_index);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Snapshot store: the bookkeeping around pkv_state_copies — which snapshot slot a save goes into, which one a prefix
+ * hit restores, eviction, and the disk tier (a preallocated O_DIRECT file, one I/O thread, a 64-bit checksum checked on
+ * read) — of src/engine/engine.cpp:87-92,284-336,361-397,949-970,1011-1261, as a host-side object (the C++ class is
+ * unholy_b200/csrc/snapshot_store.hpp; this C form takes snapshots that are one contiguous host region each, snapshot
+ * id at host_base + id * snap_bytes). Host only; one owner thread, like the engine thread. Entries do not outlive the
+ * store: the file is removed when it is destroyed.
+ * ---------------------------------------------------------------------------------------------------------------- */
+typedef struct pkv_snap pkv_snap;
+typedef struct pkv_snap_hit {
+  int32_t pages;      /* the prefix covers this many full pages; 0: no hit */
+  int32_t snap;       /* RAM snapshot to restore; the caller holds a reference until pkv_snap_put */
+  int32_t disk_slot;  /* >= 0: snap is an empty RAM slot that pkv_snap_start_load must fill from this disk slot first */
+  int32_t reserved;
+  uint64_t hash;      /* name of the boundary */
+} pkv_snap_hit;
+typedef struct pkv_snap_done { /* a finished disk operation */
+  int32_t write, ok, snap, reserved;
+  uint64_t load_id;   /* reads: what pkv_snap_start_load returned */
+} pkv_snap_done;
+typedef struct pkv_snap_counters_t { /* src/engine/engine.hpp:147-149 (snapshots, free_snapshots, disk_snapshots, snapshot_io, ...) */
+  int32_t cached, free_or_evictable, on_disk, io_pending;
+  uint64_t spills, disk_hits, disk_read_bytes, disk_write_bytes;
+} pkv_snap_counters_t;
+/* dir NULL / empty or disk_slots <= 0: no disk tier. io_hook (may be NULL) runs on the I/O thread before every
+ * operation (the reference's EngineConfig::io_hook, src/engine/engine.hpp:131: tests stall or corrupt through it). */
+PKV_API pkv_snap* pkv_snap_create(int ram_slots, uint8_t* host_base, size_t snap_bytes, const char* dir, int disk_slots,
+                                  void (*io_hook)(int write, void* user), void* hook_user);
+PKV_API void pkv_snap_destroy(pkv_snap* s);
+PKV_API int pkv_snap_disk_on(const pkv_snap* s);
+/* match_prefix's snapshot half (engine.cpp:287-333): page_hashes[i] names the boundary at the end of page i (only
+ * boundaries whose pages are all cached should be offered), allow[i] == 0 rules one out (NULL: all allowed). */
+PKV_API int pkv_snap_match(pkv_snap* s, const uint64_t* page_hashes, int npages, const uint8_t* allow, pkv_snap_hit* hit_out);
+PKV_API uint64_t pkv_snap_start_load(pkv_snap* s, const pkv_snap_hit* hit); /* start_load, engine.cpp:1128-1137; returns the load id */
+PKV_API void pkv_snap_cancel_load(pkv_snap* s, const pkv_snap_hit* hit);    /* a disk hit given up before its load was started */
+PKV_API int pkv_snap_take(pkv_snap* s);                                     /* take_snapshot; -1: none */
+PKV_API void pkv_snap_put(pkv_snap* s, int id);                             /* put_snapshot */
+/* commit_snapshot: the save into id completed and names `hash`; rolling_id / rolling_hash are the sequence's (in and out). */
+PKV_API void pkv_snap_commit(pkv_snap* s, int id, uint64_t hash, int past_prompt, int* rolling_id, uint64_t* rolling_hash);
+PKV_API int pkv_snap_spare(const pkv_snap* s);                              /* free + droppable slots (engine.cpp:577-580) */
+PKV_API void pkv_snap_spill(pkv_snap* s);                                   /* spill, engine.cpp:1163-1187 */
+PKV_API int pkv_snap_poll(pkv_snap* s, pkv_snap_done* done_out, int cap);   /* poll_io; returns the number of completions */
+PKV_API void pkv_snap_clear(pkv_snap* s);                                   /* the snapshot half of clear_cache */
+PKV_API void pkv_snap_wait_idle(pkv_snap* s);                               /* tests: the I/O thread has nothing queued or running */
+PKV_API int pkv_snap_counters(const pkv_snap* s, pkv_snap_counters_t* out);
 
 #ifdef __cplusplus
 }

@@ -25,10 +25,10 @@ uint64_t mix(uint64_t x) {
 constexpr int kVocab = 512;
 
 // Event log: flat int64 records, first word = kind.
-//   1 nchunks {seq slot s0 n}* nsaves {slot}*     a submitted step
+//   1 nchunks {seq slot s0 n}* nsaves {slot snapshot}* nrestores {slot snapshot}*     a submitted step
 //   2 table_index                                  set_block_tables (the table itself in tables[table_index])
 //   3 seq                                          request finished (its pages were released)
-//   4 running waiting free_pages cached_pages preemptions    after one iterate()
+//   4 running waiting free_pages cached_pages preemptions snapshots free_snapshots    after one iterate()
 struct Trace {
   std::vector<int64_t> ev;
   std::vector<std::vector<int32_t>> tables;
@@ -61,7 +61,15 @@ class RecordingModel final : public StepModel {
       tr_.ev.push_back(c.n);
     }
     tr_.ev.push_back(int64_t(in.save.size()));
-    for (const StateOp& s : in.save) tr_.ev.push_back(s.slot);
+    for (const StateOp& s : in.save) {
+      tr_.ev.push_back(s.slot);
+      tr_.ev.push_back(s.snapshot);
+    }
+    tr_.ev.push_back(int64_t(in.restore.size()));
+    for (const StateOp& s : in.restore) {
+      tr_.ev.push_back(s.slot);
+      tr_.ev.push_back(s.snapshot);
+    }
     // Logits: one-hot on a token that depends only on (request, position), never EOS (id 1).
     logits_.assign(in.logit_rows.size() * size_t(kVocab), 0.0f);
     for (size_t r = 0; r < in.logit_rows.size(); ++r) {
@@ -150,7 +158,7 @@ int refeng_iterate(void* h) {
   const bool did = d->engine->iterate();
   const EngineStats s = d->engine->stats();
   for (int64_t v : {int64_t(4), int64_t(s.running), int64_t(s.waiting), int64_t(s.free_pages), int64_t(s.cached_pages),
-                    int64_t(s.preemptions)})
+                    int64_t(s.preemptions), int64_t(s.snapshots), int64_t(s.free_snapshots)})
     d->tr.ev.push_back(v);
   return did ? 1 : 0;
 }

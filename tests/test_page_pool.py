@@ -53,10 +53,10 @@ class Replay:
     """Feeds the reference engine and the page pool the same requests; after every iterate() of the engine replays
     the new trace records into the pool and compares."""
 
-    def __init__(self, pkv, refeng, num_pages, page_tokens, slots, pps, budget):
+    def __init__(self, pkv, refeng, num_pages, page_tokens, slots, pps, budget, snapshots=8192):
         self.pkv, self.ref = pkv, refeng
         self.pt, self.slots, self.pps, self.budget, self.num_pages = page_tokens, slots, pps, budget, num_pages
-        self.eng = refeng.refeng_create(num_pages, page_tokens, slots, pps, budget, 8192)
+        self.eng = refeng.refeng_create(num_pages, page_tokens, slots, pps, budget, snapshots)
         self.pool = pkv.pkv_pool_create(num_pages, page_tokens, slots, pps, 1)
         self.tokens, self.handle, self.computed = {}, {}, {}
         self.waiting, self.running = deque(), []
@@ -111,18 +111,14 @@ class Replay:
             h = self.handle[rid]
             toks = self.keys(rid)
             limit = (len(toks) - 1) // self.pt
-            ok = np.zeros(max(limit, 1), np.uint8)
-            blocks = list(zip(*self.images[rid][:2])) if rid in self.images else []
-            for i in range(limit):  # a boundary can be resumed only where some sequence saved its state ...
-                hh = int(pkv.pkv_page_hash_keys(toks.ctypes.data_as(u64p), self.pt, i))
-                b = (i + 1) * self.pt   # ... and never inside a whole image block (engine.cpp:292-296)
-                ok[i] = hh in self.saved and not any(st < b < st + ln for st, ln in blocks)
+            ok = self.boundaries(rid, toks, limit)
             computed = pkv.pkv_pool_match_prefix_keys(pool, h, toks.ctypes.data_as(u64p), len(toks), ok.ctypes.data_as(u8p))
             first = min(len(toks) - computed, self.budget)
             npages = pkv.pkv_pool_seq_pages(pool, h, None, 0)
             need = -(-(computed + first) // self.pt) - npages + len(self.running)
             if need > pkv.pkv_pool_available(pool):
                 pkv.pkv_pool_release(pool, h)
+                self.on_admit_failed(rid)
                 break
             assert pkv.pkv_pool_assign_slot(pool, h) >= 0
             self.computed[rid] = computed
@@ -148,8 +144,13 @@ class Replay:
                 chunks = ev[i + 2:i + 2 + 4 * nch].reshape(nch, 4)
                 i += 2 + 4 * nch
                 nsave = int(ev[i])
-                saves = [int(x) for x in ev[i + 1:i + 1 + nsave]]
-                i += 1 + nsave
+                save_ops = [(int(a), int(b)) for a, b in ev[i + 1:i + 1 + 2 * nsave].reshape(nsave, 2)]
+                saves = [a for a, _ in save_ops]
+                i += 1 + 2 * nsave
+                nrest = int(ev[i])
+                restore_ops = [(int(a), int(b)) for a, b in ev[i + 1:i + 1 + 2 * nrest].reshape(nrest, 2)]
+                i += 1 + 2 * nrest
+                self.on_step(chunks, save_ops, restore_ops)
                 for seq, slot, s0, cn in chunks:
                     h = self.handle[int(seq)]
                     assert pkv.pkv_pool_seq_slot(pool, h) == slot, "slot assignment differs"
@@ -181,8 +182,9 @@ class Replay:
                 capi.check(pkv.pkv_pool_seq_close(pool, self.handle.pop(rid)))
                 self.running.remove(rid)
             elif kind == 4:
-                running, waiting, free_pages, cached, preempt = (int(x) for x in ev[i + 1:i + 6])
-                i += 6
+                running, waiting, free_pages, cached, preempt, snaps, free_snaps = (int(x) for x in ev[i + 1:i + 8])
+                i += 8
+                self.on_counters(snaps, free_snaps)
                 assert preempt == 0, "scenario sized to avoid preemption"
                 assert (running, waiting) == (len(self.running), len(self.waiting))
                 assert free_pages == pkv.pkv_pool_available(pool)
@@ -194,6 +196,26 @@ class Replay:
                 raise AssertionError(f"unknown trace record {kind}")
         self.cursor = n
         return did
+
+    def boundaries(self, rid, toks, limit):
+        """Which page boundaries of the prompt can be resumed at: where some sequence saved its state ..."""
+        ok = np.zeros(max(limit, 1), np.uint8)
+        blocks = list(zip(*self.images[rid][:2])) if rid in self.images else []
+        for i in range(limit):
+            hh = int(self.pkv.pkv_page_hash_keys(toks.ctypes.data_as(u64p), self.pt, i))
+            b = (i + 1) * self.pt   # ... and never inside a whole image block (engine.cpp:292-296)
+            ok[i] = hh in self.saved and not any(st < b < st + ln for st, ln in blocks)
+        return ok
+
+    def on_admit_failed(self, rid):
+        pass
+
+    # Hooks for the snapshot-store differential (tests/test_snapshot_store.py); the page tests do not use them.
+    def on_step(self, chunks, save_ops, restore_ops):
+        pass
+
+    def on_counters(self, snapshots, free_snapshots):
+        pass
 
     def drain(self, limit=200000):
         for _ in range(limit):

@@ -17,8 +17,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB = LIB_DIR / "libunholy_pkv.so"
-SOURCES = [CSRC / "pkv_kernels.cu", CSRC / "pkv_topk.cu", CSRC / "pkv_topk_cluster.cu", CSRC / "pkv_topk_f32.cu", CSRC / "pkv_state.cu", CSRC / "pkv_shard.cu", CSRC / "page_pool.cpp"]
-HEADERS = [CSRC / "pkv_numeric.cuh", CSRC / "pkv_internal.hpp", CSRC / "page_pool.hpp", PKG.parent / "include" / "unholy_pkv.h"]
+SOURCES = [CSRC / "pkv_kernels.cu", CSRC / "pkv_topk.cu", CSRC / "pkv_topk_cluster.cu", CSRC / "pkv_topk_f32.cu", CSRC / "pkv_state.cu", CSRC / "pkv_shard.cu", CSRC / "page_pool.cpp", CSRC / "snapshot_store.cpp"]
+HEADERS = [CSRC / "pkv_numeric.cuh", CSRC / "pkv_internal.hpp", CSRC / "page_pool.hpp", CSRC / "snapshot_store.hpp", PKG.parent / "include" / "unholy_pkv.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

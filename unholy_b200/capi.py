@@ -58,6 +58,22 @@ class PkvShardIo(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("rows", "keys", "idx", "gathered")]
 
 
+class PkvSnapHit(C.Structure):
+    _fields_ = [("pages", C.c_int32), ("snap", C.c_int32), ("disk_slot", C.c_int32), ("reserved", C.c_int32), ("hash", C.c_uint64)]
+
+
+class PkvSnapDone(C.Structure):
+    _fields_ = [("write", C.c_int32), ("ok", C.c_int32), ("snap", C.c_int32), ("reserved", C.c_int32), ("load_id", C.c_uint64)]
+
+
+class PkvSnapCounters(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("cached", "free_or_evictable", "on_disk", "io_pending")] + \
+               [(n, C.c_uint64) for n in ("spills", "disk_hits", "disk_read_bytes", "disk_write_bytes")]
+
+
+SNAP_IO_HOOK = C.CFUNCTYPE(None, C.c_int, C.c_void_p)
+
+
 class PkvPoolDesc(C.Structure):
     _fields_ = [("src_base", C.c_void_p), ("dst_base", C.c_void_p), ("page_bytes", C.c_uint64)]
 
@@ -121,6 +137,21 @@ _SIGS = {
     "pkv_shards_migrate_pending": (_i, [_vp]),
     "pkv_shards_migrate_landed": (_i, [_vp]),
     "pkv_shards_migrate_stats": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_float)]),
+    "pkv_snap_create": (_vp, [_i, _vp, _sz, C.c_char_p, _i, SNAP_IO_HOOK, _vp]),
+    "pkv_snap_destroy": (None, [_vp]),
+    "pkv_snap_disk_on": (_i, [_vp]),
+    "pkv_snap_match": (_i, [_vp, C.POINTER(C.c_uint64), _i, c_u8p, C.POINTER(PkvSnapHit)]),
+    "pkv_snap_start_load": (C.c_uint64, [_vp, C.POINTER(PkvSnapHit)]),
+    "pkv_snap_cancel_load": (None, [_vp, C.POINTER(PkvSnapHit)]),
+    "pkv_snap_take": (_i, [_vp]),
+    "pkv_snap_put": (None, [_vp, _i]),
+    "pkv_snap_commit": (None, [_vp, _i, C.c_uint64, _i, C.POINTER(C.c_int), C.POINTER(C.c_uint64)]),
+    "pkv_snap_spare": (_i, [_vp]),
+    "pkv_snap_spill": (None, [_vp]),
+    "pkv_snap_poll": (_i, [_vp, C.POINTER(PkvSnapDone), _i]),
+    "pkv_snap_clear": (None, [_vp]),
+    "pkv_snap_wait_idle": (None, [_vp]),
+    "pkv_snap_counters": (_i, [_vp, C.POINTER(PkvSnapCounters)]),
     "pkv_pool_create": (_vp, [_i, _i, _i, _i, _i]),
     "pkv_pool_destroy": (None, [_vp]),
     "pkv_pool_seq_open": (_i, [_vp]),
@@ -129,6 +160,7 @@ _SIGS = {
     "pkv_token_keys": (_i, [c_i32p, _i, c_i32p, c_i32p, C.POINTER(C.c_uint64), _i, C.POINTER(C.c_uint64)]),
     "pkv_pool_match_prefix_keys": (_i, [_vp, _i, C.POINTER(C.c_uint64), _i, c_u8p]),
     "pkv_pool_register_keys": (_i, [_vp, _i, C.POINTER(C.c_uint64), _i, _i]),
+    "pkv_pool_cached_prefix_keys": (_i, [_vp, C.POINTER(C.c_uint64), _i]),
     "pkv_page_hash_keys": (C.c_uint64, [C.POINTER(C.c_uint64), _i, _i]),
     "pkv_pool_assign_slot": (_i, [_vp, _i]),
     "pkv_pool_alloc": (_i, [_vp, _i, _i]),

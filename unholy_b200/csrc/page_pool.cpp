@@ -149,6 +149,18 @@ int PagePool::match_prefix(int seq, Keys tokens, int ntokens, const uint8_t* bou
   return best * page_tokens_;
 }
 
+int PagePool::cached_prefix(Keys k, int ntokens) const {
+  const int limit = (ntokens - 1) / page_tokens_;
+  if (!cache_on_ || limit <= 0) return 0;
+  uint64_t h = kHashSeed;
+  for (int i = 0; i < limit; ++i) {
+    const size_t at = size_t(i) * size_t(page_tokens_);
+    h = k.keys ? chain_page_hash_keys(h, k.keys + at, page_tokens_) : chain_page_hash(h, k.tokens + at, page_tokens_);
+    if (!by_hash_.count(h)) return i;
+  }
+  return limit;
+}
+
 int PagePool::assign_slot(int seq) {
   Seq& s = seqs_[size_t(seq)];
   if (s.slot >= 0) return s.slot;
@@ -402,6 +414,10 @@ int pkv_pool_match_prefix(pkv_pool* p, int seq, const int32_t* tokens, int ntoke
 int pkv_pool_match_prefix_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, const uint8_t* boundary_ok) {
   if (!p || !p->impl.valid(seq) || (!keys && nkeys > 0)) return -1;
   return p->impl.match_prefix(seq, pkv::PagePool::Keys{nullptr, keys}, nkeys, boundary_ok);
+}
+int pkv_pool_cached_prefix_keys(const pkv_pool* p, const uint64_t* keys, int nkeys) {
+  if (!p || (!keys && nkeys > 0)) return -1;
+  return p->impl.cached_prefix(pkv::PagePool::Keys{nullptr, keys}, nkeys);
 }
 int pkv_pool_register_keys(pkv_pool* p, int seq, const uint64_t* keys, int nkeys, int done_pos) {
   if (!p || !p->impl.valid(seq) || (!keys && nkeys > 0)) return PKV_ERR_ARG;

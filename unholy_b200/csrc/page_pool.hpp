@@ -62,6 +62,10 @@ class PagePool {
   int match_prefix(int seq, const int32_t* tokens, int ntokens, const uint8_t* boundary_ok) {
     return match_prefix(seq, Keys{tokens, nullptr}, ntokens, boundary_ok);
   }
+  // How many leading full pages of the positions (at most (ntokens - 1) / page_tokens, as match_prefix) the prefix
+  // cache names right now; nothing changes. The walk match_prefix does before it looks for a resumable boundary
+  // (src/engine/engine.cpp:289-291).
+  int cached_prefix(Keys k, int ntokens) const;
   int assign_slot(int seq);
   bool alloc(int seq, int upto);
   void register_pages(int seq, Keys k, int ntokens, int done_pos);
