@@ -82,6 +82,20 @@ PKV_API int pkv_store_rows(const uint16_t* rows, int n, int width, uint16_t* poo
 PKV_API int pkv_store_rows_fake_fp8(const uint16_t* rows, int n, int width, int quant_cols, int block, uint16_t* pool,
                                     const int32_t* table, int rows_per_page, int row_stride, int row0, pkv_stream_t stream);
 
+/* kv_chain + store_rows in one pass — kv_chain (src/kernels/elem_fast.hpp:29, src/kernels/elem_fast.hip:87-92,124-128;
+ * device body kv_chain_row, src/kernels/elem_dev.hip.hpp:50-87) is the last thing that happens to a step's KV rows
+ * before compress_chunk appends them: rmsnorm with weight w [dim] (bf16), rope on the last 2 * npair values with
+ * freqs float2 [positions][npair] = (cos, sin) at the row's position pos[r], then fake_quant_fp8 (block 64) of the other
+ * values (quant == 0 stops in front of the quantisation). The result goes to the rows' place in the pool (pool NULL:
+ * not appended) and, when rows_out is not NULL, to rows_out [n][dim] (rows_out == rows gives the reference's in-place
+ * kv_chain); `rows` is read once. NOT bit-exact against the reference's GPUs by construction: the reference sums the
+ * squares over 256 threads and uses the hardware rsqrtf, neither of which the source pins down; this kernel uses an
+ * fp32 sum and the correctly rounded 1 / sqrt. Tolerance: one bf16 step on a normalised value (a rotated value inherits
+ * the steps of its two inputs); the quantisation is exact on equal inputs. dim <= 1024 and a multiple of 8, (2 * npair) % 8 == 0, (dim - 2 * npair) % 64 == 0. */
+PKV_API int pkv_store_rows_kv_chain(const uint16_t* rows, uint16_t* rows_out, const uint16_t* w, int n, int dim, float eps,
+                                    const int32_t* pos, const float* freqs, int npair, int quant, uint16_t* pool,
+                                    const int32_t* table, int rows_per_page, int row_stride, int row0, pkv_stream_t stream);
+
 /* store_rows_fp4 — src/kernels/indexer.hpp:20-32, src/kernels/indexer.hip:18-53,802-806.
  * rows [n][128] bf16 -> MXFP4: page p at pool + p*rows_per_page*68; rows_per_page code rows of 64 B (even column =
  * low nibble) followed by rows_per_page scale rows of 4 e8m0 bytes. The reference fixes rows_per_page = 64. */

@@ -29,6 +29,7 @@ _SIGS = {
     "orc_fake_quant_fp4": (None, [_vp, _i, _i, _i, _i]),
     "orc_act_quant_fp8": (None, [_vp, _i, _vp, _vp, _i, _i, _i]),
     "orc_fake_quant_fp8": (None, [_vp, _i, _i, _i, _i]),
+    "orc_kv_chain": (None, [_vp, _vp, _i, _i, C.c_float, _vp, _vp, _i, _i]),
     "orc_store_rows_fp8": (None, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i]),
     "orc_gather_rows": (None, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i]),
     "orc_store_rows_chunks": (None, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _i]),
@@ -107,6 +108,12 @@ def act_quant_fp8(x, cols, block):
 
 def fake_quant_fp8(x, cols, block):
     lib().orc_fake_quant_fp8(_p(x), x.shape[1], x.shape[0], cols, block)
+
+
+def kv_chain(x, w, eps, pos, freqs, npair, quant=True):
+    """In place on x [rows][dim] (bf16 bits); freqs float32 [positions][npair][2] = (cos, sin)."""
+    rows, dim = x.shape
+    lib().orc_kv_chain(_p(x), _p(w), rows, dim, eps, _p(pos), _p(freqs), npair, 1 if quant else 0)
 
 
 def store_rows_fp8(rows, block, codes, scales, table, rows_per_page, s0):

@@ -246,6 +246,40 @@ void orc_fake_quant_fp8(uint16_t* x, int ldx, int rows, int cols, int block) {
     }
 }
 
+// src/kernels/elem_dev.hip.hpp:50-87 (kv_chain_row; launcher src/kernels/elem_fast.hip:87-92,124-128): the chain a KV
+// row goes through before it is appended, in place: rmsnorm with weight w (fp32: sum of squares, r = 1 / sqrt(mean +
+// eps), x = bf16(w * (x * r))), rope on the last 2 * npair dims with freqs[pos][pair] = (cos, sin) on the bf16-rounded
+// values, then fake_quant_fp8 (block 64) of the other dims. The reference's sum runs over 256 threads and a block
+// reduction and its r is the GPU's rsqrtf: the order of the additions and the last bit of r are not fixed by the
+// source, so this restatement (sequential fp32 sum, correctly rounded 1 / sqrt) pins the chain only to a tolerance:
+// one bf16 step on the normalised values (a rotated value inherits the steps of its two inputs); the quantisation
+// itself is exact on equal inputs (quant = 0 stops in front of it).
+void orc_kv_chain(uint16_t* x, const uint16_t* w, int rows, int dim, float eps, const int32_t* pos, const float* freqs,
+                  int npair, int quant) {
+  const int off = dim - 2 * npair;
+  for (int r = 0; r < rows; ++r) {
+    uint16_t* xr = x + size_t(r) * dim;
+    float ss = 0.0f;
+    for (int i = 0; i < dim; ++i) {
+      const float v = bf16_to_f32(xr[i]);
+      ss += v * v;
+    }
+    const float rr = 1.0f / std::sqrt(ss / float(dim) + eps);
+    for (int i = 0; i < dim; ++i) {
+      const float t = bf16_to_f32(xr[i]) * rr;
+      xr[i] = f32_to_bf16(bf16_to_f32(w[i]) * t);
+    }
+    for (int t = 0; t < npair; ++t) {
+      uint16_t* e = xr + off + 2 * t;
+      const float a = bf16_to_f32(e[0]), b = bf16_to_f32(e[1]);
+      const float c = freqs[(size_t(pos[r]) * npair + t) * 2], sn = freqs[(size_t(pos[r]) * npair + t) * 2 + 1];
+      e[0] = f32_to_bf16(a * c - b * sn);
+      e[1] = f32_to_bf16(a * sn + b * c);
+    }
+    if (quant) orc_fake_quant_fp8(xr, dim, 1, off, 64);
+  }
+}
+
 // src/kernels/glm_fast.hip:29-31,37-51,752-756 (glm_store_latent), layout src/kernels/glm_fast.hpp:23-28: codes
 // [pages * rows_per_page][width] and scales [pages * rows_per_page][width / block] are two separate arrays, both
 // indexed by the physical row id of position s0 + r.

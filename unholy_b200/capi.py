@@ -100,6 +100,7 @@ _SIGS = {
     "pkv_step_gather_fp8_pools": (_i, [C.POINTER(PkvStep), _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp]),
     "pkv_hadamard128": (_i, [_vp, _sz, _vp]),
     "pkv_store_rows_fake_fp8": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "pkv_store_rows_kv_chain": (_i, [_vp, _vp, _vp, _i, _i, C.c_float, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "pkv_topk_scratch_words": (_sz, [_i, _i, _i]),
     "pkv_topk_bf16": (_i, [_vp, _i, _i, C.c_longlong, _i, _vp, _vp, _sz, _vp]),
     "pkv_topk_static_scratch_words": (_sz, []),

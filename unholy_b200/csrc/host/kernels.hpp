@@ -143,6 +143,19 @@ inline void store_rows_fake_fp8(const bf16* rows, int n, int width, int quant_co
   pkv_throw(pkv_store_rows_fake_fp8(rows, n, width, quant_cols, block, dst.pool, dst.table, dst.rows_per_page, dst.row_stride,
                                     row0, reinterpret_cast<pkv_stream_t>(st)), "store_rows_fake_fp8");
 }
+// src/kernels/elem_fast.hpp:29: kv_chain in place, and the same chain fused with the append that follows it in
+// compress_chunk (kv_chain, then store_rows of the same rows: one pass, the rows are read once).
+inline void kv_chain(bf16* kv, const bf16* w, int rows, int dim, float eps, const int32_t* pos, const float2* freqs, int npair,
+                     cudaStream_t st) {
+  pkv_throw(pkv_store_rows_kv_chain(kv, kv, w, rows, dim, eps, pos, reinterpret_cast<const float*>(freqs), npair, 1, nullptr, nullptr,
+                                    0, 0, 0, reinterpret_cast<pkv_stream_t>(st)), "kv_chain");
+}
+inline void store_rows_kv_chain(const bf16* kv, bf16* kv_out, const bf16* w, int rows, int dim, float eps, const int32_t* pos,
+                                const float2* freqs, int npair, PagedRows dst, int row0, cudaStream_t st) {
+  pkv_throw(pkv_store_rows_kv_chain(kv, kv_out, w, rows, dim, eps, pos, reinterpret_cast<const float*>(freqs), npair, 1, dst.pool,
+                                    dst.table, dst.rows_per_page, dst.row_stride, row0, reinterpret_cast<pkv_stream_t>(st)),
+            "store_rows_kv_chain");
+}
 // src/kernels/ref.hpp:63.
 inline void hadamard128(bf16* x, size_t nseg, cudaStream_t st) {
   pkv_throw(pkv_hadamard128(x, nseg, reinterpret_cast<pkv_stream_t>(st)), "hadamard128");

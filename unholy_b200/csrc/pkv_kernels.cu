@@ -1079,6 +1079,78 @@ __global__ void __launch_bounds__(256) store_rows_fake_fp8_kernel(const uint16_t
   }
 }
 
+// The KV row chain in front of the append (ewtodd/unholy's kv_chain_row, src/kernels/elem_dev.hip.hpp:50-87) and the
+// append itself in one pass: rmsnorm with weight w, rope on the last 2 * npair values, fake_quant_fp8 (block 64) of
+// the others, then the row goes to its place in the pool (and / or to rows_out). One warp per row, lane l holds the
+// 16-byte vectors l, l + 32, ... of the row (at most kChainVecs each): a quantisation block of 64 values is eight
+// neighbouring lanes, a rope pair lies inside one vector. The sum of squares is fp32, lane-partial then a shuffle
+// tree; r is the correctly rounded 1 / sqrt (IEEE division and square root, no approximation).
+constexpr int kChainVecs = 4;  // rows of up to 1024 values
+__global__ void __launch_bounds__(256) kv_chain_store_kernel(const uint16_t* __restrict__ rows, uint16_t* rows_out,
+                                                             const uint16_t* __restrict__ w, int n, int dim, float eps,
+                                                             const int32_t* __restrict__ pos, const float2* __restrict__ freqs,
+                                                             int npair, int quant, uint16_t* pool, OneTable tb, int row_stride, int row0) {
+  const int lane = threadIdx.x & 31, vecs = dim >> 3, off = dim - 2 * npair;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(rows + size_t(r) * dim);
+    float v[kChainVecs][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kChainVecs; ++i) {
+      const int vi = lane + 32 * i;
+      pkv::unpack8(vi < vecs ? ld_stream(src + vi) : make_uint4(0, 0, 0, 0), v[i]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    const float rr = 1.0f / sqrtf(ss / float(dim) + eps);
+    const int p = __ldg(&pos[r]);
+    uint16_t* dst = pool ? pool + one_row(tb, row0 + r) * size_t(row_stride) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kChainVecs; ++i) {
+      const int vi = lane + 32 * i;
+      const bool live = vi < vecs;
+      float wv[8];
+      pkv::unpack8(live ? __ldg(reinterpret_cast<const uint4*>(w) + vi) : make_uint4(0, 0, 0, 0), wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = pkv::bf16_bits_to_f32(pkv::f32_to_bf16_bits(wv[e] * (v[i][e] * rr)));
+      const int c0 = vi * 8;  // first column of this vector
+      if (live && c0 >= off) {  // rope: pairs (2t, 2t + 1) of the last 2 * npair columns
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float2 f = __ldg(&freqs[size_t(p) * npair + ((c0 - off + e) >> 1)]);
+          const float a = v[i][e], b = v[i][e + 1];
+          v[i][e] = pkv::bf16_bits_to_f32(pkv::f32_to_bf16_bits(a * f.x - b * f.y));
+          v[i][e + 1] = pkv::bf16_bits_to_f32(pkv::f32_to_bf16_bits(a * f.y + b * f.x));
+        }
+      }
+      // fake_quant_fp8, block 64 = this lane and its seven neighbours (every lane runs the shuffles)
+      const float amax = pkv::group_max(pkv::absmax8(v[i]), 8);
+      uint32_t out[4];
+      if (quant && c0 < off) {
+        const float sc = pkv::e8m0_bits_to_f32(pkv::fp8_scale_exp(amax));
+        const uint2 codes = pkv::fp8_pack8(v[i], sc);
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const uint32_t lo = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(((e < 4 ? codes.x : codes.y) >> (8 * (e & 3))) & 0xffu) * sc);
+          const uint32_t hi = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(((e < 4 ? codes.x : codes.y) >> (8 * ((e + 1) & 3))) & 0xffu) * sc);
+          out[e >> 1] = lo | (hi << 16);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) out[e >> 1] = (__float_as_uint(v[i][e]) >> 16) | (__float_as_uint(v[i][e + 1]) & 0xffff0000u);
+      }
+      if (live) {
+        const uint4 o = make_uint4(out[0], out[1], out[2], out[3]);
+        if (dst) st_stream(reinterpret_cast<uint4*>(dst) + vi, o);
+        if (rows_out) reinterpret_cast<uint4*>(rows_out + size_t(r) * dim)[vi] = o;
+      }
+    }
+  }
+}
+
 // MXFP4 append of 128-wide rows: 16 threads per row.
 __global__ void __launch_bounds__(256) store_rows_fp4_kernel(const uint16_t* __restrict__ rows, int n, uint8_t* pool,
                                                              OneTable tb, int row0) {
@@ -1800,6 +1872,24 @@ int pkv_store_rows_fake_fp8(const uint16_t* rows, int n, int width, int quant_co
   store_rows_fake_fp8_kernel<<<grid_for(total, 256, 16), 256, 0, stream>>>(rows, total, width / 8, quant_cols / 8, block / 8, pool,
                                                                            OneTable{table, rows_per_page}, row_stride, row0);
   PKV_LAUNCH_CHECK("store_rows_fake_fp8");
+  return PKV_OK;
+}
+
+int pkv_store_rows_kv_chain(const uint16_t* rows, uint16_t* rows_out, const uint16_t* w, int n, int dim, float eps, const int32_t* pos,
+                            const float* freqs, int npair, int quant, uint16_t* pool, const int32_t* table, int rows_per_page,
+                            int row_stride, int row0, pkv_stream_t stream) {
+  if (n <= 0) return PKV_OK;
+  if (!rows || !w || !pos || (npair > 0 && !freqs)) return fail(PKV_ERR_ARG, "pkv_store_rows_kv_chain: null pointer");
+  if (!pool && !rows_out) return fail(PKV_ERR_ARG, "pkv_store_rows_kv_chain: neither a pool nor rows_out to write to");
+  if (pool && (!table || rows_per_page <= 0 || row_stride < dim || row_stride % 8 != 0 || row0 < 0))
+    return fail(PKV_ERR_ARG, "pkv_store_rows_kv_chain: bad pool geometry");
+  if (dim <= 0 || dim % 8 != 0 || dim > 256 * kChainVecs || npair < 0 || 2 * npair > dim || (2 * npair) % 8 != 0 || (dim - 2 * npair) % 64 != 0)
+    return fail(PKV_ERR_ARG, "pkv_store_rows_kv_chain: dim <= 1024, a multiple of 8; the rope part a multiple of 8 values, the rest of 64");
+  if (!aligned16(rows) || !aligned16(w) || !aligned16(pool) || !aligned16(rows_out) || (reinterpret_cast<uintptr_t>(freqs) & 7u))
+    return fail(PKV_ERR_ARG, "pkv_store_rows_kv_chain: rows, w, pool and rows_out must be 16-byte aligned, freqs 8-byte");
+  kv_chain_store_kernel<<<grid_for((long long)n * 32, 256, 8), 256, 0, stream>>>(rows, rows_out, w, n, dim, eps, pos, reinterpret_cast<const float2*>(freqs),
+                                                                                  npair, quant, pool, OneTable{table, rows_per_page}, row_stride, row0);
+  PKV_LAUNCH_CHECK("kv_chain_store_kernel");
   return PKV_OK;
 }
 
