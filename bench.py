@@ -46,8 +46,10 @@ FP4_PAGE_BYTES = RPP * 68             # 4,352
 APPEND_BYTES = 2 * ROW_BYTES + (KEY_DIM * 2 + 68)      # 2304 + 324
 GATHER_BYTES = K_SEL * 2 * ROW_BYTES                   # 2048 rows read and written
 STEP_BYTES_PER_GPU = LAYERS * NSEQ * (APPEND_BYTES + GATHER_BYTES)
-# dram__bytes_read.sum + dram__bytes_write.sum of one per-layer launch (ncu capture summarised under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 249_350_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one per-layer launch: the mean of the three launches captured by ncu at
+# 32k context with one resident pool (the summary under profiles/ gives the command). A launch there processes the same
+# units as the benchmark's, so the figure is not scaled.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 246_014_635
 WORKLOAD_NAME = "decode43: 64 seq x 128k ctx per GPU, page 64, 43 layers, bf16 576 rows + MXFP4 128 keys, top-2048 gather"
 
 
@@ -526,7 +528,9 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.variant == "bulk" and lpl == 1) else None,
-                         "traffic_source": "profiles/step_bulk_kernel_decode43_small.md (ncu dram__bytes_read+write, one launch)",
+                         "traffic_source": "profiles/step_bulk_kernel_decode43_context32k.md: ncu dram__bytes_read.sum + dram__bytes_write.sum, "
+                                           "mean of 3 launches at 32k context with one resident pool (2.5 GB; the same units per launch as "
+                                           "the benchmark launch, so not scaled); a third of the written bytes is still in L2 when a kernel ends",
                          "peak_kind": "of " + peak_kind,
                          "kernel": "step_bulk_kernel" if args.variant == "bulk" else "step_vec_kernel",
                          "algorithmic_bytes_per_launch": int(call_bytes)},
