@@ -80,3 +80,20 @@ def test_step_run_validates_before_touching_the_device(pkv):
     descs[0].page_bytes = 100                                                                  # not a multiple of 16
     assert pkv.pkv_copy_pages(descs, 1, 4096, 4096, 1, 0, 0, None) == capi.PKV_ERR_ARG
     assert pkv.pkv_tune(99, 0) == capi.PKV_ERR_ARG
+
+
+def test_host_objects_validate_their_arguments(pkv):
+    """The sharded host and the snapshot store refuse bad configurations before touching a device or a file."""
+    cfg = capi.PkvShardConfig(0, 16, 64, 576, 576, 2, 4, 8, 64, 0)          # no shards
+    assert not pkv.pkv_shards_create(C.byref(cfg), (C.c_int * 1)(0)) and b"bad configuration" in pkv.pkv_last_error()
+    cfg = capi.PkvShardConfig(1, 16, 64, 570, 570, 2, 4, 8, 64, 0)          # width not a multiple of 8
+    assert not pkv.pkv_shards_create(C.byref(cfg), (C.c_int * 1)(0))
+    cfg = capi.PkvShardConfig(1, 16, 64, 576, 576, 100, 4, 8, 64, 1)        # 200 pools: more than one migration launch takes
+    assert not pkv.pkv_shards_create(C.byref(cfg), (C.c_int * 1)(0))
+    assert pkv.pkv_shards_owner(None, 0) == -1 and pkv.pkv_shards_migrate_pending(None) == -1
+    assert pkv.pkv_shards_step(None, None) == capi.PKV_ERR_ARG
+    assert not pkv.pkv_snap_create(-1, None, 0, None, 0, capi.SNAP_IO_HOOK(0), None)
+    s = pkv.pkv_snap_create(2, None, 0, b"/nonexistent-dir/x", 4, capi.SNAP_IO_HOOK(0), None)   # snapshots not in host memory: tier off
+    assert s and pkv.pkv_snap_disk_on(s) == 0
+    assert pkv.pkv_snap_take(s) == 0 and pkv.pkv_snap_take(s) == 1 and pkv.pkv_snap_take(s) == -1   # slot 0 first (engine.cpp:90)
+    pkv.pkv_snap_destroy(s)
