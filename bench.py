@@ -74,6 +74,7 @@ def parse_args():
                     help="1 (default): the 43 layer calls of a step are captured once into a CUDA graph and replayed; 0: called directly")
     ap.add_argument("--workload", choices=["decode43", "prefill", "churn", "sharded", "topk", "snapshot", "gather_fp8"], default="decode43",
                     help="decode43 is the benchmark line; the others measure the remaining operations of the path")
+    ap.add_argument("--requests", type=int, default=64, help="--workload sharded: requests in total (64 = configuration 5)")
     ap.add_argument("--topk-shape", default="", help="rows,keys,k for --workload topk (default: the decode shape 64,131072,2048)")
     return ap.parse_args()
 
@@ -947,7 +948,7 @@ def measure_sharded(args, devices):
     from unholy_b200 import capi
     lib = capi.lib()
     G = len(devices)
-    L, NREQ = LAYERS, 64
+    L, NREQ = LAYERS, max(1, getattr(args, "requests", 64))
     budget_tokens = 160_000 if args.small else 2_800_000
     lo, hi = (512, 16384) if args.small else (2048, 1 << 20)
     rng = np.random.Generator(np.random.MT19937(5))
@@ -1051,7 +1052,7 @@ def measure_sharded(args, devices):
     moved = []
     if G > 1:
         mrng = np.random.Generator(np.random.MT19937(55))
-        movers = mrng.choice(NREQ, size=6, replace=False).astype(np.int32)
+        movers = mrng.choice(NREQ, size=min(6, NREQ), replace=False).astype(np.int32)
         dsts = np.array([(int(r) % G + 1 + int(mrng.integers(0, G - 1))) % G for r in movers], np.int32)
         moved = [int(r) for r in movers]
         capi.check(lib.pkv_shards_sync(S))
@@ -1089,7 +1090,7 @@ def measure_sharded(args, devices):
         capi.check(lib.pkv_shards_sync(S))
     # verification: requests read back through their owner's table (2 layers) equal the pattern their writers left
     ok = True
-    for r in sorted(set(list(range(6)) + moved)):
+    for r in sorted(set(list(range(min(6, NREQ))) + moved)):
         g = lib.pkv_shards_owner(S, r)
         with torch.cuda.device(devices[g]), torch.cuda.stream(streams[g]):
             dev = torch.device("cuda", devices[g])

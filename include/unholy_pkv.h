@@ -44,7 +44,7 @@ enum {
 PKV_API const char* pkv_last_error(void);
 PKV_API int pkv_abi_version(void);
 /* Performance knobs (no counterpart in the reference; results never depend on them). knob 0: bulk pipeline shape
- * STAGES*100+ROWS (0 = chosen by launch size); 1: bulk CTAs per SM (0 = fill shared memory); 2: programmatic dependent
+ * STAGES*100+ROWS, one of 304, 308, 408, 316 (0 = chosen by launch size); 1: bulk CTAs per SM (0 = fill shared memory); 2: programmatic dependent
  * launch on/off; 3: CTAs per SM of the vector kernels; 4: appends as tiles of the bulk launch on/off; 5: tiles whose
  * addresses are resolved together (-1 = by launch size, 0 = a warp's worth); 6: resolve the next batch late (0/1);
  * 7: top-k path (0 = one thread-block-cluster launch where the shape allows it, 1 = always the four launches that use

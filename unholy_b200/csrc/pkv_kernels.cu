@@ -1679,27 +1679,13 @@ int launch_bulk(const StepParams& P, int ctas_per_sm, cudaStream_t st) {
 int dispatch_bulk(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t st) {
   if (shape == 0) shape = many_tiles_per_cta(P) ? 308 : 304;
   switch (shape) {  // STAGES * 100 + ROWS
-    case 302: return launch_bulk<3, 2>(P, ctas_per_sm, st);
-    case 402: return launch_bulk<4, 2>(P, ctas_per_sm, st);
-    case 602: return launch_bulk<6, 2>(P, ctas_per_sm, st);
     case 304: return launch_bulk<3, 4>(P, ctas_per_sm, st);
-    case 404: return launch_bulk<4, 4>(P, ctas_per_sm, st);
-    case 604: return launch_bulk<6, 4>(P, ctas_per_sm, st);
-    case 804: return launch_bulk<8, 4>(P, ctas_per_sm, st);
-    case 1204: return launch_bulk<12, 4>(P, ctas_per_sm, st);
     case 308: return launch_bulk<3, 8>(P, ctas_per_sm, st);
     case 408: return launch_bulk<4, 8>(P, ctas_per_sm, st);
-    case 508: return launch_bulk<5, 8>(P, ctas_per_sm, st);
-    case 608: return launch_bulk<6, 8>(P, ctas_per_sm, st);
-    case 808: return launch_bulk<8, 8>(P, ctas_per_sm, st);
     case 316: return launch_bulk<3, 16>(P, ctas_per_sm, st);
-    case 416: return launch_bulk<4, 16>(P, ctas_per_sm, st);
-    case 616: return launch_bulk<6, 16>(P, ctas_per_sm, st);
-    case 332: return launch_bulk<3, 32>(P, ctas_per_sm, st);
-    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled pipeline shape");
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled shape of the single-warp pipeline (304, 308, 408, 316)");
   }
 }
-
 
 template <int STAGES, int ROWS>
 int launch_pipe(const StepParams& P0, int ctas_per_sm, cudaStream_t st) {
@@ -1772,15 +1758,10 @@ int dispatch_pipe(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t 
   if (shape == 0) shape = 308;
   switch (shape) {  // STAGES * 100 + ROWS
     case 304: return launch_pipe<3, 4>(P, ctas_per_sm, st);
-    case 404: return launch_pipe<4, 4>(P, ctas_per_sm, st);
-    case 604: return launch_pipe<6, 4>(P, ctas_per_sm, st);
     case 308: return launch_pipe<3, 8>(P, ctas_per_sm, st);
     case 408: return launch_pipe<4, 8>(P, ctas_per_sm, st);
-    case 508: return launch_pipe<5, 8>(P, ctas_per_sm, st);
     case 316: return launch_pipe<3, 16>(P, ctas_per_sm, st);
-    case 416: return launch_pipe<4, 16>(P, ctas_per_sm, st);
-    case 332: return launch_pipe<3, 32>(P, ctas_per_sm, st);
-    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled shape of the warp-specialised pipeline");
+    default: return fail(PKV_ERR_ARG, "PKV_BULK_SHAPE names no compiled shape of the warp-specialised pipeline (304, 308, 408, 316)");
   }
 }
 
