@@ -1261,10 +1261,20 @@ def run_gather_fp8(args):
     width, block, rpp, T, k = 512, 64, 256, NSEQ, K_SEL
     rows = (1 << 16) if args.small else (1 << 20)
     pages = rows // rpp
-    codes = torch.randint(0, 256, (rows, width), generator=g, device=dev, dtype=torch.uint8)
-    codes[(codes & 0x7F) == 0x7F] = 0x38                    # no NaN patterns: the check compares values
-    scales = torch.randint(120, 134, (rows, width // block), generator=g, device=dev, dtype=torch.uint8)
+    # The pool holds what the append wrote: N(0,1) latent rows with per-row magnitudes 2^[-3,3], quantised by the library's
+    # own glm_store_latent (pkv_store_rows_fp8) through the shuffled block table, so codes and scales have the
+    # distribution real rows have (uniformly random code bytes would be mostly e4m3 subnormals and zeros).
     table = torch.randperm(pages, generator=g, device=dev).to(torch.int32)
+    codes = torch.zeros(rows, width, device=dev, dtype=torch.uint8)
+    scales = torch.zeros(rows, width // block, device=dev, dtype=torch.uint8)
+    sp0 = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for r0 in range(0, rows, 1 << 16):
+        n = min(1 << 16, rows - r0)
+        mag = torch.ldexp(torch.ones(n, 1, device=dev), torch.randint(-3, 4, (n, 1), generator=g, device=dev))
+        lat = (torch.randn(n, width, generator=g, device=dev) * mag).to(torch.bfloat16)
+        capi.check(lib.pkv_store_rows_fp8(lat.data_ptr(), n, width, block, codes.data_ptr(), scales.data_ptr(), table.data_ptr(), rpp, r0, sp0))
+    torch.cuda.synchronize()
+    del lat, mag
     idx = torch.randint(0, rows, (T, k), generator=g, device=dev, dtype=torch.int32)
     idx[:, -5:] = -1
     vis = torch.full((T,), rows, dtype=torch.int32, device=dev)
@@ -1372,10 +1382,25 @@ def run_gather_fp8(args):
                                        out_l.data_ptr(), sp))
     torch.cuda.synchronize()
     ok_c = bool(torch.equal(out_c.view(torch.int16), out_l.view(torch.int16)))
+    # What writing the output alone costs: the kernel writes two of every three bytes it moves, and this GPU sustains far
+    # less for writes alone than for a copy (whose reads and writes overlap), so the output's fill time is the floor.
+    floor_buf = torch.empty_like(out)
+    for _ in range(3):
+        floor_buf.zero_()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        floor_buf.zero_()
+    e1.record()
+    torch.cuda.synchronize()
+    us_fill = e0.elapsed_time(e1) / reps * 1e3
     nbytes = T * k * (width + width // block + width * 2)
     _emit("gather_fp8", nbytes / (us * 1e-6) / 1e9, us * 1e-3, {
         "config": {"workload": f"{T} x {k} entries of fp8 rows (512 e4m3 + 8 e8m0) -> bf16, pool of {rows} rows (pkv_gather_rows_fp8)"},
         "us_per_call": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 2), "bit_exact_check": {"ok": ok and ok_b and ok_c},
+        "write_only_floor": {"what": "zero-fill (torch) of a buffer the size of the output, same timing loop",
+                             "us": round(us_fill, 2), "GBps_written": round(out.numel() * 2 / (us_fill * 1e-6) / 1e9, 1),
+                             "floor_over_kernel": round(us_fill / us, 3)},
         "step_call_64_sequences": {"what": "pkv_step_gather_fp8: 64 sequences x 2048 entries, own block tables, one launch",
                                    "us_per_call": round(us_b, 2), "GBps": round(nbytes / (us_b * 1e-6) / 1e9, 1), "ok": ok_b},
         "glm_decode_chain": {"what": f"pkv_topk_f32 (top-{kp} of {npool} pool scores x {T}) + pkv_step_gather_fp8_pools "

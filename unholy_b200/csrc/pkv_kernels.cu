@@ -1250,30 +1250,32 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
 // codes: a 16-byte load, sixteen decodes, two 16-byte stores; a thread has four units in flight. Masked entries give
 // zero rows.
 //
-// Decoding two codes at a time on the conversion hardware: an e4m3 byte b read as the fp16 pattern
-// (b & 0x80) << 8 | (b & 0x7f) << 7 is the same number divided by 256, subnormals and zeros included (fp16 has the
-// e4m3 exponent field with bias 15 instead of 7); fp16 -> fp32 is exact, the product with 2^(scale - 127 + 8) is exact
-// (a power of two, no underflow past fp32's subnormals), and fp32 -> bf16 rounds to nearest even as the scalar
-// f32_to_bf16_bits does. The two NaN codes, scale byte 0 (the factor is +0 in the reference's decode, not 2^-127) and
-// scale bytes above 246 (no finite fp32 factor) take the scalar path.
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t q, bool high, float factor) {
-  const uint32_t w = __byte_perm(q, 0u, high ? 0x4342u : 0x4140u);  // bytes (b0, b1) or (b2, b3), one per 16-bit lane
-  const uint32_t h = ((w & 0x00800080u) << 8) | ((w & 0x007f007fu) << 7);
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
-  const __nv_bfloat162 o = __floats2bfloat162_rn(f.x * factor, f.y * factor);
-  return *reinterpret_cast<const uint32_t*>(&o);
+// Decoding without a conversion instruction. A normal e4m3 code b = s eeee mmm times a power of two IS a bf16 number
+// with the same three mantissa bits: its low seven bits shifted left by four land exactly on bf16's exponent and
+// mantissa fields (eeee in the low exponent bits, mmm in the top mantissa bits), and the scale only adds to the
+// exponent. With one code per 16-bit lane of w (a byte permute), w * 16 puts the low seven bits in place and the sign
+// at bit 11; adding sign * 0xF0 moves it to bit 15 (0x80 * 16 + 0x80 * 0xF0 = 0x8000); nothing carries between the lanes
+// while the result is a normal bf16 number: scale bytes 7 .. 246. Exact: nothing is rounded. Codes with a zero exponent
+// field (zeros and e4m3 subnormals), the two NaN codes and the other scale bytes take the scalar decode, which follows
+// the reference operation for operation. (Decoding pairs on the conversion hardware instead, fp16 -> fp32 -> bf16, kept
+// that unit 84 % busy and took the same time: the kernel is bound by its stores, not by arithmetic.)
+__device__ __forceinline__ uint32_t dequant_lanes(uint32_t w, uint32_t exp_add) {
+  return w * 16u + exp_add + (w & 0x00800080u) * 0xF0u;
 }
 __device__ __forceinline__ void dequant_unit(const uint4& q, uint32_t scale_bits, uint32_t* w16) {
   const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
-  const uint32_t low7 = 0x7f7f7f7fu;
-  const bool any_nan = __vcmpeq4(q.x & low7, low7) | __vcmpeq4(q.y & low7, low7) | __vcmpeq4(q.z & low7, low7) |
-                       __vcmpeq4(q.w & low7, low7);
-  if (!any_nan && scale_bits - 1u <= 245u) {
-    const float factor = __uint_as_float((scale_bits + 8u) << 23);
+  // Any code with a zero exponent field, or any NaN code (low seven bits all ones)? A zero exponent field borrows into
+  // bit 7 of its byte when 8 is subtracted from every field; a NaN code carries into it when 1 is added to the low seven
+  // bits of every byte. (A borrow may also reach the next byte: a unit flagged for nothing only takes the slow way.)
+  uint32_t flag = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) flag |= ((qs[i] & 0x78787878u) - 0x08080808u) | ((qs[i] & 0x7f7f7f7fu) + 0x01010101u);
+  if ((flag & 0x80808080u) == 0u && scale_bits - 7u <= 239u) {
+    const uint32_t exp_add = ((scale_bits - 7u) << 7) * 0x00010001u;  // the same exponent offset in both 16-bit lanes
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      w16[2 * i] = dequant_pair(qs[i], false, factor);
-      w16[2 * i + 1] = dequant_pair(qs[i], true, factor);
+      w16[2 * i] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4140u), exp_add);      // codes 0 and 1 of the word
+      w16[2 * i + 1] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4342u), exp_add);  // codes 2 and 3
     }
   } else {
     const float sc = pkv::e8m0_bits_to_f32(scale_bits);
