@@ -442,6 +442,9 @@ PKV_API int pkv_pool_register(pkv_pool* p, int seq, const int32_t* tokens, int n
 /* release (engine.cpp:208-232): unref pages tail first and give the slot back. The handle stays open and empty (a
  * preempted request is admitted again later, engine.cpp:428-435); pkv_pool_seq_close releases and retires it. */
 PKV_API int pkv_pool_release(pkv_pool* p, int seq);
+/* The page half of drop_prefix (engine.cpp:419-425): the pages of a matched prefix whose snapshot could not be read
+ * back are unreferenced tail first; the sequence keeps its slot and is computed again from position 0. */
+PKV_API int pkv_pool_drop_prefix(pkv_pool* p, int seq);
 PKV_API int pkv_pool_seq_close(pkv_pool* p, int seq);
 
 /* Copy-on-write fork: the new sequence shares ALL pages of positions [0, ntokens) of `from`, including a partial

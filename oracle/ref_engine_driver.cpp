@@ -4,9 +4,14 @@
 // submitted chunk and state save, every finished request, and the allocator counters after each iterate(). The
 // page-pool tests replay that trace into the from-scratch allocator and compare block tables entry for entry.
 // TEST INFRASTRUCTURE ONLY; output goes to oracle/_ref/.
+#include <atomic>
+#include <chrono>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "engine/engine.hpp"
@@ -29,6 +34,7 @@ constexpr int kVocab = 512;
 //   2 table_index                                  set_block_tables (the table itself in tables[table_index])
 //   3 seq                                          request finished (its pages were released)
 //   4 running waiting free_pages cached_pages preemptions snapshots free_snapshots    after one iterate()
+//   5 disk_snapshots snapshot_io spills disk_hits  after one iterate(), only with the disk tier (follows record 4)
 struct Trace {
   std::vector<int64_t> ev;
   std::vector<std::vector<int32_t>> tables;
@@ -46,6 +52,14 @@ class RecordingModel final : public StepModel {
   int num_pages() const override { return pages_; }
   int page_tokens() const override { return page_; }
   int num_snapshots() const override { return snaps_; }
+  // One 4096-byte, 4096-aligned region per snapshot once give_host_snapshots() was called (the disk tier needs them).
+  void give_host_snapshots() {
+    snap_mem_.reset(static_cast<uint8_t*>(std::aligned_alloc(4096, size_t(snaps_ > 0 ? snaps_ : 1) * 4096)));
+    std::memset(snap_mem_.get(), 0, size_t(snaps_ > 0 ? snaps_ : 1) * 4096);
+  }
+  void snapshot_host(int id, std::vector<std::pair<uint8_t*, size_t>>& segs) const override {
+    if (snap_mem_) segs.push_back({snap_mem_.get() + size_t(id) * 4096, size_t(4096)});
+  }
   void set_block_tables(const std::vector<int32_t>& t) override {
     tr_.ev.push_back(2);
     tr_.ev.push_back(int64_t(tr_.tables.size()));
@@ -70,6 +84,12 @@ class RecordingModel final : public StepModel {
       tr_.ev.push_back(s.slot);
       tr_.ev.push_back(s.snapshot);
     }
+    // A save leaves the snapshot's bytes different from whatever the slot held before (the disk tier checksums them).
+    if (snap_mem_)
+      for (const StateOp& s : in.save) {
+        const uint64_t v = mix(++save_counter_);
+        for (size_t i = 0; i < 4096; i += 8) std::memcpy(snap_mem_.get() + size_t(s.snapshot) * 4096 + i, &v, 8);
+      }
     // Logits: one-hot on a token that depends only on (request, position), never EOS (id 1).
     logits_.assign(in.logit_rows.size() * size_t(kVocab), 0.0f);
     for (size_t r = 0; r < in.logit_rows.size(); ++r) {
@@ -88,13 +108,34 @@ class RecordingModel final : public StepModel {
   int pages_, page_, slots_, pps_, max_tokens_, snaps_;
   Trace& tr_;
   std::vector<float> logits_;
-  uint64_t ticket_ = 0;
+  uint64_t ticket_ = 0, save_counter_ = 0;
+  struct Free {
+    void operator()(uint8_t* p) const { std::free(p); }
+  };
+  std::unique_ptr<uint8_t, Free> snap_mem_;
+};
+
+// Disk operations under the test's control: the I/O thread's hook (EngineConfig::io_hook, src/engine/engine.hpp:131)
+// holds operation number i until `released` exceeds i, so the test decides between which two iterate() calls an
+// operation completes. Waits are bounded: a forgotten release delays, it does not hang.
+struct Gate {
+  std::atomic<long> started{0}, released{0};
+  void hook() {
+    const long i = started.fetch_add(1);
+    for (int spin = 0; spin < 200000 && released.load() <= i; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  }
 };
 
 struct Driver {
   Trace tr;
+  Gate gate;
+  bool disk = false;
   std::unique_ptr<RecordingModel> model;
   std::unique_ptr<Engine> engine;
+  ~Driver() {
+    gate.released = 1l << 40;  // whatever still waits at the gate goes through before the engine joins its I/O thread
+    engine.reset();
+  }
 };
 
 }  // namespace
@@ -115,6 +156,41 @@ void* refeng_create(int num_pages, int page_tokens, int max_slots, int max_pages
   };
   d->engine = std::make_unique<Engine>(*d->model, cfg, false);
   return d;
+}
+
+// The same engine with the snapshot disk tier on: `disk_slots` slots in `dir`/snapshots.bin, host memory for the
+// snapshots, disk operations gated (refeng_io_release), and no waiting for a RAM slot by the clock (save_wait_ms = 0:
+// a save that finds no slot is skipped at once), so that the trace depends on the order of calls only.
+void* refeng_create_disk(int num_pages, int page_tokens, int max_slots, int max_pages_per_seq, int max_batch_tokens,
+                         int num_snapshots, const char* dir, int disk_slots) {
+  auto* d = new Driver;
+  d->disk = true;
+  d->model = std::make_unique<RecordingModel>(num_pages, page_tokens, max_slots, max_pages_per_seq, max_batch_tokens,
+                                              num_snapshots, d->tr);
+  d->model->give_host_snapshots();
+  EngineConfig cfg;
+  cfg.max_batch_tokens = max_batch_tokens;
+  cfg.prefix_cache = true;
+  cfg.snapshot_dir = dir;
+  cfg.disk_snapshots = disk_slots;
+  cfg.save_wait_ms = 0;
+  cfg.io_hook = [d](bool) { d->gate.hook(); };
+  cfg.on_finish = [d](const RequestLog& l) {
+    d->tr.ev.push_back(3);
+    d->tr.ev.push_back(int64_t(l.id));
+  };
+  d->engine = std::make_unique<Engine>(*d->model, cfg, false);
+  return d;
+}
+
+// Lets the next n gated disk operations run and returns when they have completed: the I/O thread runs one operation at
+// a time, so either a later operation has reached the gate (everything before it is done) or, with nothing queued
+// behind them, the last one has had 5 ms since it passed the gate (it is one 4 KB read or write).
+void refeng_io_release(void* h, int n) {
+  auto* d = static_cast<Driver*>(h);
+  const long target = d->gate.released.fetch_add(n) + n;
+  for (int spin = 0; spin < 100000 && d->gate.started.load() < target; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  for (int spin = 0; spin < 50 && d->gate.started.load() <= target; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
 }
 
 void refeng_destroy(void* h) { delete static_cast<Driver*>(h); }
@@ -153,6 +229,9 @@ uint64_t refeng_submit_images(void* h, const int32_t* prompt, int n, int max_tok
   return d->engine->submit(std::move(r), [](GenOutput&&) {});
 }
 
+// Engine::abort (src/engine/engine.hpp:166): takes effect at the start of the next iterate().
+void refeng_abort(void* h, uint64_t id) { static_cast<Driver*>(h)->engine->abort(id); }
+
 int refeng_iterate(void* h) {
   auto* d = static_cast<Driver*>(h);
   const bool did = d->engine->iterate();
@@ -160,6 +239,9 @@ int refeng_iterate(void* h) {
   for (int64_t v : {int64_t(4), int64_t(s.running), int64_t(s.waiting), int64_t(s.free_pages), int64_t(s.cached_pages),
                     int64_t(s.preemptions), int64_t(s.snapshots), int64_t(s.free_snapshots)})
     d->tr.ev.push_back(v);
+  if (d->disk)
+    for (int64_t v : {int64_t(5), int64_t(s.disk_snapshots), int64_t(s.snapshot_io), int64_t(s.spills), int64_t(s.disk_hits)})
+      d->tr.ev.push_back(v);
   return did ? 1 : 0;
 }
 

@@ -36,6 +36,9 @@ def refeng():
         pytest.skip("oracle/_ref/libref_engine.so not built (no reference checkout here)")
     h = C.CDLL(str(libs["engine"]))
     h.refeng_create.restype, h.refeng_create.argtypes = C.c_void_p, [C.c_int] * 6
+    h.refeng_create_disk.restype, h.refeng_create_disk.argtypes = C.c_void_p, [C.c_int] * 6 + [C.c_char_p, C.c_int]
+    h.refeng_io_release.argtypes = [C.c_void_p, C.c_int]
+    h.refeng_abort.argtypes = [C.c_void_p, C.c_uint64]
     h.refeng_destroy.argtypes = [C.c_void_p]
     h.refeng_submit.restype, h.refeng_submit.argtypes = C.c_uint64, [C.c_void_p, i32p, C.c_int, C.c_int]
     h.refeng_submit_images.restype = C.c_uint64
@@ -53,16 +56,21 @@ class Replay:
     """Feeds the reference engine and the page pool the same requests; after every iterate() of the engine replays
     the new trace records into the pool and compares."""
 
-    def __init__(self, pkv, refeng, num_pages, page_tokens, slots, pps, budget, snapshots=8192):
+    def __init__(self, pkv, refeng, num_pages, page_tokens, slots, pps, budget, snapshots=8192, disk=None):
+        """disk: (directory, slots) turns the reference engine's snapshot disk tier on (gated I/O, see the driver)."""
         self.pkv, self.ref = pkv, refeng
         self.pt, self.slots, self.pps, self.budget, self.num_pages = page_tokens, slots, pps, budget, num_pages
-        self.eng = refeng.refeng_create(num_pages, page_tokens, slots, pps, budget, snapshots)
+        if disk:
+            self.eng = refeng.refeng_create_disk(num_pages, page_tokens, slots, pps, budget, snapshots, str(disk[0]).encode(), disk[1])
+        else:
+            self.eng = refeng.refeng_create(num_pages, page_tokens, slots, pps, budget, snapshots)
         self.pool = pkv.pkv_pool_create(num_pages, page_tokens, slots, pps, 1)
         self.tokens, self.handle, self.computed = {}, {}, {}
         self.waiting, self.running = deque(), []
         self.saved = set()
         self.images = {}
         self.first_hit = {}
+        self.aborts, self.aborted = [], set()
         self.cursor = 0
         self.tables_checked = 0
         self.max_cached = 0
@@ -86,6 +94,12 @@ class Replay:
         self.tokens[rid] = list(map(int, a))
         self.waiting.append(rid)
         return rid
+
+    def abort(self, rid):
+        """Engine::abort: the request ends at the start of the next iterate() (no step is ever in flight between two
+        iterate() calls of this driver), before that call's disk completions and admissions."""
+        self.ref.refeng_abort(self.eng, rid)
+        self.aborts.append(rid)
 
     def keys(self, rid):
         """The sequence's positions as 64-bit page-name keys (text: the token id; image positions: hash and offset)."""
@@ -122,6 +136,7 @@ class Replay:
                 break
             assert pkv.pkv_pool_assign_slot(pool, h) >= 0
             self.computed[rid] = computed
+            self.on_admitted(rid)
             self.first_hit.setdefault(rid, computed)
             self.running.append(rid)
             self.waiting.popleft()
@@ -131,6 +146,15 @@ class Replay:
         n = self.ref.refeng_trace_len(self.eng)
         ev = np.empty(n, np.int64)
         self.ref.refeng_trace_copy(self.eng, ev.ctypes.data)
+        for rid in self.aborts:                           # the engine's intake(): aborts come first
+            if rid in self.waiting or rid in self.running:
+                (self.waiting if rid in self.waiting else self.running).remove(rid)
+                if rid in self.handle:
+                    capi.check(self.pkv.pkv_pool_seq_close(self.pool, self.handle.pop(rid)))
+                self.on_finished(rid)
+                self.aborted.add(rid)
+        self.aborts = []
+        self.on_iterate_begin()
         self.admit()
         pkv, pool = self.pkv, self.pool
         i, pending_table = self.cursor, None
@@ -179,11 +203,15 @@ class Replay:
             elif kind == 3:
                 rid = int(ev[i + 1])
                 i += 2
+                if rid in self.aborted:                   # (already taken out, where the engine does it)
+                    continue
                 capi.check(pkv.pkv_pool_seq_close(pool, self.handle.pop(rid)))
                 self.running.remove(rid)
+                self.on_finished(rid)
             elif kind == 4:
                 running, waiting, free_pages, cached, preempt, snaps, free_snaps = (int(x) for x in ev[i + 1:i + 8])
                 i += 8
+                self.on_iterate_end()
                 self.on_counters(snaps, free_snaps)
                 assert preempt == 0, "scenario sized to avoid preemption"
                 assert (running, waiting) == (len(self.running), len(self.waiting))
@@ -192,6 +220,9 @@ class Replay:
                 self.max_cached = max(self.max_cached, cached)
                 if running == 1:
                     self.evicted_for_one_request = max(self.evicted_for_one_request, self.num_pages - free_pages)
+            elif kind == 5:
+                self.on_disk_counters(*(int(x) for x in ev[i + 1:i + 5]))
+                i += 5
             else:
                 raise AssertionError(f"unknown trace record {kind}")
         self.cursor = n
@@ -215,6 +246,21 @@ class Replay:
         pass
 
     def on_counters(self, snapshots, free_snapshots):
+        pass
+
+    def on_iterate_begin(self):     # the engine's poll_io, first thing in iterate()
+        pass
+
+    def on_finished(self, rid):     # the engine's release() of a request that ends
+        pass
+
+    def on_admitted(self, rid):     # the engine's start_load for a prefix that only the disk has
+        pass
+
+    def on_iterate_end(self):       # the engine's spill(), last thing in iterate()
+        pass
+
+    def on_disk_counters(self, disk_snapshots, snapshot_io, spills, disk_hits):
         pass
 
     def drain(self, limit=200000):

@@ -167,6 +167,7 @@ _SIGS = {
     "pkv_pool_alloc": (_i, [_vp, _i, _i]),
     "pkv_pool_register": (_i, [_vp, _i, c_i32p, _i, _i]),
     "pkv_pool_release": (_i, [_vp, _i]),
+    "pkv_pool_drop_prefix": (_i, [_vp, _i]),
     "pkv_pool_fork": (_i, [_vp, _i, _i]),
     "pkv_pool_cow": (_i, [_vp, _i, _i, _i, c_i32p, c_i32p, _i]),
     "pkv_pool_cow_pairs": (_i, [_vp, _i, _i, _i]),

@@ -217,6 +217,12 @@ void PagePool::release(int seq) {
   s.registered = 0;
 }
 
+void PagePool::drop_prefix(int seq) {
+  Seq& s = seqs_[size_t(seq)];
+  unref(s);
+  s.registered = 0;
+}
+
 // Fork: the child shares every page holding positions [0, ntokens) of the parent, a partial last page included.
 int PagePool::fork(int from, int ntokens) {
   const int npages = std::min((ntokens + page_tokens_ - 1) / page_tokens_, int(seqs_[size_t(from)].pages.size()));
@@ -445,6 +451,11 @@ int pkv_pool_register(pkv_pool* p, int seq, const int32_t* tokens, int ntokens, 
 int pkv_pool_release(pkv_pool* p, int seq) {
   if (!p || !p->impl.valid(seq)) return PKV_ERR_ARG;
   p->impl.release(seq);
+  return PKV_OK;
+}
+int pkv_pool_drop_prefix(pkv_pool* p, int seq) {
+  if (!p || !p->impl.valid(seq)) return PKV_ERR_ARG;
+  p->impl.drop_prefix(seq);
   return PKV_OK;
 }
 int pkv_pool_fork(pkv_pool* p, int from, int ntokens) {

@@ -73,6 +73,9 @@ class PagePool {
     register_pages(seq, Keys{tokens, nullptr}, ntokens, done_pos);
   }
   void release(int seq);
+  // The page half of drop_prefix (src/engine/engine.cpp:419-425): a matched prefix whose snapshot could not be read is
+  // given back, tail first; the sequence keeps its slot and starts over from position 0.
+  void drop_prefix(int seq);
 
   int fork(int from, int ntokens);
   // cow_pairs / compact_pairs: how many (source, destination) pairs the call would emit now; nothing changes.
