@@ -68,7 +68,9 @@ def test_oracle_f32_and_bf16_producers_agree():
 @pytest.mark.parametrize("T,n,ld,k", [(37, 5000, 5000, 512), (64, 32768, 32768, 512), (3, 8192, 8200, 1024),
                                       (4, 8193, 8193, 100), (2, 300, 304, 1024), (1, 1, 8, 1), (2, 49152, 49152, 1000),
                                       (3, 49153, 49160, 1024), (2, 200000, 200000, 64), (5, 17, 17, 3),
-                                      (2, 40960, 40960, 1024), (2, 40961, 40963, 1024), (200, 2000, 2001, 64)])
+                                      (2, 40960, 40960, 1024), (2, 40961, 40963, 1024), (200, 2000, 2001, 64),
+                                      (64, 4096, 4096, 512), (3, 4095, 4100, 1024), (3, 4097, 4097, 1024),
+                                      (3, 1025, 1025, 1000), (7, 2048, 2048, 1024), (5, 1024, 1024, 1024)])
 def test_topk_f32_gpu(pkv, cuda, kind, T, n, ld, k):
     g = tl.rng(82)
     s = scores_case(g, T, n, ld, kind)
