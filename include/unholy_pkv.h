@@ -335,8 +335,8 @@ PKV_API int pkv_ipc_close(void* ptr);
 /* ------------------------------------------------------------------------------------------------------------------
  * The pool sharded over the GPUs of one box by request ownership, with migration between shards: a C++ host object
  * (one process, one host thread and one stream per shard; no torch, no collective). The reference has no counterpart:
- * its pools are per card and pages never move (its DESIGN.md:119-123,148-149); the ordering pattern — a pull kernel
- * behind events — is that of src/engine/resident.hip:213-232,908-910. A shard owns `layers` bf16 row pools (and MXFP4
+ * its pools are per card and pages never move (the design notes at the root of its repository, lines 119-123 and
+ * 148-149); the ordering pattern — a pull kernel behind events — is that of src/engine/resident.hip:213-232,908-910. A shard owns `layers` bf16 row pools (and MXFP4
  * key pools when key_pools != 0), one page pool (the allocator above) and one block table. Calls on one pkv_shards
  * object must come from one thread at a time.
  * ---------------------------------------------------------------------------------------------------------------- */

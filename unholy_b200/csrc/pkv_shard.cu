@@ -8,8 +8,8 @@
 // next step waits for the pull, and the host releases the source's pages only after the pull's event has completed.
 // Nothing on the device spins on a flag.
 //
-// ewtodd/unholy has no sharded pool and pages never move between its cards (its DESIGN.md:119-123,148-149): parity for
-// this file is unpinned. The nearest pattern in the reference is the pull-kernel + event ordering of
+// ewtodd/unholy has no sharded pool and pages never move between its cards (the design notes at the root of its
+// repository, lines 119-123 and 148-149): parity for this file is unpinned. The nearest pattern in the reference is the pull-kernel + event ordering of
 // src/engine/resident.hip:213-232,908-910. The bookkeeping underneath is the pinned allocator (page_pool.hpp).
 #include <cuda_runtime.h>
 
