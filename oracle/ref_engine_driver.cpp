@@ -4,9 +4,13 @@
 // submitted chunk and state save, every finished request, and the allocator counters after each iterate(). The
 // page-pool tests replay that trace into the from-scratch allocator and compare block tables entry for entry.
 // TEST INFRASTRUCTURE ONLY; output goes to oracle/_ref/.
+#include <sys/syscall.h>
+#include <unistd.h>
+
 #include <atomic>
 #include <chrono>
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -119,10 +123,27 @@ class RecordingModel final : public StepModel {
 // holds operation number i until `released` exceeds i, so the test decides between which two iterate() calls an
 // operation completes. Waits are bounded: a forgotten release delays, it does not hang.
 struct Gate {
-  std::atomic<long> started{0}, released{0};
+  std::atomic<long> started{0}, released{0}, tid{0};
+  std::atomic<bool> in_hook{false};
   void hook() {
+    in_hook = true;
+    tid = long(::syscall(SYS_gettid));
     const long i = started.fetch_add(1);
     for (int spin = 0; spin < 200000 && released.load() <= i; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
+    in_hook = false;
+  }
+  // Whether the I/O thread sleeps outside the hook: with nothing at the gate that is its wait for the next operation.
+  bool idle() const {
+    if (in_hook.load() || tid.load() == 0) return false;
+    char path[64], buf[256];
+    std::snprintf(path, sizeof path, "/proc/self/task/%ld/stat", tid.load());
+    std::FILE* f = std::fopen(path, "r");
+    if (!f) return false;
+    const size_t n = std::fread(buf, 1, sizeof buf - 1, f);
+    std::fclose(f);
+    buf[n] = 0;
+    const char* p = std::strrchr(buf, ')');  // "pid (comm) S ..."
+    return p && p[1] == ' ' && p[2] == 'S';
   }
 };
 
@@ -183,14 +204,25 @@ void* refeng_create_disk(int num_pages, int page_tokens, int max_slots, int max_
   return d;
 }
 
-// Lets the next n gated disk operations run and returns when they have completed: the I/O thread runs one operation at
-// a time, so either a later operation has reached the gate (everything before it is done) or, with nothing queued
-// behind them, the last one has had 5 ms since it passed the gate (it is one 4 KB read or write).
-void refeng_io_release(void* h, int n) {
+// Lets the next n gated disk operations run and returns when they have completed. The I/O thread runs one operation
+// at a time: with `more` operations queued behind them, the next one reaching the gate means they are done; with none,
+// the thread going back to sleep outside the hook does (seen three times in a row, 200 us apart; 5 ms grace where
+// /proc cannot tell).
+void refeng_io_release(void* h, int n, int more) {
   auto* d = static_cast<Driver*>(h);
+  const auto nap = [](int us) { std::this_thread::sleep_for(std::chrono::microseconds(us)); };
   const long target = d->gate.released.fetch_add(n) + n;
-  for (int spin = 0; spin < 100000 && d->gate.started.load() < target; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
-  for (int spin = 0; spin < 50 && d->gate.started.load() <= target; ++spin) std::this_thread::sleep_for(std::chrono::microseconds(100));
+  for (int spin = 0; spin < 100000 && d->gate.started.load() < target; ++spin) nap(100);
+  if (more) {
+    for (int spin = 0; spin < 100000 && d->gate.started.load() <= target; ++spin) nap(100);
+    return;
+  }
+  int seen = 0;
+  for (int spin = 0; spin < 10000 && seen < 3; ++spin) {
+    seen = d->gate.idle() ? seen + 1 : 0;
+    nap(200);
+  }
+  if (seen < 3) nap(5000);
 }
 
 void refeng_destroy(void* h) { delete static_cast<Driver*>(h); }

@@ -37,7 +37,7 @@ def refeng():
     h = C.CDLL(str(libs["engine"]))
     h.refeng_create.restype, h.refeng_create.argtypes = C.c_void_p, [C.c_int] * 6
     h.refeng_create_disk.restype, h.refeng_create_disk.argtypes = C.c_void_p, [C.c_int] * 6 + [C.c_char_p, C.c_int]
-    h.refeng_io_release.argtypes = [C.c_void_p, C.c_int]
+    h.refeng_io_release.argtypes = [C.c_void_p, C.c_int, C.c_int]
     h.refeng_abort.argtypes = [C.c_void_p, C.c_uint64]
     h.refeng_destroy.argtypes = [C.c_void_p]
     h.refeng_submit.restype, h.refeng_submit.argtypes = C.c_uint64, [C.c_void_p, i32p, C.c_int, C.c_int]

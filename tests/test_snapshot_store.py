@@ -140,8 +140,9 @@ def test_snapshot_ids_match_reference_engine(pkv, refeng, ram_slots):
 # ---- part 1b: the same differential with the disk tier on ----------------------------------------------------------
 class Gate:
     """The store's I/O hook under the test's control, the twin of the reference driver's gate: operation number i waits
-    until `released` exceeds i; release(n) returns when those n operations have completed (a later one has reached the
-    gate, or the last one has had 5 ms since it passed)."""
+    until `released` exceeds i; release(n, more, idle) returns when those n operations have completed: with `more`
+    operations queued behind them, when the next one has reached the gate; with none, when idle() (the store's own
+    wait for an empty queue) returns."""
 
     def __init__(self):
         self.cv = threading.Condition()
@@ -155,13 +156,15 @@ class Gate:
             self.cv.notify_all()
             self.cv.wait_for(lambda: self.open or self.released > i, timeout=20)
 
-    def release(self, n):
+    def release(self, n, more, idle):
         with self.cv:
             self.released += n
             target = self.released
             self.cv.notify_all()
-            assert self.cv.wait_for(lambda: self.started >= target, timeout=10), "a released disk operation never started"
-            self.cv.wait_for(lambda: self.started > target, timeout=0.005)
+            assert self.cv.wait_for(lambda: self.started >= target + (1 if more else 0), timeout=10), \
+                "a released disk operation never started"
+        if not more:
+            idle()
 
     def open_for_good(self):
         with self.cv:
@@ -269,8 +272,9 @@ class DiskReplay(SnapReplay):
         self.ages = [a + 1 for a in self.ages] + [0] * new
         n = sum(1 for a in self.ages if a >= self.delay)
         if n:
-            self.ref.refeng_io_release(self.eng, n)
-            self.gate.release(n)
+            more = len(self.ages) > n
+            self.ref.refeng_io_release(self.eng, n, 1 if more else 0)
+            self.gate.release(n, more, lambda: self.pkv.pkv_snap_wait_idle(self.snap))
             self.ages = self.ages[n:]
 
     def settle(self):
