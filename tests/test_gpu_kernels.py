@@ -583,11 +583,15 @@ def test_gather_rows_fp8_every_code_and_scale(pkv, cuda):
     codes = g.integers(0, 256, size=(n, width), dtype=np.uint8)
     codes[:256, :] = np.arange(256, dtype=np.uint8)[:, None]          # rows of one code each
     codes[256:300, :] &= 0x7E                                           # rows without any NaN code (the paired decode)
+    mixed = g.integers(8, 0x7F, size=(60, width), dtype=np.uint8) | (g.integers(0, 2, size=(60, width), dtype=np.uint8) << 7)
+    mixed[g.random((60, width)) < 0.2] &= 0x80                          # normal codes with +-0 sprinkled in, no subnormal:
+    codes[300:360, :] = mixed                                           # the integer decode with masked zero lanes
+    codes[360:364, :] = 0                                               # rows never written
     scales = g.choice(np.array([0, 1, 5, 100, 119, 120, 126, 127, 128, 140, 200, 246, 247, 254, 255], np.uint8),
                       size=(n, width // block))
     vis = np.array([n, n], np.int32)
     idx = np.stack([g.permutation(n)[:k], g.permutation(n)[:k]]).astype(np.int32)
-    idx[0, :300] = np.arange(300)                                      # logical rows; the table scatters them
+    idx[0, :364] = np.arange(364)                                      # logical rows; the table scatters them
     phys_codes, phys_scales = np.zeros_like(codes), np.zeros_like(scales)
     for r in range(n):                                                 # logical row r lives at table[r // rpp] * rpp + r % rpp
         p = int(table[r // rpp]) * rpp + r % rpp

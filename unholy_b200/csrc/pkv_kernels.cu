@@ -1255,27 +1255,46 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
 // mantissa fields (eeee in the low exponent bits, mmm in the top mantissa bits), and the scale only adds to the
 // exponent. With one code per 16-bit lane of w (a byte permute), w * 16 puts the low seven bits in place and the sign
 // at bit 11; adding sign * 0xF0 moves it to bit 15 (0x80 * 16 + 0x80 * 0xF0 = 0x8000); nothing carries between the lanes
-// while the result is a normal bf16 number: scale bytes 7 .. 246. Exact: nothing is rounded. Codes with a zero exponent
-// field (zeros and e4m3 subnormals), the two NaN codes and the other scale bytes take the scalar decode, which follows
-// the reference operation for operation. (Decoding pairs on the conversion hardware instead, fp16 -> fp32 -> bf16, kept
-// that unit 84 % busy and took the same time: the kernel is bound by its stores, not by arithmetic.)
+// while the result is a normal bf16 number: scale bytes 7 .. 246. Exact: nothing is rounded. Three ways through a unit
+// of 16 codes, told apart with carries into bit 7 of each byte of t = code & 0x7f (no sum below exceeds 0xfe):
+//   t + 0x78 carries when t >= 8 (a normal code), t + 0x7f when t >= 1 (not a zero), t + 0x01 when t == 0x7f (a NaN);
+//   * all codes normal (what quantised rows hold almost everywhere): the integer decode as it stands;
+//   * zeros among them, nothing else (padding, rows never written): the same with the zero lanes masked to +-0;
+//   * an e4m3 subnormal, a NaN code or a scale byte outside 7 .. 246: the scalar decode, operation for operation as
+//     the reference does it.
+// (Decoding pairs on the conversion hardware instead, fp16 -> fp32 -> bf16, kept that unit 84 % busy and took the same
+// time: the kernel is bound by its stores, not by arithmetic.)
 __device__ __forceinline__ uint32_t dequant_lanes(uint32_t w, uint32_t exp_add) {
   return w * 16u + exp_add + (w & 0x00800080u) * 0xF0u;
 }
+__device__ __forceinline__ uint32_t dequant_lanes_zeros(uint32_t w, uint32_t exp_add) {
+  const uint32_t t = w & 0x007f007fu;
+  const uint32_t keep = (((t + 0x007f007fu) >> 7) & 0x00010001u) * 0xffffu;  // 0xffff in the lanes whose code is not a zero
+  return ((t * 16u + exp_add) & keep) | ((w & 0x00800080u) << 8);
+}
 __device__ __forceinline__ void dequant_unit(const uint4& q, uint32_t scale_bits, uint32_t* w16) {
   const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
-  // Any code with a zero exponent field, or any NaN code (low seven bits all ones)? A zero exponent field borrows into
-  // bit 7 of its byte when 8 is subtracted from every field; a NaN code carries into it when 1 is added to the low seven
-  // bits of every byte. (A borrow may also reach the next byte: a unit flagged for nothing only takes the slow way.)
-  uint32_t flag = 0;
+  uint32_t odd = 0, nonzero = 0xffffffffu;  // bit 7 of a byte of `odd`: a subnormal or a NaN; of `nonzero`: no zero so far
 #pragma unroll
-  for (int i = 0; i < 4; ++i) flag |= ((qs[i] & 0x78787878u) - 0x08080808u) | ((qs[i] & 0x7f7f7f7fu) + 0x01010101u);
-  if ((flag & 0x80808080u) == 0u && scale_bits - 7u <= 239u) {
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = qs[i] & 0x7f7f7f7fu, nz = t + 0x7f7f7f7fu;
+    odd |= (nz & ~(t + 0x78787878u)) | (t + 0x01010101u);
+    nonzero &= nz;
+  }
+  if ((odd & 0x80808080u) == 0u && scale_bits - 7u <= 239u) {
     const uint32_t exp_add = ((scale_bits - 7u) << 7) * 0x00010001u;  // the same exponent offset in both 16-bit lanes
+    if ((~nonzero & 0x80808080u) == 0u) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w16[2 * i] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4140u), exp_add);      // codes 0 and 1 of the word
-      w16[2 * i + 1] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4342u), exp_add);  // codes 2 and 3
+      for (int i = 0; i < 4; ++i) {
+        w16[2 * i] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4140u), exp_add);      // codes 0 and 1 of the word
+        w16[2 * i + 1] = dequant_lanes(__byte_perm(qs[i], 0u, 0x4342u), exp_add);  // codes 2 and 3
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w16[2 * i] = dequant_lanes_zeros(__byte_perm(qs[i], 0u, 0x4140u), exp_add);
+        w16[2 * i + 1] = dequant_lanes_zeros(__byte_perm(qs[i], 0u, 0x4342u), exp_add);
+      }
     }
   } else {
     const float sc = pkv::e8m0_bits_to_f32(scale_bits);
@@ -1321,8 +1340,10 @@ struct PoolList {
 };
 
 // 8 warps move data, a ninth resolves the NEXT tile's entries (index -> block table -> physical row) meanwhile, so the
-// three dependent loads of a resolution are off the data warps' path: one barrier per tile.
-constexpr int kFp8Threads = 256 + 32, kFp8CtasPerSm = 5;
+// three dependent loads of a resolution are off the data warps' path: one barrier per tile. Four CTAs per SM: the four
+// 16-byte units a data thread keeps in flight need 56 registers; at five CTAs (40 registers) they spill, and launches
+// of more than a few tiles per CTA ran 10 % slower for it.
+constexpr int kFp8Threads = 256 + 32, kFp8CtasPerSm = 4, kFp8Unroll = 4;
 template <class ROWS>
 __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(const uint8_t* __restrict__ codes,
                                                                  const uint8_t* __restrict__ scales,
@@ -1354,12 +1375,12 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
       const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
       const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
       uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
-      for (int base = 0; base < total; base += 4 * 256) {
-        uint4 q[4];
-        uint32_t sb[4];
-        bool live[4];
+      for (int base = 0; base < total; base += kFp8Unroll * 256) {
+        uint4 q[kFp8Unroll];
+        uint32_t sb[kFp8Unroll];
+        bool live[kFp8Unroll];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kFp8Unroll; ++j) {
           const int u = base + j * 256 + int(threadIdx.x);
           live[j] = false;
           if (u < total) {
@@ -1373,7 +1394,7 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kFp8Unroll; ++j) {
           const int u = base + j * 256 + int(threadIdx.x);
           if (u < total) {
             uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
