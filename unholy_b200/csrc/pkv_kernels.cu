@@ -1352,6 +1352,10 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
                                                                  const int32_t* __restrict__ q_visible, int T, int k,
                                                                  uint16_t* __restrict__ out, const PoolList pl) {
   __shared__ long long s_rid[2][kGatherRows];
+  // Programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream drains; nothing
+  // above reads global memory, everything below waits for that kernel's writes (the index list, the pools).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tiles_per_q = (k + kGatherRows - 1) / kGatherRows, upr = width >> 4, nb = width / block;
   const long long total_tiles = (long long)T * tiles_per_q;
   const bool resolver = threadIdx.x >= 256;
@@ -1788,6 +1792,27 @@ int dispatch_pipe(const StepParams& P, int shape, int ctas_per_sm, cudaStream_t 
   }
 }
 
+// Both fp8 gathers launch the same way: one wave of CTAs, programmatic dependent launch as the step kernels.
+template <class ROWSRC>
+int launch_gather_fp8(const ROWSRC& rows, const uint8_t* codes, const uint8_t* scales, int width, int block, const int32_t* idx,
+                      const int32_t* q_visible, int T, int k, uint16_t* out, const PoolList& pl, cudaStream_t stream) {
+  const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
+  const DeviceInfo& d = device_info();
+  const int sms = d.ok ? d.sms : 148;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm))));
+  cfg.blockDim = dim3(kFp8Threads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tuning().pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gather_fp8_kernel<ROWSRC>, codes, scales, rows, width, block, idx, q_visible, T, k, out, pl);
+  if (e != cudaSuccess) return fail_cuda("gather_fp8_kernel launch", e);
+  return PKV_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -2078,14 +2103,8 @@ int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32
   if (width <= 0 || width % 16 != 0 || block % 16 != 0 || rows_per_page <= 0)
     return fail(PKV_ERR_ARG, "pkv_gather_rows_fp8: width must be a positive multiple of 16");
   if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, "pkv_gather_rows_fp8: codes and out must be 16-byte aligned");
-  const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
-  const DeviceInfo& d = device_info();
-  const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
-  gather_fp8_kernel<OneSeqRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, OneSeqRows{OneTable{table, rows_per_page}}, width, block,
-                                                          idx, q_visible, T, k, out, PoolList{nullptr, nullptr, 0, 0});
-  PKV_LAUNCH_CHECK("gather_fp8_kernel");
-  return PKV_OK;
+  return launch_gather_fp8(OneSeqRows{OneTable{table, rows_per_page}}, codes, scales, width, block, idx, q_visible, T, k, out,
+                           PoolList{nullptr, nullptr, 0, 0}, static_cast<cudaStream_t>(stream));
 }
 
 // Shared by the two step-wide fp8 gathers: entries from idx [Q][k], or from pools [Q][kp] + pos (k = kp * pool + pool - 1).
@@ -2101,14 +2120,7 @@ static int step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uin
     return fail(PKV_ERR_ARG, std::string(name) + ": width must be a positive multiple of 16, the step needs pages and chunks");
   if (s.num_pages <= 0 || s.max_slots <= 0) return fail(PKV_ERR_ARG, std::string(name) + ": num_pages and max_slots must be positive");
   if (!aligned16(codes) || !aligned16(out)) return fail(PKV_ERR_ARG, std::string(name) + ": codes and out must be 16-byte aligned");
-  const long long tiles = (long long)s.Q * ((k + kGatherRows - 1) / kGatherRows);
-  const DeviceInfo& d = device_info();
-  const int sms = d.ok ? d.sms : 148;
-  const int grid = int(std::max<long long>(1, std::min<long long>(tiles, (long long)sms * kFp8CtasPerSm)));
-  gather_fp8_kernel<StepRows><<<grid, kFp8Threads, 0, stream>>>(codes, scales, StepRows{s}, width, block, idx, s.q_visible, s.Q,
-                                                                k, out, pl);
-  PKV_LAUNCH_CHECK("gather_fp8_kernel");
-  return PKV_OK;
+  return launch_gather_fp8(StepRows{s}, codes, scales, width, block, idx, s.q_visible, s.Q, k, out, pl, stream);
 }
 
 int pkv_step_gather_fp8(const pkv_step* step, const uint8_t* codes, const uint8_t* scales, int width, int block,
