@@ -46,10 +46,13 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not stale():
         return LIB
     LIB_DIR.mkdir(parents=True, exist_ok=True)
-    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *map(str, SOURCES), "-o", str(LIB)]
+    tmp = LIB.with_suffix(".so.tmp")  # linked beside the library and renamed: a reader never sees a half-written file
+    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), *map(str, SOURCES), "-o", str(tmp)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        tmp.unlink(missing_ok=True)
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB)
     if verbose:
         sys.stderr.write(res.stderr)
     return LIB
