@@ -1264,7 +1264,7 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
 //     the reference does it. (An integer-only path for subnormals, one code at a time through a seven-entry table,
 //     was no faster: 41.0 against 40.1 us on a quantised pool, where one warp in twenty meets a subnormal.)
 // (Decoding pairs on the conversion hardware instead, fp16 -> fp32 -> bf16, kept that unit 84 % busy and took the same
-// time: the kernel is bound by its stores, not by arithmetic.)
+// time at 40 registers per thread; what the kernel is short of is issue slots and overlap of its scattered loads.)
 __device__ __forceinline__ uint32_t dequant_lanes(uint32_t w, uint32_t exp_add) {
   return w * 16u + exp_add + (w & 0x00800080u) * 0xF0u;
 }
