@@ -537,7 +537,8 @@ def test_full_size_decode_step_properties(pkv, cuda):
     assert torch.equal(back.view(torch.int16), fake.view(torch.int16))
 
 
-@pytest.mark.parametrize("width,block,rpp,k", [(512, 64, 256, 2051), (128, 32, 64, 100), (256, 128, 64, 64)])
+@pytest.mark.parametrize("width,block,rpp,k", [(512, 64, 256, 2051), (128, 32, 64, 100), (256, 128, 64, 64), (384, 64, 64, 77),
+                                            (2048, 128, 32, 33), (64, 32, 64, 1000)])
 def test_gather_rows_fp8_dequant(pkv, cuda, width, block, rpp, k):
     """fp8 rows stored by pkv_store_rows_fp8, gathered and dequantised: equals the oracle's bf16(e4m3 * 2^scale) per
     entry, zero rows for masked entries; also equals fake_quant_fp8 of the original rows (store then gather-dequant is
