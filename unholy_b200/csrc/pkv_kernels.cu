@@ -115,6 +115,12 @@ Tuning& tuning() {
 // ---------------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(uint4* p, const uint4& v) { __stcs(p, v); }
+// 32 bytes at a 32-byte aligned address as one store instruction (sm_100: 256-bit global stores).
+__device__ __forceinline__ void st_stream32(void* p, const uint32_t* w) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Generic quantisers: one thread per 8 consecutive values of a row. rows x cols values; cols % block == 0,
@@ -1391,6 +1397,9 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
       const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
       const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
       uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
+      // A unit's 32 bytes leave as one 256-bit store where the output allows: two 128-bit stores from two instructions
+      // reach L2 as two partial writes of the same sector.
+      const bool wide_stores = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
       for (int base = 0; base < total; base += kFp8Unroll * 256) {
         uint4 q[kFp8Unroll];
         uint32_t sb[kFp8Unroll];
@@ -1415,8 +1424,12 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
           if (u < total) {
             uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (live[j]) dequant_unit(q[j], sb[j], w16);
-            st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
-            st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
+            if (wide_stores) {
+              st_stream32(o + 2 * u, w16);
+            } else {
+              st_stream(o + 2 * u, make_uint4(w16[0], w16[1], w16[2], w16[3]));
+              st_stream(o + 2 * u + 1, make_uint4(w16[4], w16[5], w16[6], w16[7]));
+            }
           }
         }
       }
