@@ -1266,9 +1266,9 @@ __global__ void __launch_bounds__(kVecThreads) gather_one_kernel(const uint16_t*
 //   t + 0x78 carries when t >= 8 (a normal code), t + 0x7f when t >= 1 (not a zero), t + 0x01 when t == 0x7f (a NaN);
 //   * all codes normal (what quantised rows hold almost everywhere): the integer decode as it stands;
 //   * zeros among them, nothing else (padding, rows never written): the same with the zero lanes masked to +-0;
-//   * an e4m3 subnormal, a NaN code or a scale byte outside 7 .. 246: the scalar decode, operation for operation as
-//     the reference does it. (An integer-only path for subnormals, one code at a time through a seven-entry table,
-//     was no faster: 41.0 against 40.1 us on a quantised pool, where one warp in twenty meets a subnormal.)
+//   * e4m3 subnormals or NaN codes among them (one warp in twenty of a quantised pool meets one somewhere in its 512
+//     codes): the masked decode, then those codes alone redone in floating point as the reference does it;
+//   * a scale byte outside 7 .. 246: all sixteen codes in floating point.
 // (Decoding pairs on the conversion hardware instead, fp16 -> fp32 -> bf16, kept that unit 84 % busy and took the same
 // time at 40 registers per thread; what the kernel is short of is issue slots and overlap of its scattered loads.)
 __device__ __forceinline__ uint32_t dequant_lanes(uint32_t w, uint32_t exp_add) {
@@ -1298,18 +1298,28 @@ __device__ __forceinline__ void dequant_unit(const uint4& q, uint32_t scale_bits
     }
     return;
   }
-  // Not all normal: zeros only (the masked decode), or a subnormal / NaN / extreme scale (the scalar decode)?
-  uint32_t odd = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t t = qs[i] & 0x7f7f7f7fu;
-    odd |= ((t + 0x7f7f7f7fu) & ~(t + 0x78787878u)) | (t + 0x01010101u);
-  }
-  if ((odd & 0x80808080u) == 0u && scale_ok) {
+  // Not all normal. With a scale in range: the masked decode for every code (zeros come out right, normal codes too),
+  // then only the codes that are e4m3 subnormals or NaNs are redone one by one in floating point, operation for
+  // operation as the reference does it (typically one code of the sixteen). Other scales: all sixteen that way.
+  if (scale_ok) {
+    uint32_t odd[4], any = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      const uint32_t t = qs[i] & 0x7f7f7f7fu;
+      odd[i] = (((t + 0x7f7f7f7fu) & ~(t + 0x78787878u)) | (t + 0x01010101u)) & 0x80808080u;
+      any |= odd[i];
       w16[2 * i] = dequant_lanes_zeros(__byte_perm(qs[i], 0u, 0x4140u), exp_add);
       w16[2 * i + 1] = dequant_lanes_zeros(__byte_perm(qs[i], 0u, 0x4342u), exp_add);
+    }
+    if (any == 0u) return;
+    const float sc = pkv::e8m0_bits_to_f32(scale_bits);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((odd[i >> 2] >> (8 * (i & 3) + 7)) & 1u) {
+        const uint32_t code = (qs[i >> 2] >> (8 * (i & 3))) & 0xffu;
+        const uint32_t bits = pkv::f32_to_bf16_bits(pkv::e4m3_bits_to_f32(code) * sc);
+        w16[i >> 1] = (i & 1) ? (w16[i >> 1] & 0x0000ffffu) | (bits << 16) : (w16[i >> 1] & 0xffff0000u) | bits;
+      }
     }
     return;
   }
