@@ -1385,41 +1385,57 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
   // A unit's row and column by shift and mask where the row length allows (a division costs as much as the decode);
   // the column's scale byte always by a shift: a block is 2, 4 or 8 units.
   const int upr_shift = (upr & (upr - 1)) == 0 ? 31 - __clz(upr) : -1, unit_to_block = 27 - __clz(block);
-  const long long total_tiles = (long long)T * tiles_per_q;
+  const unsigned total_tiles = unsigned(T) * unsigned(tiles_per_q);  // (the host keeps this below 2^31)
   const bool resolver = threadIdx.x >= 256;
-  const auto resolve = [&](long long w, int buf) {
-    const int t = int(w / tiles_per_q), e = int(w - (long long)t * tiles_per_q) * kGatherRows + int(threadIdx.x) - 256;
+  const auto resolve = [&](unsigned t, unsigned tile_in_q, int buf) {
+    const int e = int(tile_in_q) * kGatherRows + int(threadIdx.x) - 256;
     long long rid = -1;
     if (e < k) {
-      const int slot = rows.begin(t), vis = __ldg(&q_visible[t]);
-      const int row = pl.pools ? pl.entry(t, e) : __ldg(&idx[size_t(t) * k + e]);
-      if (row >= 0 && row < vis) rid = rows.rid(slot, t, row);
+      const int slot = rows.begin(int(t)), vis = __ldg(&q_visible[t]);
+      const int row = pl.pools ? pl.entry(int(t), e) : __ldg(&idx[size_t(t) * k + e]);
+      if (row >= 0 && row < vis) rid = rows.rid(slot, int(t), row);
     }
     s_rid[buf][threadIdx.x - 256] = rid;
   };
-  if (resolver && blockIdx.x < total_tiles) resolve(blockIdx.x, 0);
+  // A CTA's tiles are blockIdx.x, + gridDim.x, ...: (query row, tile in the row) advance by constants, one division per
+  // kernel instead of one per tile and thread.
+  const unsigned dq = gridDim.x / unsigned(tiles_per_q), dr = gridDim.x - dq * unsigned(tiles_per_q);
+  unsigned tq = blockIdx.x / unsigned(tiles_per_q), tile_in_q = blockIdx.x - tq * unsigned(tiles_per_q);
+  const auto next_tile = [&](unsigned& t, unsigned& i) {
+    t += dq, i += dr;
+    if (i >= unsigned(tiles_per_q)) i -= unsigned(tiles_per_q), ++t;
+  };
+  if (resolver && blockIdx.x < total_tiles) resolve(tq, tile_in_q, 0);
   __syncthreads();
+  // A data thread's units of a tile are tid, tid + 256, ...: with a power-of-two row length of at most 256 units their
+  // column is the same for every unit and their rows are 256 / upr apart.
+  const bool fixed_column = upr_shift >= 0 && upr <= 256;
+  const int tid = int(threadIdx.x);
+  const int r0 = fixed_column ? tid >> upr_shift : 0, c0 = fixed_column ? tid & (upr - 1) : 0, rstep = fixed_column ? 256 >> upr_shift : 0;
+  // A unit's 32 bytes leave as one 256-bit store where the output allows: two 128-bit stores from two instructions
+  // reach L2 as two partial writes of the same sector.
+  const bool wide_stores = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
   int buf = 0;
-  for (long long w = blockIdx.x; w < total_tiles; w += gridDim.x, buf ^= 1) {
+  for (unsigned w = blockIdx.x; w < total_tiles; w += gridDim.x, buf ^= 1) {
     if (resolver) {
-      if (w + gridDim.x < total_tiles) resolve(w + gridDim.x, buf ^ 1);
+      unsigned tn = tq, in = tile_in_q;
+      next_tile(tn, in);
+      if (w + gridDim.x < total_tiles) resolve(tn, in, buf ^ 1);
     } else {
-      const int t = int(w / tiles_per_q), e0 = int(w - (long long)t * tiles_per_q) * kGatherRows;
+      const int e0 = int(tile_in_q) * kGatherRows;
       const int nrows = min(kGatherRows, k - e0), total = nrows * upr;
-      uint4* o = reinterpret_cast<uint4*>(out + (size_t(t) * k + e0) * width);
-      // A unit's 32 bytes leave as one 256-bit store where the output allows: two 128-bit stores from two instructions
-      // reach L2 as two partial writes of the same sector.
-      const bool wide_stores = (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
+      uint4* o = reinterpret_cast<uint4*>(out + (size_t(tq) * k + e0) * width);
       for (int base = 0; base < total; base += kFp8Unroll * 256) {
         uint4 q[kFp8Unroll];
         uint32_t sb[kFp8Unroll];
         bool live[kFp8Unroll];
+        const int rb = fixed_column ? base >> upr_shift : 0;
 #pragma unroll
         for (int j = 0; j < kFp8Unroll; ++j) {
-          const int u = base + j * 256 + int(threadIdx.x);
+          const int u = base + j * 256 + tid;
           live[j] = false;
           if (u < total) {
-            const int r = upr_shift >= 0 ? u >> upr_shift : u / upr, c = u - r * upr;
+            const int r = fixed_column ? rb + r0 + j * rstep : u / upr, c = fixed_column ? c0 : u - r * upr;
             const long long rid = s_rid[buf][r];
             if (rid >= 0) {
               live[j] = true;
@@ -1430,7 +1446,7 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
         }
 #pragma unroll
         for (int j = 0; j < kFp8Unroll; ++j) {
-          const int u = base + j * 256 + int(threadIdx.x);
+          const int u = base + j * 256 + tid;
           if (u < total) {
             uint32_t w16[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (live[j]) dequant_unit(q[j], sb[j], w16);
@@ -1444,6 +1460,7 @@ __global__ void __launch_bounds__(kFp8Threads, kFp8CtasPerSm) gather_fp8_kernel(
         }
       }
     }
+    next_tile(tq, tile_in_q);
     __syncthreads();  // the next tile's rows are resolved, this tile's are no longer read
   }
 }
@@ -1832,6 +1849,7 @@ template <class ROWSRC>
 int launch_gather_fp8(const ROWSRC& rows, const uint8_t* codes, const uint8_t* scales, int width, int block, const int32_t* idx,
                       const int32_t* q_visible, int T, int k, uint16_t* out, const PoolList& pl, cudaStream_t stream) {
   const long long tiles = (long long)T * ((k + kGatherRows - 1) / kGatherRows);
+  if (tiles >= (1ll << 31) - (1 << 20)) return fail(PKV_ERR_LIMIT, "fp8 gather: more than 2^31 tiles of 32 entries in one call");
   const DeviceInfo& d = device_info();
   const int sms = d.ok ? d.sms : 148;
   cudaLaunchConfig_t cfg = {};
