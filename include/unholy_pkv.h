@@ -135,7 +135,9 @@ PKV_API int pkv_gather_rows(const uint16_t* pool, const int32_t* table, int rows
 /* The same gather over fp8 rows with dequantisation to bf16 — replaces the gather loop of the reference's GLM attention
  * (src/kernels/glm_fast.hip:29-31,190-227) for rows stored by pkv_store_rows_fp8 / glm_store_latent: entry -> physical
  * row -> e4m3 codes [width] and e8m0 scales [width/block] -> out bf16 [T][k][width] = code * 2^scale (exact in bf16);
- * masked entries (< 0 or >= q_visible[t]) give zero rows. */
+ * masked entries (< 0 or >= q_visible[t]) give zero rows. width a multiple of 16, codes and out 16-byte aligned (a
+ * 32-byte aligned out is written with 256-bit stores); launched with programmatic stream serialisation like the step
+ * kernels. */
 PKV_API int pkv_gather_rows_fp8(const uint8_t* codes, const uint8_t* scales, const int32_t* table, int rows_per_page, int width,
                         int block, const int32_t* idx, const int32_t* q_visible, int T, int k, uint16_t* out,
                         pkv_stream_t stream);
