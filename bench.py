@@ -600,7 +600,7 @@ def extra_ops(args, peak):
             o = ch["operations"][k]
             out[name] = {"GBps": o["GBps"], "frac_of_measured_peak": round(o["GBps"] / peak, 4), "ms": o["ms"], "algorithmic_GB": o["GB"],
                          "bit_exact": ch["bit_exact_check"]["ok"]}
-    out["churn_cfg4_what"] = ch["config"]["workload"] + f"; {ch['compaction_moves']} pages moved by compaction, {ch['cow_pages']} duplicated by copy-on-write (one launch)"
+    out["churn_cfg4_what"] = ch["config"]["workload"] + f"; {ch['compaction_moves']} pages moved by compaction, {ch['cow_pages']} duplicated by copy-on-write (one launch; timed warm, mean of five calls, L2 flushed before each)"
     return out
 
 
@@ -792,14 +792,27 @@ def measure_churn(args):
     timers = {}
     append_variant = capi.PKV_VARIANT_BULK if args.variant == "bulk" else 0
 
-    def timed(name, fn, nbytes):
+    flush_buf = []
+
+    def timed(name, fn, nbytes, warm=0, reps=1):
+        """Times fn on the device; with reps > 1 (fn must be idempotent) the mean of reps calls, each timed by itself
+        after `warm` untimed ones, with L2 flushed (a 256 MB fill) before every timed call."""
+        for _ in range(warm):
+            fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize()
+        total = 0.0
+        for r in range(reps):
+            if reps > 1:
+                if not flush_buf:
+                    flush_buf.append(torch.empty(1 << 25, dtype=torch.int64, device=dev))
+                flush_buf[0].fill_(r)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
         t = timers.setdefault(name, [0.0, 0])
-        t[0] += e0.elapsed_time(e1)
+        t[0] += total / reps
         t[1] += nbytes
 
     def pattern(writer, s0, n, layer):
@@ -843,8 +856,12 @@ def measure_churn(args):
             descs[2 * l + 1].page_bytes = FP4_PAGE_BYTES
         ids = torch.tensor(np.concatenate([src, dst]).astype(np.int32), device=dev)
         n = len(src)
+        # The copy-on-write launch is small (54 MB): a single cold call measures the first use of its kernel, not the
+        # launch; duplicating a page twice gives the same page, so it is timed warm, as the mean of five calls with L2
+        # flushed before each.
+        small = name == "cow_copy"
         timed(name, lambda: capi.check(lib.pkv_copy_pages(descs, 2 * L, ids.data_ptr(), ids.data_ptr() + 4 * n, n, N, N, sp)),
-              2 * n * L * (PAGE_BYTES + FP4_PAGE_BYTES))
+              2 * n * L * (PAGE_BYTES + FP4_PAGE_BYTES), warm=1 if small else 0, reps=5 if small else 1)
 
     def write_range(h, writer, s0, end, name, also_one_launch=False):
         while s0 < end:
